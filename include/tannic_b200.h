@@ -1,0 +1,277 @@
+/*
+ * tannic_b200.h — C ABI of the B200 (sm_100a) device backend for Tannic's operator core.
+ *
+ * Every entry point is `extern "C"`, takes plain records / pointers / sizes and returns a
+ * tn_status. The records below are layout-identical to the reference's own runtime PODs
+ * (include/tannic/runtime/tensor.h:37-73, types.h:29-44, status.h:26-32, streams.h:32-37,
+ * resources.h:35-59), so a `tannic::tensor_t*` can be passed where a `tn_tensor_t*` is
+ * expected without any marshalling. Each declaration cites the reference symbol it replaces.
+ *
+ * Conventions shared by all ops (reference include/tannic/callback.hpp:36-180):
+ *   - the caller owns every tensor; `dst` is allocated by the caller before the call with
+ *     `tn_dtype_size(dst->dtype) * dst->size` bytes and is written densely in logical
+ *     row-major order (its strides are read only by gemm / conv2d / cpy, as in the reference);
+ *   - `address` already contains the view's byte offset; strides are in ELEMENTS;
+ *   - ops are asynchronous on the stream passed in; `stream.address == 0` is the legacy
+ *     default stream;
+ *   - an op never allocates user-visible memory; scratch comes from the backend's own
+ *     stream-ordered pool;
+ *   - there is no CPU fallback: every failure is reported as a status, never by exit().
+ */
+#ifndef TANNIC_B200_H
+#define TANNIC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TN_MAX_RANK 8
+
+/* reference: enum type, include/tannic/runtime/types.h:29-44 (same order, same values) */
+typedef enum tn_dtype {
+    TN_ANY = 0,
+    TN_BOOLEAN,
+    TN_INT8,
+    TN_INT16,
+    TN_INT32,
+    TN_INT64,
+    TN_FLOAT16,
+    TN_BFLOAT16,
+    TN_FLOAT32,
+    TN_FLOAT64,
+    TN_COMPLEX64,
+    TN_COMPLEX128,
+    TN_UNKNOWN,
+    TN_TYPES
+} tn_dtype;
+
+/* reference: enum status, include/tannic/runtime/status.h:26-32 */
+typedef enum tn_status {
+    TN_SUCCESS = 0,
+    TN_ERROR,
+    TN_UNSUPPORTED_DTYPE,
+    TN_NULL_ALLOCATOR,
+    TN_INCOMPATIBLE_DEVICES
+} tn_status;
+
+/* reference: enum layout, include/tannic/runtime/tensor.h:37-41 */
+typedef enum tn_layout { TN_SINGLETON = 0, TN_CONTIGUOUS, TN_STRIDED } tn_layout;
+
+/* reference: environment / host / device records, include/tannic/runtime/resources.h:35-59 */
+typedef enum tn_environment_kind { TN_HOST = 0, TN_DEVICE } tn_environment_kind;
+typedef enum tn_host_traits { TN_PAGEABLE = 1 << 0, TN_PINNED = 1 << 1 } tn_host_traits;
+typedef struct tn_host_t { tn_host_traits traits; } tn_host_t;
+typedef struct tn_device_t { int id; } tn_device_t;
+typedef struct tn_environment_t {
+    tn_environment_kind kind;
+    union {
+        tn_host_t host;
+        tn_device_t device;
+    } resource;
+} tn_environment_t;
+
+/* reference: scalar_t / shape_t / strides_t / tensor_t, include/tannic/runtime/tensor.h:43-73 */
+typedef struct tn_scalar_t {
+    const void* address;
+    tn_dtype dtype;
+} tn_scalar_t;
+
+typedef struct tn_shape_t {
+    union {
+        const size_t* address;
+        size_t sizes[TN_MAX_RANK];
+    };
+} tn_shape_t;
+
+typedef struct tn_strides_t {
+    union {
+        const int64_t* address;
+        int64_t sizes[TN_MAX_RANK];
+    };
+} tn_strides_t;
+
+typedef struct tn_tensor_t {
+    void* address;            /* first logical element (view offset already applied)   */
+    uint8_t rank;             /* 0..8                                                   */
+    tn_shape_t shape;         /* extents                                                */
+    tn_strides_t strides;     /* element strides                                        */
+    tn_dtype dtype;
+    tn_environment_t environment;
+    size_t size;              /* logical element count                                  */
+    tn_layout layout;         /* hint computed by the front-end from the strides        */
+} tn_tensor_t;
+
+/* reference: stream_t, include/tannic/runtime/streams.h:32-34 (a cudaStream_t as integer) */
+typedef struct tn_stream_t { uintptr_t address; } tn_stream_t;
+
+/* ------------------------------------------------------------------ runtime ---------- */
+
+/* Bytes per element of a dtype (0 for any/unknown). reference: dsizeof, include/tannic/types.hpp */
+size_t tn_dtype_size(tn_dtype dtype);
+/* Text of the most recent failure on the calling thread ("" if none). No reference counterpart:
+ * the reference prints and calls exit() (src/cuda/exc.cuh:8-16). */
+const char* tn_last_error(void);
+
+/* reference: cuda::getDeviceCount / cuda::setDevice, src/cuda/mem.cu:9-17 */
+tn_status tn_device_count(int* count);
+tn_status tn_set_device(int id);
+
+/* reference: cuda::Streams::pop / put behind tannic::pop_stream / put_stream,
+ * src/cuda/streams.cu:23-38, src/bindings.cpp:22-42. One non-blocking stream per device is
+ * handed out in LIFO order, so successive ops of one thread are ordered; the pool is
+ * mutex-protected. */
+tn_status tn_stream_pop(const tn_device_t* device, tn_stream_t* stream);
+tn_status tn_stream_put(const tn_device_t* device, tn_stream_t stream);
+tn_status tn_stream_synchronize(tn_stream_t stream);
+
+/* reference: cuda::allocate / cuda::deallocate, src/cuda/mem.cu:19-36. Stream-ordered pool
+ * allocation (cudaMallocAsync on the device's pooled stream, release threshold = unlimited so
+ * freed blocks are reused without returning to the driver). */
+tn_status tn_allocate(const tn_device_t* device, size_t nbytes, void** address);
+tn_status tn_deallocate(const tn_device_t* device, void* address);
+
+/* reference: cuda::copyFromHost / copyDeviceToHost / compareFromHost, src/cuda/mem.cu:38-65 */
+tn_status tn_copy_from_host(const tn_device_t* device, const void* host, void* dev, size_t nbytes);
+tn_status tn_copy_to_host(const tn_device_t* device, const void* dev, void* host, size_t nbytes);
+tn_status tn_compare_from_host(const tn_device_t* device, const void* host, const void* dev,
+                               size_t nbytes, int* equal);
+/* reference: cuda::copy (Tensor::to), src/cuda/mem.cu:67-93 — direction from the two
+ * environments; pinned host memory copies asynchronously on `stream`, pageable synchronously. */
+tn_status tn_copy(const tn_tensor_t* src, tn_tensor_t* dst, size_t nbytes, tn_stream_t stream);
+/* Pinned host memory for the transfer path. The reference's Host(pinned) throws
+ * "not supported yet" (src/resources.cpp:24-38). */
+tn_status tn_host_allocate_pinned(size_t nbytes, void** address);
+tn_status tn_host_free_pinned(void* address);
+
+/* ------------------------------------------------------------------ elementwise ------ */
+
+/* reference: cuda::add/sub/mul/pow, src/cuda/ops-binary.cu:485-499 (CPU twin
+ * src/cpu/ops-binary.cpp:434-448). NumPy broadcast, operands may be strided views; the result
+ * is written in dst->dtype (never wider than the buffer, unlike the reference's half x int
+ * and pow(half,half) entries). Arithmetic class: any float64 or (int64 with a float) ->
+ * float64; any other float -> float32; integers wrap modulo 2^n. */
+tn_status tn_add(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_sub(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_mul(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_pow(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream);
+
+/* reference: cuda::neg/repack/log/exp/sqrt/rsqrt/abs/sin/cos/tan/sinh/cosh/tanh,
+ * src/cuda/ops-unary.cu:249-444 (CPU twin src/cpu/ops-unary.cpp:202-370). Half types compute in
+ * float32 and round once on store; rsqrt(x, eps) = 1/sqrt(x + eps). */
+tn_status tn_neg(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_repack(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_log(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_exp(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_sqrt(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_rsqrt(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, float eps);
+tn_status tn_abs(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_sin(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_cos(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_tan(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_sinh(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_cosh(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_tanh(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream);
+
+/* reference: cuda::scale, src/cuda/ops-scale.cu:126-128 (CPU twin src/cpu/ops-scale.cpp:120-122):
+ * dst = src * scalar, scalar dtype must equal the tensor dtype. */
+tn_status tn_scale(const tn_tensor_t* src, const tn_scalar_t* scalar, tn_tensor_t* dst,
+                   tn_stream_t stream);
+
+/* Fused elementwise program: the whole expression tree in ONE pass over HBM. Replaces the
+ * chain of per-node launches and full-size temporaries that Binary<>/Function<>::forward emit
+ * (include/tannic/tensor.hpp:351-371, include/tannic/functions.hpp:52-57). Semantics are those
+ * of the chain: every node computes in float32 (half types) and is rounded to the storage dtype
+ * before the next node reads it. All inputs and dst share one dtype. */
+typedef enum tn_eltwise_opcode {
+    TN_OP_ADD = 0, TN_OP_SUB, TN_OP_MUL, TN_OP_POW,
+    TN_OP_NEG, TN_OP_LOG, TN_OP_EXP, TN_OP_SQRT, TN_OP_RSQRT, TN_OP_ABS,
+    TN_OP_SIN, TN_OP_COS, TN_OP_TAN, TN_OP_SINH, TN_OP_COSH, TN_OP_TANH,
+    TN_OP_SCALE,
+    TN_OP_COUNT
+} tn_eltwise_opcode;
+
+#define TN_PROGRAM_MAX_INPUTS 4
+#define TN_PROGRAM_MAX_NODES 16
+
+/* Node k produces value (TN_PROGRAM_MAX_INPUTS + k); operands name an input (0..3) or an
+ * earlier node's value. The last node is the result. `imm` is eps for RSQRT and the factor
+ * for SCALE. */
+typedef struct tn_eltwise_node_t {
+    uint8_t opcode;
+    uint8_t lhs;
+    uint8_t rhs;  /* ignored by unary nodes */
+    float imm;
+} tn_eltwise_node_t;
+
+tn_status tn_eltwise_program(const tn_tensor_t* const* inputs, int n_inputs,
+                             const tn_eltwise_node_t* nodes, int n_nodes,
+                             tn_tensor_t* dst, tn_stream_t stream);
+
+/* ------------------------------------------------------------------ contractions ----- */
+
+/* reference: cuda::gemm, src/cuda/matmul.cu:189-191 (CPU twin src/cpu/matmul.cpp:254-256).
+ * Batched C[b] = A[b] . B[b]; batch dims broadcast; a transposed operand is recognised by
+ * stride[-1] > stride[-2]. fp16/bf16 (and their mixes with fp32) accumulate in float32 and run
+ * on the tcgen05 tensor-core path when the operands are TMA-addressable, otherwise on the SIMT
+ * path; integer pairs accumulate in the output integer type. The batch counter is 64-bit
+ * (the reference's wraps at 256, src/cuda/matmul.cu:45). */
+tn_status tn_gemm(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream);
+
+/* matmul followed by multiplication with a scalar of dst's dtype, in one kernel:
+ * dst = round(round(A.B) * scale). Replaces the gemm + scale pair of
+ * `matmul(Q, K^T) * 0.125` (src/transformations.cpp:33-39 then src/operations.cpp:40-43). */
+tn_status tn_gemm_scaled(const tn_tensor_t* a, const tn_tensor_t* b, const tn_scalar_t* scale,
+                         tn_tensor_t* dst, tn_stream_t stream);
+
+/* reference: cuda::conv2d (two overloads), src/cuda/conv2d.cu:216-222 (CPU twin
+ * src/cpu/conv2d.cpp:257-265). NCHW cross-correlation, zero padding, floor output size,
+ * bias (rank 1, [Cout]) seeds the accumulator. Rank / shape mismatches return TN_ERROR. */
+tn_status tn_conv2d(const tn_tensor_t* x, const tn_tensor_t* w, tn_tensor_t* y, tn_stream_t stream,
+                    const size_t pad[2], const size_t stride[2]);
+tn_status tn_conv2d_bias(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_t* bias,
+                         tn_tensor_t* y, tn_stream_t stream, const size_t pad[2],
+                         const size_t stride[2]);
+
+/* ------------------------------------------------------------------ reductions ------- */
+
+/* reference: cuda::argmax/argmin/argsum/argmean, src/cuda/argred.cu:167-213 (CPU twin
+ * src/cpu/argred.cpp:289-347). Index results are int64; the first occurrence wins and NaN is
+ * never selected; sum/mean keep the input dtype and accumulate in float32 (half types),
+ * float64 (float32/float64) or int64 (integers), as the reference's device path does. */
+tn_status tn_argmax(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, uint8_t axis);
+tn_status tn_argmin(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, uint8_t axis);
+tn_status tn_argsum(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, uint8_t axis);
+tn_status tn_argmean(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, uint8_t axis);
+/* Value maximum along an axis (= src[argmax]); the reference has no such op
+ * (include/tannic/reductions.hpp:41-44 lists argmax/argmin/sum/mean only). */
+tn_status tn_max(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, uint8_t axis);
+/* max, sum and argmax along one axis in a single pass over src (each output may be NULL).
+ * Replaces three cuda::arg* launches that would each re-read src. */
+tn_status tn_reduce_stats(const tn_tensor_t* src, tn_tensor_t* max_out, tn_tensor_t* sum_out,
+                          tn_tensor_t* argmax_out, tn_stream_t stream, uint8_t axis);
+
+/* ------------------------------------------------------------------ utilities -------- */
+
+/* reference: cuda::cpy, src/cuda/cpy.cu:55-69 — strided -> strided copy (slice assignment). */
+tn_status tn_cpy(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream);
+/* reference: cuda::allclose, src/cuda/val.cu:82-89 — |a-b| <= atol + rtol*|b| for all elements;
+ * synchronises the stream and writes 0/1 to *close. */
+tn_status tn_allclose(const tn_tensor_t* a, const tn_tensor_t* b, tn_stream_t stream, double rtol,
+                      double atol, int* close);
+
+/* Number of CTAs of the tensor-core kernels that gave up on a bounded wait since load (0 in a
+ * healthy run); synchronises the device. The reference has no device-side waits to bound. */
+tn_status tn_device_errors(unsigned int* count);
+
+/* Number of kernels this library has launched on the calling process since load (all threads).
+ * Used by the benchmark to count launches inside its timed region. */
+uint64_t tn_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TANNIC_B200_H */

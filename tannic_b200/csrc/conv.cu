@@ -1,0 +1,169 @@
+// tn_conv2d / tn_conv2d_bias: NCHW cross-correlation with zero padding. Replaces
+// src/cuda/conv2d.cu of the reference (one single-thread block per output element).
+//
+// Paths:
+//   1x1, stride 1, no padding, dense fp16/bf16 tensors -> batched tensor-core GEMM
+//        y[n] = W[Cout, Cin] . x[n][Cin, H*W]   (x[n] is an N-major B operand);
+//   everything else -> direct SIMT kernel (any dtype, any strides), accumulating in float32
+//        for half/float32, float64 for float64 and wrapping int64 for integers.
+#include "gemm_tc.cuh"
+
+namespace tnb {
+namespace {
+
+constexpr int kThreads = 256;
+
+struct ConvArgs {
+    const void* x;
+    const void* w;
+    const void* bias;
+    void* y;
+    int dt;
+    int64_t N, Cin, H, W, Cout, Kh, Kw, Ho, Wo;
+    int64_t pad_h, pad_w, str_h, str_w;
+    int64_t xs[4], ws[4], ys[4];
+    int64_t bias_stride;
+    int64_t total;
+};
+
+// One thread per output element; threads of a warp share (n, co) almost always, so the
+// weight loads are broadcasts and the x loads are contiguous along the output row.
+template <typename C>
+__global__ void __launch_bounds__(kThreads) conv2d_direct(const __grid_constant__ ConvArgs g) {
+    const int64_t step = (int64_t)gridDim.x * kThreads;
+    for (int64_t o = (int64_t)blockIdx.x * kThreads + threadIdx.x; o < g.total; o += step) {
+        int64_t rem = o;
+        const int64_t ow = rem % g.Wo; rem /= g.Wo;
+        const int64_t oh = rem % g.Ho; rem /= g.Ho;
+        const int64_t co = rem % g.Cout;
+        const int64_t n = rem / g.Cout;
+        // the bias seeds the accumulator (src/cpu/conv2d.cpp:66-113)
+        C acc = g.bias ? load_as<C>(g.bias, g.dt, co * g.bias_stride) : C(0);
+        const int64_t base_h = oh * g.str_h - g.pad_h, base_w = ow * g.str_w - g.pad_w;
+        for (int64_t ci = 0; ci < g.Cin; ++ci) {
+            for (int64_t kh = 0; kh < g.Kh; ++kh) {
+                const int64_t ih = base_h + kh;
+                if (ih < 0 || ih >= g.H) continue;
+                for (int64_t kw = 0; kw < g.Kw; ++kw) {
+                    const int64_t iw = base_w + kw;
+                    if (iw < 0 || iw >= g.W) continue;
+                    const C xv = load_as<C>(g.x, g.dt, n * g.xs[0] + ci * g.xs[1] + ih * g.xs[2] + iw * g.xs[3]);
+                    const C wv = load_as<C>(g.w, g.dt, co * g.ws[0] + ci * g.ws[1] + kh * g.ws[2] + kw * g.ws[3]);
+                    if constexpr (std::is_same<C, int64_t>::value) acc = (int64_t)((uint64_t)acc + (uint64_t)xv * (uint64_t)wv);
+                    else acc += xv * wv;
+                }
+            }
+        }
+        store_as<C>(g.y, g.dt, n * g.ys[0] + co * g.ys[1] + oh * g.ys[2] + ow * g.ys[3], acc);
+    }
+}
+
+bool dense_nchw(const tn_tensor_t* t) {
+    int64_t expect = 1;
+    for (int d = 3; d >= 0; --d) {
+        if (t->shape.sizes[d] != 1 && t->strides.sizes[d] != expect) return false;
+        expect *= (int64_t)t->shape.sizes[d];
+    }
+    return true;
+}
+
+tn_status conv_impl(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_t* bias, tn_tensor_t* y,
+                    tn_stream_t stream, const size_t pad[2], const size_t stride[2]) {
+    if (!x || !w || !y || !pad || !stride) return fail(TN_ERROR, "null argument");
+    // dtypes must match, as in the reference's tables (src/cpu/conv2d.cpp:221-253)
+    if (x->dtype != w->dtype || !is_numeric(x->dtype) || y->dtype != x->dtype || (bias && bias->dtype != x->dtype))
+        return fail(TN_UNSUPPORTED_DTYPE, "conv2d: dtypes (%d, %d) -> %d unsupported", (int)x->dtype, (int)w->dtype, (int)y->dtype);
+    if (x->rank != 4 || w->rank != 4 || y->rank != 4 || (bias && bias->rank != 1))
+        return fail(TN_ERROR, "conv2d: expected ranks 4, 4 -> 4 (bias 1)");
+    if (stride[0] == 0 || stride[1] == 0) return fail(TN_ERROR, "conv2d: zero stride");
+    ConvArgs g;
+    g.x = x->address;
+    g.w = w->address;
+    g.bias = bias ? bias->address : nullptr;
+    g.y = y->address;
+    g.dt = x->dtype;
+    g.N = (int64_t)x->shape.sizes[0];
+    g.Cin = (int64_t)x->shape.sizes[1];
+    g.H = (int64_t)x->shape.sizes[2];
+    g.W = (int64_t)x->shape.sizes[3];
+    g.Cout = (int64_t)w->shape.sizes[0];
+    g.Kh = (int64_t)w->shape.sizes[2];
+    g.Kw = (int64_t)w->shape.sizes[3];
+    if ((int64_t)w->shape.sizes[1] != g.Cin) return fail(TN_ERROR, "conv2d: kernel expects %zu input channels, signal has %lld", w->shape.sizes[1], (long long)g.Cin);
+    if (bias && (int64_t)bias->shape.sizes[0] != g.Cout) return fail(TN_ERROR, "conv2d: bias length %zu, %lld output channels", bias->shape.sizes[0], (long long)g.Cout);
+    g.pad_h = (int64_t)pad[0];
+    g.pad_w = (int64_t)pad[1];
+    g.str_h = (int64_t)stride[0];
+    g.str_w = (int64_t)stride[1];
+    if (g.H + 2 * g.pad_h < g.Kh || g.W + 2 * g.pad_w < g.Kw) return fail(TN_ERROR, "conv2d: kernel larger than the padded signal");
+    g.Ho = (g.H + 2 * g.pad_h - g.Kh) / g.str_h + 1;  // floor, src/cpu/conv2d.cpp:136-137
+    g.Wo = (g.W + 2 * g.pad_w - g.Kw) / g.str_w + 1;
+    if ((int64_t)y->shape.sizes[0] != g.N || (int64_t)y->shape.sizes[1] != g.Cout || (int64_t)y->shape.sizes[2] != g.Ho ||
+        (int64_t)y->shape.sizes[3] != g.Wo)
+        return fail(TN_ERROR, "conv2d: result shape does not match [%lld,%lld,%lld,%lld]", (long long)g.N, (long long)g.Cout, (long long)g.Ho, (long long)g.Wo);
+    if (x->environment.kind != TN_DEVICE || w->environment.kind != TN_DEVICE ||
+        x->environment.resource.device.id != w->environment.resource.device.id ||
+        x->environment.resource.device.id != y->environment.resource.device.id ||
+        (bias && (bias->environment.kind != TN_DEVICE || bias->environment.resource.device.id != y->environment.resource.device.id)))
+        return fail(TN_INCOMPATIBLE_DEVICES, "operands must live on one device");
+    TN_TRY(use_device_of(y));
+    for (int d = 0; d < 4; ++d) {
+        g.xs[d] = x->strides.sizes[d];
+        g.ws[d] = w->strides.sizes[d];
+        g.ys[d] = y->strides.sizes[d];
+    }
+    g.bias_stride = bias ? bias->strides.sizes[0] : 0;
+    g.total = g.N * g.Cout * g.Ho * g.Wo;
+    if (g.total == 0) return TN_SUCCESS;
+    cudaStream_t s = as_cuda(stream);
+
+    if (is_half(g.dt) && g.Kh == 1 && g.Kw == 1 && g.str_h == 1 && g.str_w == 1 && g.pad_h == 0 && g.pad_w == 0 &&
+        dense_nchw(x) && dense_nchw(w) && dense_nchw(y) && (!bias || g.bias_stride == 1)) {
+        TcGemm p;
+        p.a = g.w;
+        p.b = g.x;
+        p.d = g.y;
+        p.bias = g.bias;
+        p.ab_dtype = p.d_dtype = g.dt;
+        p.M = g.Cout;
+        p.N = g.H * g.W;
+        p.K = g.Cin;
+        p.lda = g.Cin;
+        p.ldb = p.N;
+        p.ldd = p.N;
+        p.batches = g.N;
+        p.a_batch = 0;
+        p.b_batch = g.Cin * p.N;
+        p.d_batch = g.Cout * p.N;
+        p.b_n_major = true;
+        if (tc_gemm_eligible(p)) return tc_gemm(p, s);
+    }
+
+    const int64_t cap = (int64_t)sm_count() * 8;
+    int64_t blocks = ceil_div(g.total, kThreads);
+    if (blocks > cap) blocks = cap;
+    if (g.dt == TN_FLOAT64) conv2d_direct<double><<<(int)blocks, kThreads, 0, s>>>(g);
+    else if (is_float(g.dt)) conv2d_direct<float><<<(int)blocks, kThreads, 0, s>>>(g);
+    else conv2d_direct<int64_t><<<(int)blocks, kThreads, 0, s>>>(g);
+    return after_launch("conv2d_direct");
+}
+
+}  // namespace
+}  // namespace tnb
+
+using namespace tnb;
+
+extern "C" {
+
+tn_status tn_conv2d(const tn_tensor_t* x, const tn_tensor_t* w, tn_tensor_t* y, tn_stream_t stream, const size_t pad[2],
+                    const size_t stride[2]) {
+    return conv_impl(x, w, nullptr, y, stream, pad, stride);
+}
+
+tn_status tn_conv2d_bias(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_t* bias, tn_tensor_t* y,
+                         tn_stream_t stream, const size_t pad[2], const size_t stride[2]) {
+    if (!bias) return fail(TN_ERROR, "null bias");
+    return conv_impl(x, w, bias, y, stream, pad, stride);
+}
+
+}  // extern "C"

@@ -1,0 +1,853 @@
+// Elementwise family: add/sub/mul/pow with NumPy broadcast, the unary math functions, scale,
+// and the fused elementwise program. Replaces src/cuda/ops-binary.cu, ops-unary.cu, ops-scale.cu
+// of the reference.
+//
+// Three kernels stream HBM exactly once with 128-bit accesses:
+//   ew_flat     both operands dense (or a single broadcast scalar) -> one flat range;
+//   ew_rows     dst viewed as [rows, cols]; each operand is dense along cols or constant
+//               along cols, with an arbitrary row pitch (covers row- and column-broadcast);
+//   ew_program  the same [rows, cols] geometry for up to 4 inputs and a list of nodes.
+// Everything else (mixed dtypes, ragged widths, arbitrary strided views) goes through
+// ew_generic, which decodes the linear index per element.
+#include "common.cuh"
+
+#include <cmath>
+#include <cstring>
+
+namespace tnb {
+namespace {
+
+constexpr int kThreads = 256;
+
+struct Imm {
+    double f;
+    int64_t i;
+};
+
+// ------------------------------------------------------------------ the operations ----
+template <int OP, bool FAST, typename C>
+__device__ __forceinline__ C apply_op(C a, C b, Imm imm) {
+    if constexpr (std::is_floating_point<C>::value) {
+        if constexpr (OP == TN_OP_ADD) return a + b;
+        else if constexpr (OP == TN_OP_SUB) return a - b;
+        else if constexpr (OP == TN_OP_MUL) return a * b;
+        else if constexpr (OP == TN_OP_SCALE) return a * static_cast<C>(imm.f);
+        else if constexpr (OP == TN_OP_NEG) return -a;
+        else if constexpr (OP == TN_OP_ABS) return fabs(a);
+        else if constexpr (std::is_same<C, float>::value) {
+            if constexpr (OP == TN_OP_POW) return powf(a, b);
+            else if constexpr (OP == TN_OP_LOG) return FAST ? __logf(a) : logf(a);
+            else if constexpr (OP == TN_OP_EXP) return FAST ? __expf(a) : expf(a);
+            else if constexpr (OP == TN_OP_SQRT) return sqrtf(a);
+            else if constexpr (OP == TN_OP_RSQRT) {
+                // The reference evaluates 1.0 / sqrt(x + eps) in double and narrows once
+                // (src/cpu/ops-unary.cpp:138-146); half storage is insensitive to it.
+                if constexpr (FAST) return 1.0f / sqrtf(a + static_cast<float>(imm.f));
+                else return static_cast<float>(1.0 / sqrt(static_cast<double>(a) + imm.f));
+            }
+            else if constexpr (OP == TN_OP_SIN) return sinf(a);
+            else if constexpr (OP == TN_OP_COS) return cosf(a);
+            else if constexpr (OP == TN_OP_TAN) return tanf(a);
+            else if constexpr (OP == TN_OP_SINH) return sinhf(a);
+            else if constexpr (OP == TN_OP_COSH) return coshf(a);
+            else if constexpr (OP == TN_OP_TANH) return tanhf(a);
+            else return a;
+        } else {
+            if constexpr (OP == TN_OP_POW) return pow(a, b);
+            else if constexpr (OP == TN_OP_LOG) return log(a);
+            else if constexpr (OP == TN_OP_EXP) return exp(a);
+            else if constexpr (OP == TN_OP_SQRT) return sqrt(a);
+            else if constexpr (OP == TN_OP_RSQRT) return 1.0 / sqrt(a + imm.f);
+            else if constexpr (OP == TN_OP_SIN) return sin(a);
+            else if constexpr (OP == TN_OP_COS) return cos(a);
+            else if constexpr (OP == TN_OP_TAN) return tan(a);
+            else if constexpr (OP == TN_OP_SINH) return sinh(a);
+            else if constexpr (OP == TN_OP_COSH) return cosh(a);
+            else if constexpr (OP == TN_OP_TANH) return tanh(a);
+            else return a;
+        }
+    } else {
+        // Integers wrap modulo 2^n: do the arithmetic unsigned, narrow on store.
+        using U = typename std::make_unsigned<C>::type;
+        U x = static_cast<U>(a), y = static_cast<U>(b);
+        if constexpr (OP == TN_OP_ADD) return static_cast<C>(x + y);
+        else if constexpr (OP == TN_OP_SUB) return static_cast<C>(x - y);
+        else if constexpr (OP == TN_OP_MUL) return static_cast<C>(x * y);
+        else if constexpr (OP == TN_OP_SCALE) return static_cast<C>(x * static_cast<U>(imm.i));
+        else if constexpr (OP == TN_OP_NEG) return static_cast<C>(U(0) - x);
+        else if constexpr (OP == TN_OP_ABS) return a < 0 ? static_cast<C>(U(0) - x) : a;
+        else return a;
+    }
+}
+
+constexpr bool op_is_binary(int op) { return op <= TN_OP_POW; }
+constexpr bool op_is_float_only(int op) {
+    return op == TN_OP_POW || (op >= TN_OP_LOG && op <= TN_OP_TANH && op != TN_OP_ABS);
+}
+
+template <typename T> struct alignas(16) Vec {
+    static constexpr int N = 16 / sizeof(T);
+    T e[N];
+};
+
+template <typename T>
+__device__ __forceinline__ Vec<T> load_vec(const T* p) {
+    Vec<T> v;
+    *reinterpret_cast<uint4*>(&v) = __ldg(reinterpret_cast<const uint4*>(p));
+    return v;
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T* p, const Vec<T>& v) {
+    *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(&v);
+}
+template <typename T>
+__device__ __forceinline__ Vec<T> splat_vec(T s) {
+    Vec<T> v;
+#pragma unroll
+    for (int i = 0; i < Vec<T>::N; ++i) v.e[i] = s;
+    return v;
+}
+
+template <typename T, int OP>
+__device__ __forceinline__ Vec<T> apply_vec(const Vec<T>& a, const Vec<T>& b, Imm imm) {
+    using C = typename compute_of<T>::type;
+    constexpr bool FAST = sizeof(T) == 2;
+    Vec<T> d;
+#pragma unroll
+    for (int i = 0; i < Vec<T>::N; ++i)
+        d.e[i] = from_compute<T, C>(apply_op<OP, FAST, C>(to_compute<C>(a.e[i]), to_compute<C>(b.e[i]), imm));
+    return d;
+}
+
+template <typename T, int OP>
+__device__ __forceinline__ T apply_one(T a, T b, Imm imm) {
+    using C = typename compute_of<T>::type;
+    constexpr bool FAST = sizeof(T) == 2;
+    return from_compute<T, C>(apply_op<OP, FAST, C>(to_compute<C>(a), to_compute<C>(b), imm));
+}
+
+// ------------------------------------------------------------------ ew_flat -----------
+// d[i] = op(a[i*sa], b[i*sb]) for i < n with sa, sb in {0, 1}. Vector body + scalar tail.
+template <typename T, int OP>
+__global__ void __launch_bounds__(kThreads) ew_flat(const T* __restrict__ a, const T* __restrict__ b,
+                                                    T* __restrict__ d, int64_t n, int sa, int sb, Imm imm) {
+    constexpr int V = Vec<T>::N;
+    constexpr int UNROLL = 4;
+    constexpr bool BIN = op_is_binary(OP);
+    const int64_t nvec = n / V;
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    const int64_t tid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    Vec<T> ca, cb;
+    if (sa == 0) ca = splat_vec(a[0]);
+    if (BIN && sb == 0) cb = splat_vec(b[0]);
+    int64_t i = tid;
+    for (; i + (UNROLL - 1) * stride < nvec; i += UNROLL * stride) {
+        Vec<T> va[UNROLL], vb[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int64_t off = (i + u * stride) * V;
+            va[u] = sa ? load_vec(a + off) : ca;
+            if (BIN) vb[u] = sb ? load_vec(b + off) : cb;
+            else vb[u] = va[u];
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) store_vec(d + (i + u * stride) * V, apply_vec<T, OP>(va[u], vb[u], imm));
+    }
+    for (; i < nvec; i += stride) {
+        Vec<T> va = sa ? load_vec(a + i * V) : ca;
+        Vec<T> vb = BIN ? (sb ? load_vec(b + i * V) : cb) : va;
+        store_vec(d + i * V, apply_vec<T, OP>(va, vb, imm));
+    }
+    const int64_t tail = nvec * V + tid;
+    if (tail < n) {
+        T x = a[sa ? tail : 0];
+        T y = BIN ? b[sb ? tail : 0] : x;
+        d[tail] = apply_one<T, OP>(x, y, imm);
+    }
+}
+
+// ------------------------------------------------------------------ ew_rows -----------
+// dst is [rows, cols] dense. Operand X contributes X[r * x_rs + c * x_in] with x_in in {0, 1}.
+// A thread owns one 16-byte column slot and walks down the rows (blockIdx.y strided), so an
+// operand that does not vary with the row (row-broadcast) is loaded once and kept in registers.
+struct RowsGeom {
+    int64_t rows, cols;
+    int64_t a_rs, b_rs;
+    int a_in, b_in;
+};
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(kThreads) ew_rows(const T* __restrict__ a, const T* __restrict__ b,
+                                                    T* __restrict__ d, RowsGeom g, Imm imm) {
+    constexpr int V = Vec<T>::N;
+    constexpr int UNROLL = 4;
+    constexpr bool BIN = op_is_binary(OP);
+    const int64_t cvec = g.cols / V;
+    const int64_t rstep = gridDim.y;
+    for (int64_t cv = (int64_t)blockIdx.x * kThreads + threadIdx.x; cv < cvec; cv += (int64_t)gridDim.x * kThreads) {
+        const int64_t c = cv * V;
+        const bool a_fixed = g.a_in && g.a_rs == 0, b_fixed = BIN && g.b_in && g.b_rs == 0;
+        Vec<T> fa, fb;
+        if (a_fixed) fa = load_vec(a + c);
+        if (b_fixed) fb = load_vec(b + c);
+        int64_t r = blockIdx.y;
+        for (; r + (UNROLL - 1) * rstep < g.rows; r += UNROLL * rstep) {
+            Vec<T> va[UNROLL], vb[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int64_t rr = r + u * rstep;
+                va[u] = a_fixed ? fa : (g.a_in ? load_vec(a + rr * g.a_rs + c) : splat_vec(__ldg(a + rr * g.a_rs)));
+                if (!BIN) vb[u] = va[u];
+                else vb[u] = b_fixed ? fb : (g.b_in ? load_vec(b + rr * g.b_rs + c) : splat_vec(__ldg(b + rr * g.b_rs)));
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u)
+                store_vec(d + (r + u * rstep) * g.cols + c, apply_vec<T, OP>(va[u], vb[u], imm));
+        }
+        for (; r < g.rows; r += rstep) {
+            Vec<T> va = a_fixed ? fa : (g.a_in ? load_vec(a + r * g.a_rs + c) : splat_vec(__ldg(a + r * g.a_rs)));
+            Vec<T> vb = !BIN ? va : (b_fixed ? fb : (g.b_in ? load_vec(b + r * g.b_rs + c) : splat_vec(__ldg(b + r * g.b_rs))));
+            store_vec(d + r * g.cols + c, apply_vec<T, OP>(va, vb, imm));
+        }
+    }
+}
+
+// ------------------------------------------------------------------ ew_generic --------
+struct GenericArgs {
+    const void* a;
+    const void* b;
+    void* d;
+    int adt, bdt, ddt;
+    int rank;
+    int64_t n;
+    int64_t sizes[TN_MAX_RANK];
+    int64_t sa[TN_MAX_RANK];
+    int64_t sb[TN_MAX_RANK];
+    Imm imm;
+};
+
+template <typename C, int OP, typename I>
+__global__ void __launch_bounds__(kThreads) ew_generic(GenericArgs g) {
+    const I n = static_cast<I>(g.n);
+    const I step = static_cast<I>(gridDim.x) * kThreads;
+    for (I lin = static_cast<I>(blockIdx.x) * kThreads + threadIdx.x; lin < n; lin += step) {
+        I rem = lin;
+        int64_t oa = 0, ob = 0;
+        for (int dim = g.rank - 1; dim >= 0; --dim) {
+            const I size = static_cast<I>(g.sizes[dim]);
+            const I coord = rem % size;
+            rem /= size;
+            oa += static_cast<int64_t>(coord) * g.sa[dim];
+            ob += static_cast<int64_t>(coord) * g.sb[dim];
+        }
+        C x = load_as<C>(g.a, g.adt, oa);
+        C y = op_is_binary(OP) ? load_as<C>(g.b, g.bdt, ob) : x;
+        store_as<C>(g.d, g.ddt, static_cast<int64_t>(lin), apply_op<OP, false, C>(x, y, g.imm));
+    }
+}
+
+// ------------------------------------------------------------------ host planning ------
+// Broadcast-aligned, size-1-free, coalesced view of the operands over dst's logical shape.
+struct Plan {
+    int rank = 0;
+    int64_t n = 1;
+    int64_t sizes[TN_MAX_RANK] = {0};
+    int64_t st[TN_PROGRAM_MAX_INPUTS][TN_MAX_RANK] = {{0}};
+};
+
+tn_status build_plan(const tn_tensor_t* const* ops, int nops, const tn_tensor_t* dst, Plan& plan) {
+    const int R = dst->rank;
+    if (R > TN_MAX_RANK) return fail(TN_ERROR, "rank %d exceeds %d", R, TN_MAX_RANK);
+    int64_t sizes[TN_MAX_RANK];
+    int64_t st[TN_PROGRAM_MAX_INPUTS][TN_MAX_RANK];
+    int64_t n = 1;
+    for (int d = 0; d < R; ++d) {
+        sizes[d] = (int64_t)dst->shape.sizes[d];
+        n *= sizes[d];
+    }
+    for (int k = 0; k < nops; ++k) {
+        const tn_tensor_t* t = ops[k];
+        if (t->rank > R) return fail(TN_ERROR, "operand rank %d exceeds result rank %d", (int)t->rank, R);
+        const int off = R - t->rank;
+        for (int d = 0; d < R; ++d) {
+            if (d < off) { st[k][d] = 0; continue; }
+            const int64_t sz = (int64_t)t->shape.sizes[d - off];
+            if (sz != 1 && sz != sizes[d])
+                return fail(TN_ERROR, "operand extent %lld does not broadcast to %lld at dim %d",
+                            (long long)sz, (long long)sizes[d], d);
+            st[k][d] = sz == 1 ? 0 : t->strides.sizes[d - off];
+        }
+    }
+    // drop extent-1 dims, then merge neighbours that every operand walks contiguously
+    int r = 0;
+    for (int d = 0; d < R; ++d) {
+        if (sizes[d] == 1) continue;
+        bool merged = false;
+        if (r > 0) {
+            merged = true;
+            for (int k = 0; k < nops; ++k)
+                if (plan.st[k][r - 1] != st[k][d] * sizes[d]) { merged = false; break; }
+            if (merged) {
+                plan.sizes[r - 1] *= sizes[d];
+                for (int k = 0; k < nops; ++k) plan.st[k][r - 1] = st[k][d];
+            }
+        }
+        if (!merged) {
+            plan.sizes[r] = sizes[d];
+            for (int k = 0; k < nops; ++k) plan.st[k][r] = st[k][d];
+            ++r;
+        }
+    }
+    plan.rank = r;
+    plan.n = n;
+    return TN_SUCCESS;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int flat_grid(int64_t work_items) {
+    const int64_t cap = (int64_t)sm_count() * 8;  // 8 CTAs of 256 threads fill an SM
+    int64_t blocks = ceil_div(work_items, kThreads);
+    if (blocks < 1) blocks = 1;
+    return (int)(blocks < cap ? blocks : cap);
+}
+
+// Launches the fastest kernel that the geometry allows for a same-dtype op.
+template <typename T, int OP>
+tn_status launch_typed(const Plan& plan, const void* a, const void* b, void* d, Imm imm, cudaStream_t s, bool* done) {
+    constexpr int V = Vec<T>::N;
+    constexpr bool BIN = op_is_binary(OP);
+    *done = false;
+    if (plan.n == 0) { *done = true; return TN_SUCCESS; }
+    const T* pa = static_cast<const T*>(a);
+    const T* pb = static_cast<const T*>(BIN ? b : a);
+    T* pd = static_cast<T*>(d);
+    if (!aligned16(d)) return TN_SUCCESS;
+    if (plan.rank <= 1) {
+        const int64_t sa = plan.rank ? plan.st[0][0] : 0;
+        const int64_t sb = BIN ? (plan.rank ? plan.st[1][0] : 0) : sa;
+        if ((sa != 0 && sa != 1) || (sb != 0 && sb != 1)) return TN_SUCCESS;
+        if ((sa == 1 && !aligned16(a)) || (BIN && sb == 1 && !aligned16(b))) return TN_SUCCESS;
+        const int grid = flat_grid(ceil_div(plan.n, V * 4));
+        ew_flat<T, OP><<<grid, kThreads, 0, s>>>(pa, pb, pd, plan.n, (int)sa, (int)sb, imm);
+        *done = true;
+        return after_launch("ew_flat");
+    }
+    if (plan.rank == 2) {
+        RowsGeom g;
+        g.rows = plan.sizes[0];
+        g.cols = plan.sizes[1];
+        g.a_rs = plan.st[0][0];
+        g.a_in = (int)plan.st[0][1];
+        g.b_rs = BIN ? plan.st[1][0] : g.a_rs;
+        g.b_in = BIN ? (int)plan.st[1][1] : g.a_in;
+        if (g.cols % V) return TN_SUCCESS;
+        if ((plan.st[0][1] != 0 && plan.st[0][1] != 1) || (BIN && plan.st[1][1] != 0 && plan.st[1][1] != 1)) return TN_SUCCESS;
+        if (g.a_rs < 0 || g.b_rs < 0) return TN_SUCCESS;
+        if (g.a_in && (!aligned16(a) || g.a_rs % V)) return TN_SUCCESS;
+        if (BIN && g.b_in && (!aligned16(b) || g.b_rs % V)) return TN_SUCCESS;
+        const int64_t cvec = g.cols / V;
+        int gx = (int)ceil_div(cvec, kThreads);
+        const int64_t cap = (int64_t)sm_count() * 8;
+        if (gx > cap) gx = (int)cap;
+        int64_t gy = cap / gx;
+        if (gy < 1) gy = 1;
+        if (gy > g.rows) gy = g.rows;
+        if (gy > 65535) gy = 65535;
+        ew_rows<T, OP><<<dim3(gx, (unsigned)gy), kThreads, 0, s>>>(pa, pb, pd, g, imm);
+        *done = true;
+        return after_launch("ew_rows");
+    }
+    return TN_SUCCESS;
+}
+
+template <typename C, int OP>
+tn_status launch_generic(const Plan& plan, const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, Imm imm,
+                         cudaStream_t s) {
+    if (plan.n == 0) return TN_SUCCESS;
+    GenericArgs g;
+    g.a = a->address;
+    g.b = b ? b->address : a->address;
+    g.d = dst->address;
+    g.adt = a->dtype;
+    g.bdt = b ? b->dtype : a->dtype;
+    g.ddt = dst->dtype;
+    g.rank = plan.rank;
+    g.n = plan.n;
+    for (int d = 0; d < plan.rank; ++d) {
+        g.sizes[d] = plan.sizes[d];
+        g.sa[d] = plan.st[0][d];
+        g.sb[d] = b ? plan.st[1][d] : plan.st[0][d];
+    }
+    g.imm = imm;
+    const int grid = flat_grid(plan.n);
+    if (plan.n < (int64_t(1) << 31)) ew_generic<C, OP, uint32_t><<<grid, kThreads, 0, s>>>(g);
+    else ew_generic<C, OP, uint64_t><<<grid, kThreads, 0, s>>>(g);
+    return after_launch("ew_generic");
+}
+
+// Arithmetic class of a dtype pair (mirrors the result types of the reference's tables,
+// src/cpu/ops-binary.cpp:168-430): 0 = int64 wrap, 1 = float32, 2 = float64.
+int compute_class(int a, int b) {
+    if (a == TN_FLOAT64 || b == TN_FLOAT64) return 2;
+    const bool fa = is_float(a), fb = is_float(b);
+    if ((fa && b == TN_INT64) || (fb && a == TN_INT64)) return 2;
+    if (fa || fb) return 1;
+    return 0;
+}
+
+// Pairs the reference accepts (src/cpu/ops-binary.cpp:168-430); everything else is
+// TN_UNSUPPORTED_DTYPE, exactly as its default table entry.
+bool pair_supported(int op, int a, int b) {
+    if (!is_numeric(a) || !is_numeric(b)) return false;
+    if (is_int(a) && is_int(b)) return op != TN_OP_POW;
+    auto half_ok = [](int h, int o) { return o == h || o == TN_FLOAT32 || o == TN_FLOAT64 || is_int(o); };
+    if (is_half(a)) return half_ok(a, b);
+    if (is_half(b)) return half_ok(b, a);
+    auto wide_ok = [](int o) { return o == TN_FLOAT32 || o == TN_FLOAT64 || o == TN_INT32; };
+    return wide_ok(a) && wide_ok(b);
+}
+
+template <int OP>
+tn_status typed_dispatch(int dt, const Plan& plan, const void* a, const void* b, void* d, Imm imm, cudaStream_t s,
+                         bool* done) {
+    switch (dt) {
+        case TN_FLOAT16: return launch_typed<__half, OP>(plan, a, b, d, imm, s, done);
+        case TN_BFLOAT16: return launch_typed<__nv_bfloat16, OP>(plan, a, b, d, imm, s, done);
+        case TN_FLOAT32: return launch_typed<float, OP>(plan, a, b, d, imm, s, done);
+        case TN_FLOAT64: return launch_typed<double, OP>(plan, a, b, d, imm, s, done);
+        default: break;
+    }
+    if constexpr (!op_is_float_only(OP)) {
+        switch (dt) {
+            case TN_INT8: return launch_typed<int8_t, OP>(plan, a, b, d, imm, s, done);
+            case TN_INT16: return launch_typed<int16_t, OP>(plan, a, b, d, imm, s, done);
+            case TN_INT32: return launch_typed<int32_t, OP>(plan, a, b, d, imm, s, done);
+            case TN_INT64: return launch_typed<int64_t, OP>(plan, a, b, d, imm, s, done);
+            default: break;
+        }
+    }
+    *done = false;
+    return TN_SUCCESS;
+}
+
+template <int OP>
+tn_status generic_dispatch(int cls, const Plan& plan, const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst,
+                           Imm imm, cudaStream_t s) {
+    if (cls == 2) return launch_generic<double, OP>(plan, a, b, dst, imm, s);
+    if (cls == 1) return launch_generic<float, OP>(plan, a, b, dst, imm, s);
+    if constexpr (!op_is_float_only(OP)) return launch_generic<int64_t, OP>(plan, a, b, dst, imm, s);
+    return fail(TN_UNSUPPORTED_DTYPE, "operation needs a floating dtype");
+}
+
+template <int OP>
+tn_status binary(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream) {
+    if (!a || !b || !dst) return fail(TN_ERROR, "null tensor");
+    if (!pair_supported(OP, a->dtype, b->dtype) || !is_numeric(dst->dtype))
+        return fail(TN_UNSUPPORTED_DTYPE, "binary op %d: dtype pair (%d, %d) -> %d unsupported", OP, (int)a->dtype,
+                    (int)b->dtype, (int)dst->dtype);
+    if (a->environment.kind != TN_DEVICE || b->environment.kind != TN_DEVICE ||
+        a->environment.resource.device.id != b->environment.resource.device.id ||
+        a->environment.resource.device.id != dst->environment.resource.device.id)
+        return fail(TN_INCOMPATIBLE_DEVICES, "operands must live on one device");
+    TN_TRY(use_device_of(dst));
+    Plan plan;
+    const tn_tensor_t* ops[2] = {a, b};
+    TN_TRY(build_plan(ops, 2, dst, plan));
+    cudaStream_t s = as_cuda(stream);
+    Imm imm{0.0, 0};
+    if (a->dtype == b->dtype && a->dtype == dst->dtype) {
+        bool done = false;
+        TN_TRY((typed_dispatch<OP>(a->dtype, plan, a->address, b->address, dst->address, imm, s, &done)));
+        if (done) return TN_SUCCESS;
+    }
+    return generic_dispatch<OP>(compute_class(a->dtype, b->dtype), plan, a, b, dst, imm, s);
+}
+
+bool unary_supported(int op, int dt) {
+    if (op == TN_OP_NEG || op == TN_OP_SCALE || op == TN_OP_COUNT /* repack */) return is_numeric(dt);
+    if (op == TN_OP_ABS) return is_float(dt) || dt == TN_INT32 || dt == TN_INT64;  // src/cpu/ops-unary.cpp:288-300
+    return is_float(dt);
+}
+
+template <int OP>
+tn_status unary(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, Imm imm) {
+    if (!src || !dst) return fail(TN_ERROR, "null tensor");
+    if (!unary_supported(OP, src->dtype) || !is_numeric(dst->dtype))
+        return fail(TN_UNSUPPORTED_DTYPE, "unary op %d: dtype %d unsupported", OP, (int)src->dtype);
+    if (src->environment.kind != TN_DEVICE ||
+        src->environment.resource.device.id != dst->environment.resource.device.id)
+        return fail(TN_INCOMPATIBLE_DEVICES, "operands must live on one device");
+    TN_TRY(use_device_of(dst));
+    Plan plan;
+    const tn_tensor_t* ops[1] = {src};
+    TN_TRY(build_plan(ops, 1, dst, plan));
+    cudaStream_t s = as_cuda(stream);
+    if (src->dtype == dst->dtype) {
+        bool done = false;
+        TN_TRY((typed_dispatch<OP>(src->dtype, plan, src->address, nullptr, dst->address, imm, s, &done)));
+        if (done) return TN_SUCCESS;
+    }
+    const int cls = src->dtype == TN_FLOAT64 ? 2 : (is_float(src->dtype) ? 1 : 0);
+    return generic_dispatch<OP>(cls, plan, src, nullptr, dst, imm, s);
+}
+
+// Reads a host scalar of dtype `dt` (reference: scalar_t, include/tannic/runtime/tensor.h:43-46).
+bool read_scalar(const tn_scalar_t* sc, Imm* imm) {
+    const void* p = sc->address;
+    switch (sc->dtype) {
+        case TN_INT8: imm->i = *static_cast<const int8_t*>(p); break;
+        case TN_INT16: imm->i = *static_cast<const int16_t*>(p); break;
+        case TN_INT32: imm->i = *static_cast<const int32_t*>(p); break;
+        case TN_INT64: imm->i = *static_cast<const int64_t*>(p); break;
+        case TN_FLOAT16: { __half h; memcpy(&h, p, 2); imm->f = __half2float(h); break; }
+        case TN_BFLOAT16: { __nv_bfloat16 h; memcpy(&h, p, 2); imm->f = __bfloat162float(h); break; }
+        case TN_FLOAT32: imm->f = *static_cast<const float*>(p); break;
+        case TN_FLOAT64: imm->f = *static_cast<const double*>(p); break;
+        default: return false;
+    }
+    if (is_int(sc->dtype)) imm->f = (double)imm->i;
+    else imm->i = (int64_t)imm->f;
+    return true;
+}
+
+// ------------------------------------------------------------------ fused program ------
+// One pass over HBM for a whole expression tree. Values 0..3 are the inputs, value 4+k is the
+// result of node k; every node result is rounded to the storage type T before it is reused,
+// which is what the reference's one-kernel-per-node chain does through its temporaries.
+constexpr int kMaxIn = TN_PROGRAM_MAX_INPUTS;
+constexpr int kMaxNodes = TN_PROGRAM_MAX_NODES;
+
+struct ProgArgs {
+    const void* in[kMaxIn];
+    void* d;
+    int64_t rs[kMaxIn];  // row pitch (elements)
+    int inner[kMaxIn];   // 1: dense along cols, 0: constant along cols
+    int64_t rows, cols;
+    int n_inputs, n_nodes;
+    tn_eltwise_node_t nodes[kMaxNodes];
+};
+
+struct ProgGenericArgs {
+    const void* in[kMaxIn];
+    void* d;
+    int rank;
+    int64_t n;
+    int64_t sizes[TN_MAX_RANK];
+    int64_t st[kMaxIn][TN_MAX_RANK];
+    int n_inputs, n_nodes;
+    tn_eltwise_node_t nodes[kMaxNodes];
+};
+
+template <typename T, typename C>
+__device__ __forceinline__ C round_to_storage(C v) {
+    if constexpr (std::is_same<T, C>::value) return v;
+    else return to_compute<C>(from_compute<T, C>(v));
+}
+
+template <typename C, bool FAST>
+__device__ __forceinline__ C apply_dynamic(int op, C a, C b, float immf) {
+    const Imm imm{(double)immf, 0};
+    switch (op) {
+        case TN_OP_ADD: return apply_op<TN_OP_ADD, FAST, C>(a, b, imm);
+        case TN_OP_SUB: return apply_op<TN_OP_SUB, FAST, C>(a, b, imm);
+        case TN_OP_MUL: return apply_op<TN_OP_MUL, FAST, C>(a, b, imm);
+        case TN_OP_POW: return apply_op<TN_OP_POW, FAST, C>(a, b, imm);
+        case TN_OP_NEG: return apply_op<TN_OP_NEG, FAST, C>(a, b, imm);
+        case TN_OP_LOG: return apply_op<TN_OP_LOG, FAST, C>(a, b, imm);
+        case TN_OP_EXP: return apply_op<TN_OP_EXP, FAST, C>(a, b, imm);
+        case TN_OP_SQRT: return apply_op<TN_OP_SQRT, FAST, C>(a, b, imm);
+        case TN_OP_RSQRT: return apply_op<TN_OP_RSQRT, FAST, C>(a, b, imm);
+        case TN_OP_ABS: return apply_op<TN_OP_ABS, FAST, C>(a, b, imm);
+        case TN_OP_SIN: return apply_op<TN_OP_SIN, FAST, C>(a, b, imm);
+        case TN_OP_COS: return apply_op<TN_OP_COS, FAST, C>(a, b, imm);
+        case TN_OP_TAN: return apply_op<TN_OP_TAN, FAST, C>(a, b, imm);
+        case TN_OP_SINH: return apply_op<TN_OP_SINH, FAST, C>(a, b, imm);
+        case TN_OP_COSH: return apply_op<TN_OP_COSH, FAST, C>(a, b, imm);
+        case TN_OP_TANH: return apply_op<TN_OP_TANH, FAST, C>(a, b, imm);
+        case TN_OP_SCALE: return apply_op<TN_OP_SCALE, FAST, C>(a, b, imm);
+        default: return a;
+    }
+}
+
+// Programs compiled ahead of time: the node list is a compile-time constant, so the evaluator
+// unrolls into straight-line code with every value in a register. The dynamic evaluator runs
+// any other program with its values in local memory.
+struct NodeSpec { int op, lhs, rhs; };
+
+struct ProgDynamic { static constexpr int N = 0; };
+
+// log(x0) + x1*x1 - exp(x0)
+struct ProgLogSquareExp {
+    static constexpr int N = 5;
+    static constexpr NodeSpec nodes[N] = {{TN_OP_LOG, 0, 0}, {TN_OP_MUL, 1, 1}, {TN_OP_ADD, 4, 5}, {TN_OP_EXP, 0, 0}, {TN_OP_SUB, 6, 7}};
+};
+// x0*x1 + x2
+struct ProgMulAdd {
+    static constexpr int N = 2;
+    static constexpr NodeSpec nodes[N] = {{TN_OP_MUL, 0, 1}, {TN_OP_ADD, 4, 2}};
+};
+// (x0 - x1) * (x0 - x1)
+struct ProgSquaredDiff {
+    static constexpr int N = 2;
+    static constexpr NodeSpec nodes[N] = {{TN_OP_SUB, 0, 1}, {TN_OP_MUL, 4, 4}};
+};
+// x0 * rsqrt(x1, eps) * x2   (normalisation scale)
+struct ProgNormScale {
+    static constexpr int N = 3;
+    static constexpr NodeSpec nodes[N] = {{TN_OP_RSQRT, 1, 1}, {TN_OP_MUL, 0, 4}, {TN_OP_MUL, 5, 2}};
+};
+
+template <typename T, typename P, int K, int V>
+__device__ __forceinline__ void eval_static(typename compute_of<T>::type (&val)[kMaxIn + (P::N ? P::N : 1)][V],
+                                            const tn_eltwise_node_t* nodes) {
+    using C = typename compute_of<T>::type;
+    constexpr bool FAST = sizeof(T) == 2;
+    if constexpr (K < P::N) {
+        constexpr NodeSpec nd = P::nodes[K];
+        const Imm imm{(double)nodes[K].imm, 0};
+#pragma unroll
+        for (int i = 0; i < V; ++i)
+            val[kMaxIn + K][i] = round_to_storage<T, C>(apply_op<nd.op, FAST, C>(val[nd.lhs][i], val[nd.rhs][i], imm));
+        eval_static<T, P, K + 1, V>(val, nodes);
+    }
+}
+
+template <typename T, typename P>
+__global__ void __launch_bounds__(kThreads) ew_program_rows(const __grid_constant__ ProgArgs g) {
+    using C = typename compute_of<T>::type;
+    constexpr bool FAST = sizeof(T) == 2;
+    constexpr int V = Vec<T>::N;
+    constexpr bool STATIC = P::N > 0;
+    const int64_t cvec = g.cols / V;
+    const int64_t rstep = gridDim.y;
+    for (int64_t cv = (int64_t)blockIdx.x * kThreads + threadIdx.x; cv < cvec; cv += (int64_t)gridDim.x * kThreads) {
+        const int64_t c = cv * V;
+        Vec<T> fixed[kMaxIn];
+#pragma unroll
+        for (int k = 0; k < kMaxIn; ++k)
+            if (k < g.n_inputs && g.inner[k] && g.rs[k] == 0) fixed[k] = load_vec(static_cast<const T*>(g.in[k]) + c);
+        for (int64_t r = blockIdx.y; r < g.rows; r += rstep) {
+            Vec<T> vin[kMaxIn];
+#pragma unroll
+            for (int k = 0; k < kMaxIn; ++k) {
+                if (k >= g.n_inputs) continue;
+                const T* base = static_cast<const T*>(g.in[k]);
+                if (g.inner[k]) vin[k] = g.rs[k] == 0 ? fixed[k] : load_vec(base + r * g.rs[k] + c);
+                else vin[k] = splat_vec(__ldg(base + r * g.rs[k]));
+            }
+            Vec<T> out;
+            if constexpr (STATIC) {
+                C val[kMaxIn + P::N][V];
+#pragma unroll
+                for (int k = 0; k < kMaxIn; ++k)
+#pragma unroll
+                    for (int i = 0; i < V; ++i) val[k][i] = k < g.n_inputs ? to_compute<C>(vin[k].e[i]) : C(0);
+                eval_static<T, P, 0, V>(val, g.nodes);
+#pragma unroll
+                for (int i = 0; i < V; ++i) out.e[i] = from_compute<T, C>(val[kMaxIn + P::N - 1][i]);
+            } else {
+                C val[kMaxIn + kMaxNodes][V];
+#pragma unroll
+                for (int k = 0; k < kMaxIn; ++k)
+#pragma unroll
+                    for (int i = 0; i < V; ++i) val[k][i] = k < g.n_inputs ? to_compute<C>(vin[k].e[i]) : C(0);
+                for (int n = 0; n < g.n_nodes; ++n) {
+                    const tn_eltwise_node_t nd = g.nodes[n];
+#pragma unroll
+                    for (int i = 0; i < V; ++i)
+                        val[kMaxIn + n][i] = round_to_storage<T, C>(apply_dynamic<C, FAST>(nd.opcode, val[nd.lhs][i], val[nd.rhs][i], nd.imm));
+                }
+#pragma unroll
+                for (int i = 0; i < V; ++i) out.e[i] = from_compute<T, C>(val[kMaxIn + g.n_nodes - 1][i]);
+            }
+            store_vec(static_cast<T*>(g.d) + r * g.cols + c, out);
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) ew_program_generic(const __grid_constant__ ProgGenericArgs g) {
+    using C = typename compute_of<T>::type;
+    constexpr bool FAST = sizeof(T) == 2;
+    const int64_t step = (int64_t)gridDim.x * kThreads;
+    for (int64_t lin = (int64_t)blockIdx.x * kThreads + threadIdx.x; lin < g.n; lin += step) {
+        int64_t rem = lin;
+        int64_t off[kMaxIn] = {0, 0, 0, 0};
+        for (int dim = g.rank - 1; dim >= 0; --dim) {
+            const int64_t coord = rem % g.sizes[dim];
+            rem /= g.sizes[dim];
+#pragma unroll
+            for (int k = 0; k < kMaxIn; ++k) off[k] += coord * g.st[k][dim];
+        }
+        C val[kMaxIn + kMaxNodes];
+#pragma unroll
+        for (int k = 0; k < kMaxIn; ++k)
+            val[k] = k < g.n_inputs ? to_compute<C>(static_cast<const T*>(g.in[k])[off[k]]) : C(0);
+        for (int n = 0; n < g.n_nodes; ++n) {
+            const tn_eltwise_node_t nd = g.nodes[n];
+            val[kMaxIn + n] = round_to_storage<T, C>(apply_dynamic<C, FAST>(nd.opcode, val[nd.lhs], val[nd.rhs], nd.imm));
+        }
+        static_cast<T*>(g.d)[lin] = from_compute<T, C>(val[kMaxIn + g.n_nodes - 1]);
+    }
+}
+
+template <typename P>
+bool matches(const tn_eltwise_node_t* nodes, int n) {
+    if (n != P::N) return false;
+    for (int k = 0; k < n; ++k) {
+        const bool bin = op_is_binary(nodes[k].opcode);
+        if (nodes[k].opcode != P::nodes[k].op || nodes[k].lhs != P::nodes[k].lhs) return false;
+        if (bin && nodes[k].rhs != P::nodes[k].rhs) return false;
+    }
+    return true;
+}
+
+template <typename T>
+tn_status launch_program(const Plan& plan, const tn_tensor_t* const* inputs, int n_inputs,
+                         const tn_eltwise_node_t* nodes, int n_nodes, tn_tensor_t* dst, cudaStream_t s) {
+    constexpr int V = Vec<T>::N;
+    if (plan.n == 0) return TN_SUCCESS;
+    // [rows, cols] geometry?
+    bool rows_ok = plan.rank <= 2 && aligned16(dst->address);
+    const int64_t rows = plan.rank == 2 ? plan.sizes[0] : 1;
+    const int64_t cols = plan.rank == 0 ? 1 : plan.sizes[plan.rank - 1];
+    if (cols % V) rows_ok = false;
+    for (int k = 0; rows_ok && k < n_inputs; ++k) {
+        const int64_t inner = plan.rank ? plan.st[k][plan.rank - 1] : 0;
+        const int64_t rs = plan.rank == 2 ? plan.st[k][0] : 0;
+        if ((inner != 0 && inner != 1) || rs < 0) rows_ok = false;
+        if (inner == 1 && (!aligned16(inputs[k]->address) || rs % V)) rows_ok = false;
+    }
+    if (rows_ok) {
+        ProgArgs g;
+        memset(&g, 0, sizeof(g));
+        for (int k = 0; k < n_inputs; ++k) {
+            g.in[k] = inputs[k]->address;
+            g.inner[k] = plan.rank ? (int)plan.st[k][plan.rank - 1] : 0;
+            g.rs[k] = plan.rank == 2 ? plan.st[k][0] : 0;
+        }
+        g.d = dst->address;
+        g.rows = rows;
+        g.cols = cols;
+        g.n_inputs = n_inputs;
+        g.n_nodes = n_nodes;
+        for (int k = 0; k < n_nodes; ++k) g.nodes[k] = nodes[k];
+        const int64_t cvec = cols / V;
+        const int64_t cap = (int64_t)sm_count() * 8;
+        int gx = (int)ceil_div(cvec, kThreads);
+        if (gx > cap) gx = (int)cap;
+        int64_t gy = cap / gx;
+        if (gy < 1) gy = 1;
+        if (gy > rows) gy = rows;
+        if (gy > 65535) gy = 65535;
+        const dim3 grid(gx, (unsigned)gy);
+        if (matches<ProgLogSquareExp>(nodes, n_nodes)) ew_program_rows<T, ProgLogSquareExp><<<grid, kThreads, 0, s>>>(g);
+        else if (matches<ProgMulAdd>(nodes, n_nodes)) ew_program_rows<T, ProgMulAdd><<<grid, kThreads, 0, s>>>(g);
+        else if (matches<ProgSquaredDiff>(nodes, n_nodes)) ew_program_rows<T, ProgSquaredDiff><<<grid, kThreads, 0, s>>>(g);
+        else if (matches<ProgNormScale>(nodes, n_nodes)) ew_program_rows<T, ProgNormScale><<<grid, kThreads, 0, s>>>(g);
+        else ew_program_rows<T, ProgDynamic><<<grid, kThreads, 0, s>>>(g);
+        return after_launch("ew_program_rows");
+    }
+    ProgGenericArgs g;
+    memset(&g, 0, sizeof(g));
+    for (int k = 0; k < n_inputs; ++k) {
+        g.in[k] = inputs[k]->address;
+        for (int d = 0; d < plan.rank; ++d) g.st[k][d] = plan.st[k][d];
+    }
+    g.d = dst->address;
+    g.rank = plan.rank;
+    g.n = plan.n;
+    for (int d = 0; d < plan.rank; ++d) g.sizes[d] = plan.sizes[d];
+    g.n_inputs = n_inputs;
+    g.n_nodes = n_nodes;
+    for (int k = 0; k < n_nodes; ++k) g.nodes[k] = nodes[k];
+    ew_program_generic<T><<<flat_grid(plan.n), kThreads, 0, s>>>(g);
+    return after_launch("ew_program_generic");
+}
+
+}  // namespace
+
+bool read_host_scalar(const tn_scalar_t* sc, double* f, int64_t* i) {
+    Imm imm{0.0, 0};
+    if (!sc || !sc->address || !read_scalar(sc, &imm)) return false;
+    *f = imm.f;
+    *i = imm.i;
+    return true;
+}
+
+}  // namespace tnb
+
+using namespace tnb;
+
+extern "C" {
+
+tn_status tn_add(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* d, tn_stream_t s) { return binary<TN_OP_ADD>(a, b, d, s); }
+tn_status tn_sub(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* d, tn_stream_t s) { return binary<TN_OP_SUB>(a, b, d, s); }
+tn_status tn_mul(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* d, tn_stream_t s) { return binary<TN_OP_MUL>(a, b, d, s); }
+tn_status tn_pow(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* d, tn_stream_t s) { return binary<TN_OP_POW>(a, b, d, s); }
+
+tn_status tn_neg(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_NEG>(x, d, s, Imm{0, 0}); }
+tn_status tn_repack(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_COUNT>(x, d, s, Imm{0, 0}); }
+tn_status tn_log(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_LOG>(x, d, s, Imm{0, 0}); }
+tn_status tn_exp(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_EXP>(x, d, s, Imm{0, 0}); }
+tn_status tn_sqrt(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_SQRT>(x, d, s, Imm{0, 0}); }
+tn_status tn_rsqrt(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s, float eps) { return unary<TN_OP_RSQRT>(x, d, s, Imm{(double)eps, 0}); }
+tn_status tn_abs(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_ABS>(x, d, s, Imm{0, 0}); }
+tn_status tn_sin(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_SIN>(x, d, s, Imm{0, 0}); }
+tn_status tn_cos(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_COS>(x, d, s, Imm{0, 0}); }
+tn_status tn_tan(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_TAN>(x, d, s, Imm{0, 0}); }
+tn_status tn_sinh(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_SINH>(x, d, s, Imm{0, 0}); }
+tn_status tn_cosh(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_COSH>(x, d, s, Imm{0, 0}); }
+tn_status tn_tanh(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_TANH>(x, d, s, Imm{0, 0}); }
+
+tn_status tn_scale(const tn_tensor_t* src, const tn_scalar_t* scalar, tn_tensor_t* dst, tn_stream_t stream) {
+    if (!src || !scalar || !dst) return fail(TN_ERROR, "null argument");
+    // same-dtype only, as the reference's table (src/cpu/ops-scale.cpp:103-114)
+    if (scalar->dtype != src->dtype || !is_numeric(src->dtype))
+        return fail(TN_UNSUPPORTED_DTYPE, "scale: tensor dtype %d, scalar dtype %d", (int)src->dtype, (int)scalar->dtype);
+    Imm imm{0.0, 0};
+    if (!scalar->address || !read_scalar(scalar, &imm)) return fail(TN_ERROR, "scale: unreadable scalar");
+    return unary<TN_OP_SCALE>(src, dst, stream, imm);
+}
+
+tn_status tn_eltwise_program(const tn_tensor_t* const* inputs, int n_inputs, const tn_eltwise_node_t* nodes,
+                             int n_nodes, tn_tensor_t* dst, tn_stream_t stream) {
+    if (!inputs || !nodes || !dst) return fail(TN_ERROR, "null argument");
+    if (n_inputs < 1 || n_inputs > TN_PROGRAM_MAX_INPUTS || n_nodes < 1 || n_nodes > TN_PROGRAM_MAX_NODES)
+        return fail(TN_ERROR, "program with %d inputs / %d nodes is out of range", n_inputs, n_nodes);
+    const int dt = dst->dtype;
+    if (!is_float(dt)) return fail(TN_UNSUPPORTED_DTYPE, "fused programs run on floating dtypes, got %d", dt);
+    for (int k = 0; k < n_inputs; ++k) {
+        if (!inputs[k]) return fail(TN_ERROR, "null input %d", k);
+        if (inputs[k]->dtype != dt) return fail(TN_UNSUPPORTED_DTYPE, "input %d has dtype %d, result has %d", k, (int)inputs[k]->dtype, dt);
+        if (inputs[k]->environment.kind != TN_DEVICE ||
+            inputs[k]->environment.resource.device.id != dst->environment.resource.device.id)
+            return fail(TN_INCOMPATIBLE_DEVICES, "operands must live on one device");
+    }
+    for (int k = 0; k < n_nodes; ++k) {
+        const tn_eltwise_node_t& nd = nodes[k];
+        if (nd.opcode >= TN_OP_COUNT) return fail(TN_ERROR, "node %d: unknown opcode %d", k, (int)nd.opcode);
+        auto ok = [&](int v) { return v < n_inputs || (v >= TN_PROGRAM_MAX_INPUTS && v < TN_PROGRAM_MAX_INPUTS + k); };
+        if (!ok(nd.lhs) || (op_is_binary(nd.opcode) && !ok(nd.rhs)))
+            return fail(TN_ERROR, "node %d reads a value that is not defined before it", k);
+    }
+    TN_TRY(use_device_of(dst));
+    // unary nodes read only lhs; normalise rhs so the kernels may index it blindly
+    tn_eltwise_node_t local[TN_PROGRAM_MAX_NODES];
+    for (int k = 0; k < n_nodes; ++k) {
+        local[k] = nodes[k];
+        if (!op_is_binary(local[k].opcode)) local[k].rhs = local[k].lhs;
+    }
+    Plan plan;
+    TN_TRY(build_plan(inputs, n_inputs, dst, plan));
+    cudaStream_t s = as_cuda(stream);
+    switch (dt) {
+        case TN_FLOAT16: return launch_program<__half>(plan, inputs, n_inputs, local, n_nodes, dst, s);
+        case TN_BFLOAT16: return launch_program<__nv_bfloat16>(plan, inputs, n_inputs, local, n_nodes, dst, s);
+        case TN_FLOAT32: return launch_program<float>(plan, inputs, n_inputs, local, n_nodes, dst, s);
+        default: return launch_program<double>(plan, inputs, n_inputs, local, n_nodes, dst, s);
+    }
+}
+
+}  // extern "C"

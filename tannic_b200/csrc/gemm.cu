@@ -1,0 +1,284 @@
+// tn_gemm / tn_gemm_scaled: shape and stride analysis, choice between the tcgen05 kernel
+// (16-bit operands that TMA can address) and the SIMT kernel (everything else: fp32/fp64,
+// integers, mixed pairs, odd pitches). Replaces src/cuda/matmul.cu of the reference.
+#include "gemm_tc.cuh"
+
+namespace tnb {
+
+bool read_host_scalar(const tn_scalar_t* sc, double* f, int64_t* i);
+tn_status tc_abort_count(unsigned int* count);
+
+namespace {
+
+constexpr int kMaxBatchDims = TN_MAX_RANK - 2;
+
+struct SimtArgs {
+    const void* a;
+    const void* b;
+    void* d;
+    int adt, bdt, ddt;
+    int64_t M, N, K;
+    int64_t a_sm, a_sk, b_sk, b_sn, d_sm, d_sn;  // element strides of the matrix dims
+    int nbatch;                                  // number of batch dims
+    int64_t batches;
+    int64_t bsize[kMaxBatchDims];
+    int64_t a_bs[kMaxBatchDims], b_bs[kMaxBatchDims], d_bs[kMaxBatchDims];
+    int has_scale;
+    double scale_f;
+    int64_t scale_i;
+};
+
+constexpr int TM = 64, TN = 64, TK = 16;
+
+// 64x64 tile per CTA of 256 threads, 4x4 outputs per thread, operands converted to the
+// accumulator type C while they are staged in shared memory. Accumulation over k is in
+// ascending order inside each thread, as in the reference loop (src/cpu/matmul.cpp:21-41).
+template <typename C>
+__global__ void __launch_bounds__(256) gemm_simt(const __grid_constant__ SimtArgs g) {
+    __shared__ C As[TK][TM + 1];
+    __shared__ C Bs[TK][TN + 1];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    for (int64_t batch = blockIdx.z; batch < g.batches; batch += gridDim.z) {
+        int64_t oa = 0, ob = 0, od = 0, rem = batch;
+        for (int dim = g.nbatch - 1; dim >= 0; --dim) {
+            const int64_t c = rem % g.bsize[dim];
+            rem /= g.bsize[dim];
+            oa += c * g.a_bs[dim];
+            ob += c * g.b_bs[dim];
+            od += c * g.d_bs[dim];
+        }
+        const int64_t m0 = (int64_t)blockIdx.y * TM, n0 = (int64_t)blockIdx.x * TN;
+        C acc[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[i][j] = C(0);
+        for (int64_t k0 = 0; k0 < g.K; k0 += TK) {
+            // 64x16 elements of A and 16x64 of B: 4 of each per thread
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int idx = threadIdx.x + e * 256;
+                {
+                    const int kk = idx & 15, mm = idx >> 4;  // k fastest: suits K-contiguous A
+                    const int64_t m = m0 + mm, k = k0 + kk;
+                    As[kk][mm] = (m < g.M && k < g.K) ? load_as<C>(g.a, g.adt, oa + m * g.a_sm + k * g.a_sk) : C(0);
+                }
+                {
+                    int kk, nn;
+                    if (g.b_sn == 1) { nn = idx & 63; kk = idx >> 6; }  // n fastest: N-contiguous B
+                    else { kk = idx & 15; nn = idx >> 4; }               // k fastest: K-contiguous B
+                    const int64_t n = n0 + nn, k = k0 + kk;
+                    Bs[kk][nn] = (n < g.N && k < g.K) ? load_as<C>(g.b, g.bdt, ob + k * g.b_sk + n * g.b_sn) : C(0);
+                }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int kk = 0; kk < TK; ++kk) {
+                C av[4], bv[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) bv[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if constexpr (std::is_same<C, int64_t>::value)
+                            acc[i][j] = (int64_t)((uint64_t)acc[i][j] + (uint64_t)av[i] * (uint64_t)bv[j]);
+                        else
+                            acc[i][j] += av[i] * bv[j];
+                    }
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int64_t m = m0 + ty * 4 + i;
+            if (m >= g.M) continue;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int64_t n = n0 + tx * 4 + j;
+                if (n >= g.N) continue;
+                const int64_t off = od + m * g.d_sm + n * g.d_sn;
+                if (g.has_scale) {
+                    // round to the result dtype, multiply by the scalar, round again
+                    store_as<C>(g.d, g.ddt, off, acc[i][j]);
+                    C r = load_as<C>(g.d, g.ddt, off);
+                    if constexpr (std::is_same<C, int64_t>::value) r = (int64_t)((uint64_t)r * (uint64_t)g.scale_i);
+                    else r = r * static_cast<C>(g.scale_f);
+                    store_as<C>(g.d, g.ddt, off, r);
+                } else {
+                    store_as<C>(g.d, g.ddt, off, acc[i][j]);
+                }
+            }
+        }
+    }
+}
+
+// Operand pairs of the reference's table (src/cpu/matmul.cpp:189-252).
+bool pair_supported(int a, int b) {
+    if (!is_numeric(a) || !is_numeric(b)) return false;
+    if (is_int(a) && is_int(b)) return true;
+    auto half_ok = [](int h, int o) { return o == h || o == TN_FLOAT32 || o == TN_FLOAT64 || is_int(o); };
+    if (is_half(a)) return half_ok(a, b);
+    if (is_half(b)) return half_ok(b, a);
+    auto wide_ok = [](int o) { return o == TN_FLOAT32 || o == TN_FLOAT64 || o == TN_INT32; };
+    return wide_ok(a) && wide_ok(b);
+}
+
+int compute_class(int a, int b) {
+    if (a == TN_FLOAT64 || b == TN_FLOAT64) return 2;
+    const bool fa = is_float(a), fb = is_float(b);
+    if ((fa && b == TN_INT64) || (fb && a == TN_INT64)) return 2;
+    if (fa || fb) return 1;
+    return 0;
+}
+
+tn_status gemm_impl(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, const tn_scalar_t* scale,
+                    tn_stream_t stream) {
+    if (!a || !b || !dst) return fail(TN_ERROR, "null tensor");
+    if (!pair_supported(a->dtype, b->dtype) || !is_numeric(dst->dtype))
+        return fail(TN_UNSUPPORTED_DTYPE, "gemm: dtype pair (%d, %d) -> %d unsupported", (int)a->dtype, (int)b->dtype,
+                    (int)dst->dtype);
+    if (a->rank < 2 || b->rank < 2 || dst->rank < 2)
+        return fail(TN_ERROR, "gemm: operands must have rank >= 2 (got %d, %d -> %d)", (int)a->rank, (int)b->rank, (int)dst->rank);
+    if (a->environment.kind != TN_DEVICE || b->environment.kind != TN_DEVICE ||
+        a->environment.resource.device.id != b->environment.resource.device.id ||
+        a->environment.resource.device.id != dst->environment.resource.device.id)
+        return fail(TN_INCOMPATIBLE_DEVICES, "operands must live on one device");
+    TN_TRY(use_device_of(dst));
+
+    SimtArgs g;
+    g.a = a->address;
+    g.b = b->address;
+    g.d = dst->address;
+    g.adt = a->dtype;
+    g.bdt = b->dtype;
+    g.ddt = dst->dtype;
+    const int ra = a->rank, rb = b->rank, rd = dst->rank;
+    g.M = (int64_t)dst->shape.sizes[rd - 2];
+    g.N = (int64_t)dst->shape.sizes[rd - 1];
+    g.K = (int64_t)a->shape.sizes[ra - 1];
+    if ((int64_t)a->shape.sizes[ra - 2] != g.M || (int64_t)b->shape.sizes[rb - 1] != g.N ||
+        (int64_t)b->shape.sizes[rb - 2] != g.K)
+        return fail(TN_ERROR, "gemm: shapes do not contract ([%lld,%lld] x [%lld,%lld] -> [%lld,%lld])",
+                    (long long)a->shape.sizes[ra - 2], (long long)g.K, (long long)b->shape.sizes[rb - 2],
+                    (long long)b->shape.sizes[rb - 1], (long long)g.M, (long long)g.N);
+    g.a_sm = a->strides.sizes[ra - 2];
+    g.a_sk = a->strides.sizes[ra - 1];
+    g.b_sk = b->strides.sizes[rb - 2];
+    g.b_sn = b->strides.sizes[rb - 1];
+    g.d_sm = dst->strides.sizes[rd - 2];
+    g.d_sn = dst->strides.sizes[rd - 1];
+    g.nbatch = rd - 2;
+    g.batches = 1;
+    for (int dim = 0; dim < g.nbatch; ++dim) {
+        g.bsize[dim] = (int64_t)dst->shape.sizes[dim];
+        g.batches *= g.bsize[dim];
+        g.d_bs[dim] = dst->strides.sizes[dim];
+        // batch dims broadcast NumPy-style: missing or extent-1 dims reuse the operand
+        // (src/cpu/matmul.cpp:96-124)
+        const int da = dim + (ra - rd), db = dim + (rb - rd);
+        g.a_bs[dim] = (da >= 0 && da < ra - 2 && a->shape.sizes[da] != 1) ? a->strides.sizes[da] : 0;
+        g.b_bs[dim] = (db >= 0 && db < rb - 2 && b->shape.sizes[db] != 1) ? b->strides.sizes[db] : 0;
+        if (da >= 0 && da < ra - 2 && a->shape.sizes[da] != 1 && (int64_t)a->shape.sizes[da] != g.bsize[dim])
+            return fail(TN_ERROR, "gemm: batch dim %d of the first operand does not broadcast", dim);
+        if (db >= 0 && db < rb - 2 && b->shape.sizes[db] != 1 && (int64_t)b->shape.sizes[db] != g.bsize[dim])
+            return fail(TN_ERROR, "gemm: batch dim %d of the second operand does not broadcast", dim);
+    }
+    g.has_scale = 0;
+    g.scale_f = 1.0;
+    g.scale_i = 1;
+    if (scale) {
+        if (scale->dtype != dst->dtype) return fail(TN_UNSUPPORTED_DTYPE, "gemm_scaled: scalar dtype %d, result dtype %d", (int)scale->dtype, (int)dst->dtype);
+        if (!read_host_scalar(scale, &g.scale_f, &g.scale_i)) return fail(TN_ERROR, "gemm_scaled: unreadable scalar");
+        g.has_scale = 1;
+    }
+    if (g.M == 0 || g.N == 0 || g.batches == 0) return TN_SUCCESS;
+    cudaStream_t s = as_cuda(stream);
+
+    // ---- tensor-core path: 16-bit operands of one type, result of that type or fp32,
+    //      row-major result, batch dims that collapse to one stride per operand.
+    if (a->dtype == b->dtype && is_half(a->dtype) && (dst->dtype == a->dtype || dst->dtype == TN_FLOAT32) &&
+        g.a_sk == 1 && g.d_sn == 1 && (g.b_sk == 1 || g.b_sn == 1) && g.K > 0) {
+        // collapse the batch dims of each operand into (count, stride); possible when walking
+        // them in row-major order advances by a constant stride, or the operand is shared
+        auto collapse = [&](const int64_t* bs, int64_t* stride) {
+            bool any = false, all = true;
+            int64_t expect = 0;
+            for (int dim = g.nbatch - 1; dim >= 0; --dim) {
+                if (g.bsize[dim] == 1) continue;
+                if (bs[dim] == 0) { all = false; continue; }
+                if (!any) { expect = bs[dim]; *stride = bs[dim]; any = true; }
+                if (bs[dim] != expect) return false;
+                expect = bs[dim] * g.bsize[dim];
+            }
+            if (!any) { *stride = 0; return true; }  // shared by every batch
+            return all;                                // partial broadcast does not collapse
+        };
+        int64_t sa = 0, sb = 0, sd = 0;
+        if (collapse(g.a_bs, &sa) && collapse(g.b_bs, &sb) && collapse(g.d_bs, &sd) && (sd != 0 || g.batches == 1)) {
+            TcGemm p;
+            p.a = g.a;
+            p.b = g.b;
+            p.d = g.d;
+            p.ab_dtype = a->dtype;
+            p.d_dtype = dst->dtype;
+            p.M = g.M;
+            p.N = g.N;
+            p.K = g.K;
+            p.lda = g.a_sm;
+            p.b_n_major = g.b_sk != 1;  // then b_sn == 1: rows of B are N-contiguous
+            p.ldb = p.b_n_major ? g.b_sk : g.b_sn;
+            p.ldd = g.d_sm;
+            p.batches = g.batches;
+            p.a_batch = sa;
+            p.b_batch = sb;
+            p.d_batch = sd;
+            // [B, M, K] x shared [K, N] with dense A and D folds into one tall GEMM
+            if (g.batches > 1 && sb == 0 && sa == g.M * g.a_sm && sd == g.M * g.d_sm) {
+                p.M = g.M * g.batches;
+                p.batches = 1;
+                p.a_batch = p.d_batch = 0;
+            }
+            p.has_scale = g.has_scale != 0;
+            p.scale = (float)g.scale_f;
+            if (tc_gemm_eligible(p)) return tc_gemm(p, s);
+        }
+    }
+
+    // ---- SIMT path
+    const int64_t gx = ceil_div(g.N, TN), gy = ceil_div(g.M, TM);
+    if (gy > 65535) return fail(TN_ERROR, "gemm: M = %lld is too large for the SIMT path", (long long)g.M);
+    const dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)(g.batches < 65535 ? g.batches : 65535));
+    switch (compute_class(a->dtype, b->dtype)) {
+        case 2: gemm_simt<double><<<grid, 256, 0, s>>>(g); break;
+        case 1: gemm_simt<float><<<grid, 256, 0, s>>>(g); break;
+        default: gemm_simt<int64_t><<<grid, 256, 0, s>>>(g); break;
+    }
+    return after_launch("gemm_simt");
+}
+
+}  // namespace
+}  // namespace tnb
+
+using namespace tnb;
+
+extern "C" {
+
+tn_status tn_gemm(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream) {
+    return gemm_impl(a, b, dst, nullptr, stream);
+}
+
+tn_status tn_gemm_scaled(const tn_tensor_t* a, const tn_tensor_t* b, const tn_scalar_t* scale, tn_tensor_t* dst,
+                         tn_stream_t stream) {
+    if (!scale) return fail(TN_ERROR, "null scalar");
+    return gemm_impl(a, b, dst, scale, stream);
+}
+
+tn_status tn_device_errors(unsigned int* count) {
+    if (!count) return fail(TN_ERROR, "null count");
+    return tc_abort_count(count);
+}
+
+}  // extern "C"

@@ -1,0 +1,467 @@
+// Batched GEMM on the 5th-generation tensor cores of sm_100a: tcgen05.mma with the fp32
+// accumulator in tensor memory, operands staged in shared memory by TMA through a multistage
+// mbarrier pipeline, warp-specialised roles, persistent CTAs (one per SM).
+//
+//   warp 0      TMA producer   (one elected lane issues cp.async.bulk.tensor loads)
+//   warp 1      MMA issuer     (one elected lane issues tcgen05.mma / tcgen05.commit)
+//   warps 2..5  epilogue       (tcgen05.ld -> convert -> transposed through smem -> coalesced
+//                               stores; each warp owns the TMEM lane quarter (warp % 4))
+//
+// CTA tile 128 x 256 x 64: one UMMA is M=128, N=256, K=16, so a K-block is four MMAs. The
+// 512 TMEM columns hold two 128x256 fp32 accumulators, so the epilogue of tile i overlaps the
+// main loop of tile i+1. No multicast is used anywhere: every CTA issues its own TMA loads and
+// L2 provides the reuse between neighbouring tiles.
+//
+// Every wait on an mbarrier is bounded. When a wait runs out the CTA raises an abort flag, all
+// roles leave their loops, outstanding TMA transactions are given time to land, tensor memory
+// is released and a device-side error counter is incremented (read by tn_device_errors()).
+#include "gemm_tc.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+
+namespace tnb {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;            // 64 x 2 bytes = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 4;
+constexpr uint32_t A_BYTES = BM * BK * 2;        // 16 KiB
+constexpr uint32_t B_BYTES = BN * BK * 2;        // 32 KiB
+constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr uint32_t TMEM_COLS = 512;              // two accumulators of BN fp32 columns
+constexpr int STAGING_PITCH = 33;                // words per staged row (conflict-free transpose)
+constexpr uint32_t STAGING_BYTES = kEpilogueWarps * 32 * STAGING_PITCH * 4;
+constexpr uint32_t SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + STAGING_BYTES + 256 /*barriers*/;
+
+constexpr uint32_t kSpinFast = 2048;      // polls without sleeping
+constexpr uint32_t kSpinLimit = 1u << 20; // then ~64 ns sleeps: gives up after roughly 0.1 s
+
+__device__ unsigned int g_tc_aborts = 0;
+
+// ------------------------------------------------------------------ PTX wrappers ------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Bounded wait. Returns false when the CTA is aborting (this wait or another one ran out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        if (mbar_test(bar, parity)) return true;
+        if (it >= kSpinFast) {
+            if (*abort_flag) return false;
+            __nanosleep(64);
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+        " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a 128-byte-swizzled tile (sm_100 format: start address,
+// leading / stride byte offsets in 16-byte units, version 1 at bit 46, layout type 2 =
+// SWIZZLE_128B at bits 61-63).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr & 0x3FFFF) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+struct KernelArgs {
+    void* d;
+    const void* bias;
+    int64_t M, N, K;
+    int64_t ldd, d_batch;
+    int m_tiles, n_tiles;
+    int64_t total_tiles;
+    int a_batched, b_batched;  // 0: operand shared by all batches (batch coordinate pinned to 0)
+    int is_bf16;               // operand format: 1 = bf16, 0 = fp16
+    int d_is_f32;
+    int has_scale;
+    float scale;
+};
+
+// Tiles are walked in groups of 16 row-tiles so that the CTAs running at the same time share
+// rows of A and columns of B in L2.
+constexpr int kGroupM = 16;
+__device__ __forceinline__ void tile_coords(int64_t t, int m_tiles, int n_tiles, int& batch, int& mt, int& nt) {
+    const int64_t per_batch = static_cast<int64_t>(m_tiles) * n_tiles;
+    batch = static_cast<int>(t / per_batch);
+    int r = static_cast<int>(t - static_cast<int64_t>(batch) * per_batch);
+    const int group_span = kGroupM * n_tiles;
+    const int g = r / group_span;
+    r -= g * group_span;
+    const int rows_in_group = min(kGroupM, m_tiles - g * kGroupM);
+    nt = r / rows_in_group;
+    mt = g * kGroupM + (r - nt * rows_in_group);
+}
+
+template <typename OutT>
+__device__ __forceinline__ OutT finish(float acc, const KernelArgs& g, float bias) {
+    float v = acc + bias;
+    if constexpr (std::is_same<OutT, float>::value) {
+        return g.has_scale ? v * g.scale : v;
+    } else {
+        OutT r = from_compute<OutT, float>(v);
+        if (g.has_scale) r = from_compute<OutT, float>(to_compute<float>(r) * g.scale);
+        return r;
+    }
+}
+
+template <bool B_N_MAJOR>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KernelArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
+    uint8_t* base_ptr = smem_raw + (base - raw);
+    const uint32_t staging = base + STAGES * STAGE_BYTES;
+    uint32_t* staging_ptr = reinterpret_cast<uint32_t*>(base_ptr + STAGES * STAGE_BYTES);
+    const uint32_t bars = staging + STAGING_BYTES;
+    // barrier layout (8 bytes each): full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, accf0 = bars + 16 * STAGES, acce0 = accf0 + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + STAGES * STAGE_BYTES + STAGING_BYTES + 16 * STAGES + 32);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_blocks = static_cast<int>((g.K + BK - 1) / BK);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(accf0 + 8 * b, 1);
+            mbar_init(acce0 + 8 * b, kEpilogueWarps);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer ----
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
+                int batch, mt, nt;
+                tile_coords(t, g.m_tiles, g.n_tiles, batch, mt, nt);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t parity = ((it / STAGES) & 1) ^ 1;
+                    if (!mbar_wait(empty0 + 8 * s, parity, abort_flag)) { ok = false; break; }
+                    const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
+                    mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                    tma_load_3d(sa, &map_a, full0 + 8 * s, kb * BK, mt * BM, g.a_batched ? batch : 0);
+                    if constexpr (B_N_MAJOR) {
+                        // four boxes of 64 columns x BK rows, 8 KiB each
+#pragma unroll
+                        for (int c = 0; c < BN / 64; ++c)
+                            tma_load_3d(sb + c * (64 * BK * 2), &map_b, full0 + 8 * s, nt * BN + c * 64, kb * BK, g.b_batched ? batch : 0);
+                    } else {
+                        tma_load_3d(sb, &map_b, full0 + 8 * s, kb * BK, nt * BN, g.b_batched ? batch : 0);
+                    }
+                }
+            }
+            if (!ok) {
+                // give transactions that were already issued time to land before smem goes away
+                for (int spin = 0; spin < 4096; ++spin) __nanosleep(64);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer ------
+        if (lane == 0) {
+            // instruction descriptor: D = F32 (bits 4-5 = 1), A/B format (bits 7-9, 10-12:
+            // 0 = F16, 1 = BF16), B major (bit 16), N >> 3 (bits 17-22), M >> 4 (bits 24-28)
+            const uint32_t fmt = g.is_bf16 ? 1u : 0u;
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((B_N_MAJOR ? 1u : 0u) << 16) |
+                                   (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+            uint32_t it = 0, local_tile = 0;
+            bool ok = true;
+            for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x, ++local_tile) {
+                const int buf = local_tile & 1;
+                const uint32_t acc_parity = ((local_tile >> 1) & 1) ^ 1;
+                if (!mbar_wait(acce0 + 8 * buf, acc_parity, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t tmem_acc = tmem_base + buf * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t parity = (it / STAGES) & 1;
+                    if (!mbar_wait(full0 + 8 * s, parity, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // K-major: 16 elements = 32 bytes further along the swizzled row.
+                        const uint64_t da = smem_desc(sa + k * UMMA_K * 2, 16, 1024);
+                        // N-major: 16 k-rows of 128 bytes further; 64-column boxes are 8 KiB apart.
+                        const uint64_t db = B_N_MAJOR ? smem_desc(sb + k * UMMA_K * 128, 64 * BK * 2, 1024)
+                                                      : smem_desc(sb + k * UMMA_K * 2, 16, 1024);
+                        umma_f16(tmem_acc, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
+                }
+                if (ok) umma_commit(accf0 + 8 * buf);  // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue --------
+        const int ew = warp - 2;                 // staging slot
+        const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter+32)
+        uint32_t* stage_rows = staging_ptr + ew * 32 * STAGING_PITCH;
+        uint32_t local_tile = 0;
+        bool ok = true;
+        for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x, ++local_tile) {
+            int batch, mt, nt;
+            tile_coords(t, g.m_tiles, g.n_tiles, batch, mt, nt);
+            const int buf = local_tile & 1;
+            const uint32_t parity = (local_tile >> 1) & 1;
+            if (!mbar_wait(accf0 + 8 * buf, parity, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int64_t row0 = static_cast<int64_t>(mt) * BM + quarter * 32;
+            const int64_t col_base = static_cast<int64_t>(nt) * BN;
+            const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+            float bias = 0.0f;
+            if (g.bias != nullptr && row0 + lane < g.M) {
+                bias = g.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(g.bias)[row0 + lane])
+                                 : __half2float(static_cast<const __half*>(g.bias)[row0 + lane]);
+            }
+            uint8_t* dbase = static_cast<uint8_t*>(g.d) + static_cast<size_t>(batch) * g.d_batch * (g.d_is_f32 ? 4 : 2);
+            for (int c = 0; c < BN / 32; ++c) {
+                const int64_t col0 = col_base + c * 32;
+                if (col0 >= g.N || row0 >= g.M) break;  // warp-uniform
+                uint32_t v[32];
+                tmem_load_32x32(taddr0 + c * 32, v);
+                // lane owns row (row0 + lane), columns col0 .. col0+31: stage, then write rows
+                // out with lanes across columns so that every store instruction is contiguous
+                __syncwarp();
+                if (g.d_is_f32) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        stage_rows[lane * STAGING_PITCH + j] = __float_as_uint(finish<float>(__uint_as_float(v[j]), g, bias));
+                } else if (g.is_bf16) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const __nv_bfloat16 h = finish<__nv_bfloat16>(__uint_as_float(v[j]), g, bias);
+                        stage_rows[lane * STAGING_PITCH + j] = static_cast<uint32_t>(__bfloat16_as_ushort(h));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const __half h = finish<__half>(__uint_as_float(v[j]), g, bias);
+                        stage_rows[lane * STAGING_PITCH + j] = static_cast<uint32_t>(__half_as_ushort(h));
+                    }
+                }
+                __syncwarp();
+                const int64_t col = col0 + lane;
+                if (col < g.N) {
+                    const int rows = static_cast<int>(min(static_cast<int64_t>(32), g.M - row0));
+                    if (g.d_is_f32) {
+                        float* out = reinterpret_cast<float*>(dbase) + row0 * g.ldd + col;
+                        for (int r = 0; r < rows; ++r) out[r * g.ldd] = __uint_as_float(stage_rows[r * STAGING_PITCH + lane]);
+                    } else {
+                        uint16_t* out = reinterpret_cast<uint16_t*>(dbase) + row0 * g.ldd + col;
+                        for (int r = 0; r < rows; ++r) out[r * g.ldd] = static_cast<uint16_t>(stage_rows[r * STAGING_PITCH + lane]);
+                    }
+                }
+            }
+            // this warp has finished reading the accumulator
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce0 + 8 * buf);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && *abort_flag) atomicAdd(&g_tc_aborts, 1u);
+}
+
+// ------------------------------------------------------------------ host --------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// 3-D map (inner, rows, batch) over a 16-bit matrix; box = box_inner x box_rows x 1, 128B swizzle.
+tn_status make_map(CUtensorMap* map, const void* ptr, bool bf16, int64_t inner, int64_t rows, int64_t batches,
+                   int64_t row_pitch, int64_t batch_pitch, int box_inner, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(TN_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)(batches > 0 ? batches : 1)};
+    // a pitch is irrelevant for an extent of 1 but must still be a non-zero multiple of 16 bytes
+    cuuint64_t pitch_rows = (cuuint64_t)row_pitch * 2;
+    cuuint64_t pitch_batch = (cuuint64_t)(batch_pitch > 0 ? batch_pitch : row_pitch * rows) * 2;
+    if (pitch_rows == 0) pitch_rows = (cuuint64_t)inner * 2;
+    if (pitch_batch == 0) pitch_batch = pitch_rows;
+    cuuint64_t strides[2] = {pitch_rows, pitch_batch};
+    cuuint32_t box[3] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TN_ERROR, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return TN_SUCCESS;
+}
+
+bool mult8(int64_t v) { return (v & 7) == 0; }
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+bool tc_gemm_eligible(const TcGemm& p) {
+    if (p.ab_dtype != TN_FLOAT16 && p.ab_dtype != TN_BFLOAT16) return false;
+    if (p.d_dtype != p.ab_dtype && p.d_dtype != TN_FLOAT32) return false;
+    if (p.M <= 0 || p.N <= 0 || p.K <= 0 || p.batches <= 0) return false;
+    if (!aligned16(p.a) || !aligned16(p.b)) return false;
+    if (!mult8(p.lda) || !mult8(p.ldb) || !mult8(p.a_batch) || !mult8(p.b_batch)) return false;
+    if (p.lda < p.K) return false;
+    if (p.b_n_major ? p.ldb < p.N : p.ldb < p.K) return false;
+    // extents must fit the 32-bit coordinates of a tensor map with headroom
+    if (p.M >= (int64_t(1) << 31) || p.N >= (int64_t(1) << 31) || p.K >= (int64_t(1) << 31) || p.batches >= (int64_t(1) << 31)) return false;
+    const int64_t tiles = ceil_div(p.M, BM) * ceil_div(p.N, BN) * p.batches;
+    return tiles < (int64_t(1) << 40);
+}
+
+tn_status tc_gemm(const TcGemm& p, cudaStream_t stream) {
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(tc_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute(tc_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    });
+    // the attribute is per device: set again when the current device changes
+    static thread_local int attr_device = -1;
+    int dev = 0;
+    TN_CUDA(cudaGetDevice(&dev));
+    if (attr_device != dev) {
+        TN_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        TN_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_device = dev;
+    }
+    if (attr_err != cudaSuccess) return fail(TN_ERROR, "cannot reserve %u bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(attr_err));
+
+    const bool bf16 = p.ab_dtype == TN_BFLOAT16;
+    CUtensorMap map_a, map_b;
+    TN_TRY(make_map(&map_a, p.a, bf16, p.K, p.M, p.a_batch ? p.batches : 1, p.lda, p.a_batch, BK, BM));
+    if (p.b_n_major) TN_TRY(make_map(&map_b, p.b, bf16, p.N, p.K, p.b_batch ? p.batches : 1, p.ldb, p.b_batch, 64, BK));
+    else TN_TRY(make_map(&map_b, p.b, bf16, p.K, p.N, p.b_batch ? p.batches : 1, p.ldb, p.b_batch, BK, BN));
+
+    KernelArgs g;
+    g.d = p.d;
+    g.bias = p.bias;
+    g.M = p.M;
+    g.N = p.N;
+    g.K = p.K;
+    g.ldd = p.ldd;
+    g.d_batch = p.d_batch;
+    g.m_tiles = (int)ceil_div(p.M, BM);
+    g.n_tiles = (int)ceil_div(p.N, BN);
+    g.total_tiles = (int64_t)g.m_tiles * g.n_tiles * p.batches;
+    g.a_batched = p.a_batch != 0;
+    g.b_batched = p.b_batch != 0;
+    g.is_bf16 = bf16;
+    g.d_is_f32 = p.d_dtype == TN_FLOAT32;
+    g.has_scale = p.has_scale;
+    g.scale = p.scale;
+    const int64_t sms = sm_count();
+    const int grid = (int)(g.total_tiles < sms ? g.total_tiles : sms);
+    if (p.b_n_major) tc_gemm_kernel<true><<<grid, kThreads, SMEM_BYTES, stream>>>(map_a, map_b, g);
+    else tc_gemm_kernel<false><<<grid, kThreads, SMEM_BYTES, stream>>>(map_a, map_b, g);
+    return after_launch("tc_gemm_kernel");
+}
+
+tn_status tc_abort_count(unsigned int* count) {
+    TN_CUDA(cudaMemcpyFromSymbol(count, g_tc_aborts, sizeof(unsigned int)));
+    return TN_SUCCESS;
+}
+
+}  // namespace tnb

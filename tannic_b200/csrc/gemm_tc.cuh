@@ -1,0 +1,32 @@
+// Interface between the GEMM / conv dispatchers and the tcgen05 tensor-core kernel.
+#pragma once
+
+#include "common.cuh"
+
+namespace tnb {
+
+// One batched GEMM  D[b] = A[b] . B[b]^T-or-not  on 16-bit operands with fp32 accumulation in
+// TMEM. A is K-major ([M, K], K contiguous). B is K-major ([N, K], K contiguous: the layout of
+// `W` in `matmul(X, W.transpose(-1,-2))`) or N-major ([K, N], N contiguous: plain matmul, and
+// the activation matrix [Cin, H*W] of a 1x1 convolution).
+struct TcGemm {
+    const void* a = nullptr;
+    const void* b = nullptr;
+    void* d = nullptr;
+    const void* bias = nullptr;  // optional per-row (M) bias of the operand dtype, seeds the accumulator
+    int ab_dtype = 0;            // TN_FLOAT16 or TN_BFLOAT16
+    int d_dtype = 0;             // ab_dtype or TN_FLOAT32
+    int64_t M = 0, N = 0, K = 0;
+    int64_t lda = 0, ldb = 0, ldd = 0;              // leading dimensions in elements
+    int64_t batches = 1;
+    int64_t a_batch = 0, b_batch = 0, d_batch = 0;  // batch strides in elements, 0 = shared
+    bool b_n_major = false;
+    bool has_scale = false;      // d = round(round(acc) * scale)
+    float scale = 1.0f;
+};
+
+// True when TMA can address the operands (16-byte aligned bases and pitches).
+bool tc_gemm_eligible(const TcGemm& p);
+tn_status tc_gemm(const TcGemm& p, cudaStream_t stream);
+
+}  // namespace tnb

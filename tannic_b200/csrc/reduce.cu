@@ -1,0 +1,449 @@
+// Axis reductions: argmax / argmin (int64 index, first occurrence, NaN never selected),
+// sum / mean (accumulate wider than storage), value max, and a fused max+sum+argmax pass.
+// Replaces src/cuda/argred.cu of the reference (one thread per output, serial over the axis).
+//
+// Kernels:
+//   reduce_rows_warp   dense source, last axis: one warp per row, 16-byte loads where the row
+//                      is aligned, shuffle combine; rows may start at any element offset
+//                      (197-wide bf16 rows have a 394-byte pitch);
+//   reduce_rows_block  same geometry for long rows: one CTA per row;
+//   reduce_split       few, very long rows: every row is cut into segments whose partial
+//                      results go to scratch memory, a second kernel combines them;
+//   reduce_cols        dense source, inner axis: one thread per output column, coalesced
+//                      across the inner extent;
+//   reduce_strided     any view: one thread per output.
+#include "common.cuh"
+
+#include <cfloat>
+#include <climits>
+
+namespace tnb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int64_t kNoIndex = INT64_MAX;
+
+template <typename T> struct acc_of { using type = int64_t; };  // integers: int64 (src/cuda/argred.cu:167-187)
+template <> struct acc_of<__half> { using type = float; };
+template <> struct acc_of<__nv_bfloat16> { using type = float; };
+template <> struct acc_of<float> { using type = double; };
+template <> struct acc_of<double> { using type = double; };
+
+template <typename T> struct cmp_of { using type = T; };
+template <> struct cmp_of<__half> { using type = float; };
+template <> struct cmp_of<__nv_bfloat16> { using type = float; };
+
+template <typename C, bool MIN> __device__ __forceinline__ C cmp_init() {
+    if constexpr (std::is_same<C, float>::value) return MIN ? INFINITY : -INFINITY;
+    else if constexpr (std::is_same<C, double>::value) return MIN ? (double)INFINITY : -(double)INFINITY;
+    else if constexpr (std::is_same<C, int8_t>::value) return MIN ? INT8_MAX : INT8_MIN;
+    else if constexpr (std::is_same<C, int16_t>::value) return MIN ? INT16_MAX : INT16_MIN;
+    else if constexpr (std::is_same<C, int32_t>::value) return MIN ? INT32_MAX : INT32_MIN;
+    else return MIN ? INT64_MAX : INT64_MIN;
+}
+
+// Running state of one lane. The lane visits its elements in ascending index order, so a
+// strict comparison keeps the first occurrence; an element equal to the initial value never
+// wins, which leaves index 0 for rows made of -inf / NaN only (src/cpu/argred.cpp:80-108).
+template <typename T, bool SUM, bool ARG, bool MIN>
+struct State {
+    using A = typename acc_of<T>::type;
+    using C = typename cmp_of<T>::type;
+    A sum;
+    C best;
+    int64_t idx;
+    __device__ __forceinline__ void init() {
+        sum = A(0);
+        best = cmp_init<C, MIN>();
+        idx = kNoIndex;
+    }
+    __device__ __forceinline__ void feed(T raw, int64_t i) {
+        if constexpr (SUM) sum += to_compute<A>(raw);
+        if constexpr (ARG) {
+            const C v = to_compute<C>(raw);
+            if (MIN ? (v < best) : (v > best)) {
+                best = v;
+                idx = i;
+            }
+        }
+    }
+    __device__ __forceinline__ void merge(A osum, C obest, int64_t oidx) {
+        if constexpr (SUM) sum += osum;
+        if constexpr (ARG) {
+            const bool better = MIN ? (obest < best) : (obest > best);
+            if (better || (obest == best && oidx < idx)) {
+                best = obest;
+                idx = oidx;
+            }
+        }
+    }
+    __device__ __forceinline__ void merge(const State& o) { merge(o.sum, o.best, o.idx); }
+};
+
+template <typename V> __device__ __forceinline__ V shfl_xor(V v, int mask) { return __shfl_xor_sync(0xffffffffu, v, mask); }
+template <> __device__ __forceinline__ int8_t shfl_xor<int8_t>(int8_t v, int mask) { return (int8_t)__shfl_xor_sync(0xffffffffu, (int)v, mask); }
+template <> __device__ __forceinline__ int16_t shfl_xor<int16_t>(int16_t v, int mask) { return (int16_t)__shfl_xor_sync(0xffffffffu, (int)v, mask); }
+template <> __device__ __forceinline__ int64_t shfl_xor<int64_t>(int64_t v, int mask) { return (int64_t)__shfl_xor_sync(0xffffffffu, (long long)v, mask); }
+
+template <typename T, bool SUM, bool ARG, bool MIN>
+__device__ __forceinline__ void warp_combine(State<T, SUM, ARG, MIN>& st) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        typename State<T, SUM, ARG, MIN>::A osum = SUM ? shfl_xor(st.sum, m) : st.sum;
+        typename State<T, SUM, ARG, MIN>::C obest = ARG ? shfl_xor(st.best, m) : st.best;
+        int64_t oidx = ARG ? shfl_xor(st.idx, m) : st.idx;
+        st.merge(osum, obest, oidx);
+    }
+}
+
+struct Outputs {
+    void* sum;      // storage dtype: sum or mean
+    void* value;    // storage dtype: max / min value
+    int64_t* index; // int64
+    int mean;       // divide the sum by the axis length
+};
+
+template <typename T, bool SUM, bool ARG, bool MIN>
+__device__ __forceinline__ void write_out(const State<T, SUM, ARG, MIN>& st, const Outputs& out, int64_t o, int64_t len,
+                                          T first) {
+    using A = typename acc_of<T>::type;
+    if constexpr (SUM) {
+        if (out.sum) {
+            A s = st.sum;
+            if (out.mean) s = s / static_cast<A>(len);
+            static_cast<T*>(out.sum)[o] = from_compute<T, A>(s);
+        }
+    }
+    if constexpr (ARG) {
+        const bool none = st.idx == kNoIndex;
+        if (out.index) out.index[o] = none ? 0 : st.idx;
+        if (out.value) static_cast<T*>(out.value)[o] = none ? first : from_compute<T, typename cmp_of<T>::type>(st.best);
+    }
+}
+
+// Feeds elements [lo, hi) of a dense row to `st`; `lane` of `lanes` cooperating threads.
+// Whole 16-byte groups are fetched with one load, ragged edges element by element.
+template <typename T, bool SUM, bool ARG, bool MIN>
+__device__ __forceinline__ void scan_dense(State<T, SUM, ARG, MIN>& st, const T* row, int64_t lo, int64_t hi, int lane,
+                                           int lanes) {
+    constexpr int V = 16 / sizeof(T);
+    const uintptr_t base = reinterpret_cast<uintptr_t>(row + lo);
+    // element offset (relative to lo) of the first 16-byte boundary at or before row+lo
+    const int64_t head = -static_cast<int64_t>((base & 15) / sizeof(T));
+    const int64_t n = hi - lo;
+    for (int64_t g = head + (int64_t)lane * V; g < n; g += (int64_t)lanes * V) {
+        if (g >= 0 && g + V <= n) {
+            alignas(16) T e[V];
+            *reinterpret_cast<uint4*>(e) = __ldg(reinterpret_cast<const uint4*>(row + lo + g));
+#pragma unroll
+            for (int k = 0; k < V; ++k) st.feed(e[k], lo + g + k);
+        } else {
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                const int64_t j = g + k;
+                if (j >= 0 && j < n) st.feed(row[lo + j], lo + j);
+            }
+        }
+    }
+}
+
+template <typename T, bool SUM, bool ARG, bool MIN>
+__global__ void __launch_bounds__(kThreads) reduce_rows_warp(const T* __restrict__ src, int64_t rows, int64_t len, Outputs out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * kThreads) >> 5;
+    for (int64_t r = warp; r < rows; r += nwarps) {
+        const T* row = src + r * len;
+        State<T, SUM, ARG, MIN> st;
+        st.init();
+        scan_dense(st, row, 0, len, lane, 32);
+        warp_combine(st);
+        if (lane == 0) write_out(st, out, r, len, len > 0 ? row[0] : T());
+    }
+}
+
+template <typename T, bool SUM, bool ARG, bool MIN>
+__device__ __forceinline__ void block_combine(State<T, SUM, ARG, MIN>& st) {
+    using S = State<T, SUM, ARG, MIN>;
+    __shared__ typename S::A s_sum[kThreads / 32];
+    __shared__ typename S::C s_best[kThreads / 32];
+    __shared__ int64_t s_idx[kThreads / 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    warp_combine(st);
+    __syncthreads();  // protects the arrays across successive calls
+    if (lane == 0) {
+        s_sum[warp] = st.sum;
+        s_best[warp] = st.best;
+        s_idx[warp] = st.idx;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        if (lane < kThreads / 32) {
+            st.sum = s_sum[lane];
+            st.best = s_best[lane];
+            st.idx = s_idx[lane];
+        } else {
+            st.init();
+        }
+        warp_combine(st);
+    }
+}
+
+template <typename T, bool SUM, bool ARG, bool MIN>
+__global__ void __launch_bounds__(kThreads) reduce_rows_block(const T* __restrict__ src, int64_t rows, int64_t len, Outputs out) {
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const T* row = src + r * len;
+        State<T, SUM, ARG, MIN> st;
+        st.init();
+        scan_dense(st, row, 0, len, threadIdx.x, kThreads);
+        block_combine(st);
+        if (threadIdx.x == 0) write_out(st, out, r, len, len > 0 ? row[0] : T());
+    }
+}
+
+// Partial result of one segment of one row, kept in scratch memory between the two kernels of
+// the split reduction.
+template <typename T> struct Partial {
+    typename acc_of<T>::type sum;
+    typename cmp_of<T>::type best;
+    int64_t idx;
+};
+
+template <typename T, bool SUM, bool ARG, bool MIN>
+__global__ void __launch_bounds__(kThreads) reduce_split_partial(const T* __restrict__ src, int64_t len, int splits,
+                                                                 Partial<T>* __restrict__ scratch) {
+    const int64_t r = blockIdx.y;
+    const int seg = blockIdx.x;
+    const int64_t per = (len + splits - 1) / splits;
+    const int64_t lo = (int64_t)seg * per;
+    const int64_t hi = lo + per < len ? lo + per : len;
+    State<T, SUM, ARG, MIN> st;
+    st.init();
+    if (lo < hi) scan_dense(st, src + r * len, lo, hi, threadIdx.x, kThreads);
+    block_combine(st);
+    if (threadIdx.x == 0) {
+        Partial<T> p;
+        p.sum = st.sum;
+        p.best = st.best;
+        p.idx = st.idx;
+        scratch[r * splits + seg] = p;
+    }
+}
+
+template <typename T, bool SUM, bool ARG, bool MIN>
+__global__ void __launch_bounds__(32) reduce_split_final(const T* __restrict__ src, int64_t rows, int64_t len, int splits,
+                                                         const Partial<T>* __restrict__ scratch, Outputs out) {
+    const int64_t r = blockIdx.x;
+    if (r >= rows) return;
+    State<T, SUM, ARG, MIN> st;
+    st.init();
+    // segments are visited in ascending order per lane and merged with the lowest-index rule
+    for (int s = threadIdx.x; s < splits; s += 32) {
+        const Partial<T> p = scratch[r * splits + s];
+        st.merge(p.sum, p.best, p.idx);
+    }
+    warp_combine(st);
+    if (threadIdx.x == 0) write_out(st, out, r, len, len > 0 ? src[r * len] : T());
+}
+
+// Source dense as [outer, len, inner]; thread per (outer, inner) output.
+template <typename T, bool SUM, bool ARG, bool MIN>
+__global__ void __launch_bounds__(kThreads) reduce_cols(const T* __restrict__ src, int64_t outer, int64_t len, int64_t inner,
+                                                        Outputs out) {
+    const int64_t total = outer * inner;
+    const int64_t step = (int64_t)gridDim.x * kThreads;
+    for (int64_t o = (int64_t)blockIdx.x * kThreads + threadIdx.x; o < total; o += step) {
+        const int64_t ou = o / inner, in = o - ou * inner;
+        const T* col = src + ou * len * inner + in;
+        State<T, SUM, ARG, MIN> st;
+        st.init();
+        int64_t l = 0;
+        for (; l + 4 <= len; l += 4) {
+            T v0 = __ldg(col + (l + 0) * inner), v1 = __ldg(col + (l + 1) * inner);
+            T v2 = __ldg(col + (l + 2) * inner), v3 = __ldg(col + (l + 3) * inner);
+            st.feed(v0, l);
+            st.feed(v1, l + 1);
+            st.feed(v2, l + 2);
+            st.feed(v3, l + 3);
+        }
+        for (; l < len; ++l) st.feed(__ldg(col + l * inner), l);
+        write_out(st, out, o, len, len > 0 ? col[0] : T());
+    }
+}
+
+struct StridedGeom {
+    int rank;                     // dims other than the axis
+    int64_t sizes[TN_MAX_RANK];   // their extents, outermost first
+    int64_t strides[TN_MAX_RANK]; // their element strides
+    int64_t len, axis_stride, total;
+};
+
+template <typename T, bool SUM, bool ARG, bool MIN>
+__global__ void __launch_bounds__(kThreads) reduce_strided(const T* __restrict__ src, StridedGeom g, Outputs out) {
+    const int64_t step = (int64_t)gridDim.x * kThreads;
+    for (int64_t o = (int64_t)blockIdx.x * kThreads + threadIdx.x; o < g.total; o += step) {
+        int64_t rem = o, off = 0;
+        for (int d = g.rank - 1; d >= 0; --d) {
+            const int64_t c = rem % g.sizes[d];
+            rem /= g.sizes[d];
+            off += c * g.strides[d];
+        }
+        State<T, SUM, ARG, MIN> st;
+        st.init();
+        for (int64_t l = 0; l < g.len; ++l) st.feed(src[off + l * g.axis_stride], l);
+        write_out(st, out, o, g.len, g.len > 0 ? src[off] : T());
+    }
+}
+
+// ------------------------------------------------------------------ host --------------
+int grid_cap() { return sm_count() * 8; }
+
+template <typename T, bool SUM, bool ARG, bool MIN>
+tn_status launch(const tn_tensor_t* src, int axis, Outputs out, cudaStream_t s) {
+    const int R = src->rank;
+    int64_t outer = 1, inner = 1;
+    const int64_t len = (int64_t)src->shape.sizes[axis];
+    for (int d = 0; d < axis; ++d) outer *= (int64_t)src->shape.sizes[d];
+    for (int d = axis + 1; d < R; ++d) inner *= (int64_t)src->shape.sizes[d];
+    const int64_t total = outer * inner;
+    if (total == 0) return TN_SUCCESS;
+    // dense row-major?
+    bool dense = true;
+    int64_t expect = 1;
+    for (int d = R - 1; d >= 0; --d) {
+        const int64_t sz = (int64_t)src->shape.sizes[d];
+        if (sz != 1 && src->strides.sizes[d] != expect) dense = false;
+        expect *= sz;
+    }
+    const T* p = static_cast<const T*>(src->address);
+    const int cap = grid_cap();
+    if (dense && inner == 1) {
+        const int64_t row_bytes = len * (int64_t)sizeof(T);
+        if (total < (int64_t)sm_count() && row_bytes >= (int64_t(1) << 20)) {
+            // few very long rows: cut each into segments so every SM streams a share
+            int splits = (int)ceil_div((int64_t)sm_count() * 4, total);
+            const int64_t max_splits = ceil_div(row_bytes, int64_t(64) << 10);
+            if (splits > max_splits) splits = (int)max_splits;
+            if (splits > 1024) splits = 1024;
+            Partial<T>* scratch = nullptr;
+            TN_TRY(scratch_alloc(reinterpret_cast<void**>(&scratch), sizeof(Partial<T>) * total * splits, s));
+            reduce_split_partial<T, SUM, ARG, MIN><<<dim3(splits, (unsigned)total), kThreads, 0, s>>>(p, len, splits, scratch);
+            tn_status st = after_launch("reduce_split_partial");
+            if (st == TN_SUCCESS) {
+                reduce_split_final<T, SUM, ARG, MIN><<<(unsigned)total, 32, 0, s>>>(p, total, len, splits, scratch, out);
+                st = after_launch("reduce_split_final");
+            }
+            tn_status fr = scratch_free(scratch, s);
+            return st != TN_SUCCESS ? st : fr;
+        }
+        if (row_bytes >= 16384) {
+            const int grid = (int)(total < cap ? total : cap);
+            reduce_rows_block<T, SUM, ARG, MIN><<<grid, kThreads, 0, s>>>(p, total, len, out);
+            return after_launch("reduce_rows_block");
+        }
+        int64_t blocks = ceil_div(total, kThreads / 32);
+        if (blocks > cap) blocks = cap;
+        reduce_rows_warp<T, SUM, ARG, MIN><<<(int)blocks, kThreads, 0, s>>>(p, total, len, out);
+        return after_launch("reduce_rows_warp");
+    }
+    if (dense) {
+        int64_t blocks = ceil_div(total, kThreads);
+        if (blocks > cap) blocks = cap;
+        reduce_cols<T, SUM, ARG, MIN><<<(int)blocks, kThreads, 0, s>>>(p, outer, len, inner, out);
+        return after_launch("reduce_cols");
+    }
+    StridedGeom g;
+    g.rank = 0;
+    for (int d = 0; d < R; ++d) {
+        if (d == axis) continue;
+        g.sizes[g.rank] = (int64_t)src->shape.sizes[d];
+        g.strides[g.rank] = src->strides.sizes[d];
+        ++g.rank;
+    }
+    g.len = len;
+    g.axis_stride = src->strides.sizes[axis];
+    g.total = total;
+    int64_t blocks = ceil_div(total, kThreads);
+    if (blocks > cap) blocks = cap;
+    reduce_strided<T, SUM, ARG, MIN><<<(int)blocks, kThreads, 0, s>>>(p, g, out);
+    return after_launch("reduce_strided");
+}
+
+template <bool SUM, bool ARG, bool MIN>
+tn_status by_dtype(const tn_tensor_t* src, int axis, Outputs out, cudaStream_t s) {
+    switch (src->dtype) {
+        case TN_INT8: return launch<int8_t, SUM, ARG, MIN>(src, axis, out, s);
+        case TN_INT16: return launch<int16_t, SUM, ARG, MIN>(src, axis, out, s);
+        case TN_INT32: return launch<int32_t, SUM, ARG, MIN>(src, axis, out, s);
+        case TN_INT64: return launch<int64_t, SUM, ARG, MIN>(src, axis, out, s);
+        case TN_FLOAT16: return launch<__half, SUM, ARG, MIN>(src, axis, out, s);
+        case TN_BFLOAT16: return launch<__nv_bfloat16, SUM, ARG, MIN>(src, axis, out, s);
+        case TN_FLOAT32: return launch<float, SUM, ARG, MIN>(src, axis, out, s);
+        case TN_FLOAT64: return launch<double, SUM, ARG, MIN>(src, axis, out, s);
+        default: return fail(TN_UNSUPPORTED_DTYPE, "reduction: dtype %d unsupported", (int)src->dtype);
+    }
+}
+
+tn_status check(const tn_tensor_t* src, const tn_tensor_t* dst, uint8_t axis, bool index_out, bool floats_only) {
+    if (!src || !dst) return fail(TN_ERROR, "null tensor");
+    if (axis >= src->rank) return fail(TN_ERROR, "axis %d out of range for rank %d", (int)axis, (int)src->rank);
+    if (floats_only ? !is_float(src->dtype) : !is_numeric(src->dtype))
+        return fail(TN_UNSUPPORTED_DTYPE, "reduction: dtype %d unsupported", (int)src->dtype);
+    if (index_out ? dst->dtype != TN_INT64 : dst->dtype != src->dtype)
+        return fail(TN_UNSUPPORTED_DTYPE, "reduction: result dtype %d does not fit source dtype %d", (int)dst->dtype,
+                    (int)src->dtype);
+    if (src->environment.kind != TN_DEVICE || dst->environment.kind != TN_DEVICE ||
+        src->environment.resource.device.id != dst->environment.resource.device.id)
+        return fail(TN_INCOMPATIBLE_DEVICES, "operands must live on one device");
+    int64_t expect = 1;
+    for (int d = 0; d < src->rank; ++d)
+        if (d != axis) expect *= (int64_t)src->shape.sizes[d];
+    if ((int64_t)dst->size != expect)
+        return fail(TN_ERROR, "reduction: result holds %zu elements, expected %lld", dst->size, (long long)expect);
+    return use_device_of(dst);
+}
+
+}  // namespace
+}  // namespace tnb
+
+using namespace tnb;
+
+extern "C" {
+
+tn_status tn_argmax(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, uint8_t axis) {
+    TN_TRY(check(src, dst, axis, true, false));
+    return by_dtype<false, true, false>(src, axis, Outputs{nullptr, nullptr, static_cast<int64_t*>(dst->address), 0}, as_cuda(stream));
+}
+
+tn_status tn_argmin(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, uint8_t axis) {
+    TN_TRY(check(src, dst, axis, true, false));
+    return by_dtype<false, true, true>(src, axis, Outputs{nullptr, nullptr, static_cast<int64_t*>(dst->address), 0}, as_cuda(stream));
+}
+
+tn_status tn_argsum(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, uint8_t axis) {
+    TN_TRY(check(src, dst, axis, false, false));
+    return by_dtype<true, false, false>(src, axis, Outputs{dst->address, nullptr, nullptr, 0}, as_cuda(stream));
+}
+
+tn_status tn_argmean(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, uint8_t axis) {
+    TN_TRY(check(src, dst, axis, false, true));  // floats only, src/cpu/argred.cpp:304-315
+    return by_dtype<true, false, false>(src, axis, Outputs{dst->address, nullptr, nullptr, 1}, as_cuda(stream));
+}
+
+tn_status tn_max(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, uint8_t axis) {
+    TN_TRY(check(src, dst, axis, false, false));
+    return by_dtype<false, true, false>(src, axis, Outputs{nullptr, dst->address, nullptr, 0}, as_cuda(stream));
+}
+
+tn_status tn_reduce_stats(const tn_tensor_t* src, tn_tensor_t* max_out, tn_tensor_t* sum_out, tn_tensor_t* argmax_out,
+                          tn_stream_t stream, uint8_t axis) {
+    if (!max_out && !sum_out && !argmax_out) return fail(TN_ERROR, "reduce_stats: no output requested");
+    if (max_out) TN_TRY(check(src, max_out, axis, false, false));
+    if (sum_out) TN_TRY(check(src, sum_out, axis, false, false));
+    if (argmax_out) TN_TRY(check(src, argmax_out, axis, true, false));
+    Outputs out{sum_out ? sum_out->address : nullptr, max_out ? max_out->address : nullptr,
+                argmax_out ? static_cast<int64_t*>(argmax_out->address) : nullptr, 0};
+    return by_dtype<true, true, false>(src, axis, out, as_cuda(stream));
+}
+
+}  // extern "C"

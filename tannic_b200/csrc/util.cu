@@ -1,0 +1,142 @@
+// Strided copy (slice assignment) and tolerance comparison. Replace src/cuda/cpy.cu and
+// src/cuda/val.cu of the reference.
+#include "common.cuh"
+
+namespace tnb {
+namespace {
+
+constexpr int kThreads = 256;
+
+struct PairGeom {
+    int rank;
+    int64_t n;
+    int64_t sizes[TN_MAX_RANK];
+    int64_t sa[TN_MAX_RANK];
+    int64_t sb[TN_MAX_RANK];
+};
+
+__device__ __forceinline__ void decode(const PairGeom& g, int64_t lin, int64_t& oa, int64_t& ob) {
+    oa = ob = 0;
+    for (int d = g.rank - 1; d >= 0; --d) {
+        const int64_t c = lin % g.sizes[d];
+        lin /= g.sizes[d];
+        oa += c * g.sa[d];
+        ob += c * g.sb[d];
+    }
+}
+
+// dst[off_b(i)] = src[off_a(i)] for every logical index i, moving elements as raw words.
+template <typename W>
+__global__ void __launch_bounds__(kThreads) cpy_strided(const W* __restrict__ src, W* __restrict__ dst, PairGeom g) {
+    const int64_t step = (int64_t)gridDim.x * kThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < g.n; i += step) {
+        int64_t oa, ob;
+        decode(g, i, oa, ob);
+        dst[ob] = src[oa];
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) allclose_kernel(const T* __restrict__ a, const T* __restrict__ b, PairGeom g,
+                                                            double rtol, double atol, int* mismatch) {
+    const int64_t step = (int64_t)gridDim.x * kThreads;
+    bool bad = false;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < g.n; i += step) {
+        int64_t oa, ob;
+        decode(g, i, oa, ob);
+        const double x = to_compute<double>(a[oa]), y = to_compute<double>(b[ob]);
+        // a NaN on either side never trips this test, exactly as in src/cuda/val.cu:8-40
+        if (fabs(x - y) > atol + rtol * fabs(y)) bad = true;
+    }
+    if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(mismatch, 1);
+}
+
+// Geometry over `shape_of`'s logical shape; extent-1 dims of either side read offset 0
+// (src/cpu/cpy.cpp:19-43).
+void make_geom(const tn_tensor_t* a, const tn_tensor_t* b, const tn_tensor_t* shape_of, PairGeom& g) {
+    g.rank = shape_of->rank;
+    g.n = 1;
+    for (int d = 0; d < g.rank; ++d) {
+        g.sizes[d] = (int64_t)shape_of->shape.sizes[d];
+        g.n *= g.sizes[d];
+        g.sa[d] = a->shape.sizes[d] == 1 ? 0 : a->strides.sizes[d];
+        g.sb[d] = b->shape.sizes[d] == 1 ? 0 : b->strides.sizes[d];
+    }
+}
+
+int grid_for(int64_t n) {
+    const int64_t cap = (int64_t)sm_count() * 8;
+    int64_t blocks = ceil_div(n, kThreads);
+    if (blocks < 1) blocks = 1;
+    return (int)(blocks < cap ? blocks : cap);
+}
+
+}  // namespace
+}  // namespace tnb
+
+using namespace tnb;
+
+extern "C" {
+
+tn_status tn_cpy(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream) {
+    if (!src || !dst) return fail(TN_ERROR, "null tensor");
+    if (src->dtype != dst->dtype || dtype_bytes(src->dtype) == 0)
+        return fail(TN_UNSUPPORTED_DTYPE, "cpy: dtypes %d -> %d", (int)src->dtype, (int)dst->dtype);
+    if (src->rank != dst->rank) return fail(TN_ERROR, "cpy: ranks %d and %d differ", (int)src->rank, (int)dst->rank);
+    if (src->environment.kind != TN_DEVICE || dst->environment.kind != TN_DEVICE ||
+        src->environment.resource.device.id != dst->environment.resource.device.id)
+        return fail(TN_INCOMPATIBLE_DEVICES, "operands must live on one device");
+    TN_TRY(use_device_of(dst));
+    PairGeom g;
+    make_geom(src, dst, dst, g);
+    if (g.n == 0) return TN_SUCCESS;
+    cudaStream_t s = as_cuda(stream);
+    const int grid = grid_for(g.n);
+    switch (dtype_bytes(src->dtype)) {
+        case 1: cpy_strided<uint8_t><<<grid, kThreads, 0, s>>>(static_cast<const uint8_t*>(src->address), static_cast<uint8_t*>(dst->address), g); break;
+        case 2: cpy_strided<uint16_t><<<grid, kThreads, 0, s>>>(static_cast<const uint16_t*>(src->address), static_cast<uint16_t*>(dst->address), g); break;
+        case 4: cpy_strided<uint32_t><<<grid, kThreads, 0, s>>>(static_cast<const uint32_t*>(src->address), static_cast<uint32_t*>(dst->address), g); break;
+        case 8: cpy_strided<uint64_t><<<grid, kThreads, 0, s>>>(static_cast<const uint64_t*>(src->address), static_cast<uint64_t*>(dst->address), g); break;
+        default: cpy_strided<uint4><<<grid, kThreads, 0, s>>>(static_cast<const uint4*>(src->address), static_cast<uint4*>(dst->address), g); break;
+    }
+    return after_launch("cpy_strided");
+}
+
+tn_status tn_allclose(const tn_tensor_t* a, const tn_tensor_t* b, tn_stream_t stream, double rtol, double atol, int* close) {
+    if (!a || !b || !close) return fail(TN_ERROR, "null argument");
+    if (a->dtype != b->dtype || !is_float(a->dtype))
+        return fail(TN_UNSUPPORTED_DTYPE, "allclose: dtypes %d and %d", (int)a->dtype, (int)b->dtype);
+    if (a->rank != b->rank || a->size != b->size) return fail(TN_ERROR, "allclose: shapes differ");
+    if (a->environment.kind != TN_DEVICE || b->environment.kind != TN_DEVICE ||
+        a->environment.resource.device.id != b->environment.resource.device.id)
+        return fail(TN_INCOMPATIBLE_DEVICES, "operands must live on one device");
+    TN_TRY(use_device_of(a));
+    PairGeom g;
+    make_geom(a, b, a, g);
+    cudaStream_t s = as_cuda(stream);
+    *close = 1;
+    if (g.n == 0) return TN_SUCCESS;
+    int* flag = nullptr;
+    TN_TRY(scratch_alloc(reinterpret_cast<void**>(&flag), sizeof(int), s));
+    cudaError_t err = cudaMemsetAsync(flag, 0, sizeof(int), s);
+    if (err == cudaSuccess) {
+        const int grid = grid_for(g.n);
+        switch (a->dtype) {
+            case TN_FLOAT16: allclose_kernel<__half><<<grid, kThreads, 0, s>>>(static_cast<const __half*>(a->address), static_cast<const __half*>(b->address), g, rtol, atol, flag); break;
+            case TN_BFLOAT16: allclose_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(a->address), static_cast<const __nv_bfloat16*>(b->address), g, rtol, atol, flag); break;
+            case TN_FLOAT32: allclose_kernel<float><<<grid, kThreads, 0, s>>>(static_cast<const float*>(a->address), static_cast<const float*>(b->address), g, rtol, atol, flag); break;
+            default: allclose_kernel<double><<<grid, kThreads, 0, s>>>(static_cast<const double*>(a->address), static_cast<const double*>(b->address), g, rtol, atol, flag); break;
+        }
+        count_launch();
+        err = cudaGetLastError();
+    }
+    int mismatch = 0;
+    if (err == cudaSuccess) err = cudaMemcpyAsync(&mismatch, flag, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+    scratch_free(flag, s);
+    if (err != cudaSuccess) return fail(TN_ERROR, "allclose failed: %s", cudaGetErrorString(err));
+    *close = mismatch ? 0 : 1;
+    return TN_SUCCESS;
+}
+
+}  // extern "C"
