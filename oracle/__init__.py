@@ -1,0 +1,189 @@
+"""TEST INFRASTRUCTURE — Python handles on the parity oracle.
+
+`oracle.port()`  loads oracle/liboracle.so, the C restatement of the reference's algorithms
+                 (tannic_oracle.c);
+`oracle.ref()`   loads oracle/_ref/libtannic_ref.so, the reference's own CPU kernels compiled
+                 from its sources (None when it was never built on this machine).
+
+Only tests/, `__graft_entry__.smoke()` and the CPU-baseline leg of bench.py may import this
+package; the product (tannic_b200) never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import torch
+
+from tannic_b200 import _abi as A
+
+HERE = Path(__file__).resolve().parent
+PORT_PATH = HERE / "liboracle.so"
+REF_PATH = HERE / "_ref" / "libtannic_ref.so"
+
+ACC_STORAGE, ACC_WIDE = 0, 1
+BINARY = {"add": 0, "sub": 1, "mul": 2, "pow": 3}
+UNARY = {"neg": 0, "repack": 1, "log": 2, "exp": 3, "sqrt": 4, "rsqrt": 5, "abs": 6, "sin": 7, "cos": 8, "tan": 9,
+         "sinh": 10, "cosh": 11, "tanh": 12}
+REDUCE = {"argmax": 0, "argmin": 1, "sum": 2, "mean": 3, "max": 4}
+
+_TP = C.POINTER(A.TensorT)
+_port = None
+_ref = None
+
+
+def build(with_reference: bool = True) -> None:
+    """Compile the C restatement (and, where the reference tree exists, oracle/_ref)."""
+    target = "all" if with_reference else str(PORT_PATH)
+    subprocess.run(["make", "-s", "-C", str(HERE), target], check=True)
+
+
+def port() -> C.CDLL:
+    global _port
+    if _port is None:
+        if not PORT_PATH.exists():
+            build(with_reference=False)
+        lib = C.CDLL(str(PORT_PATH))
+        lib.orc_binary.argtypes = [C.c_int, _TP, _TP, _TP]
+        lib.orc_unary.argtypes = [C.c_int, _TP, _TP, C.c_float]
+        lib.orc_scale.argtypes = [_TP, C.POINTER(A.ScalarT), _TP]
+        lib.orc_gemm.argtypes = [_TP, _TP, _TP, C.c_int, C.c_int]
+        lib.orc_conv2d.argtypes = [_TP, _TP, _TP, _TP, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t), C.c_int]
+        lib.orc_reduce.argtypes = [C.c_int, _TP, _TP, C.c_uint8, C.c_int]
+        lib.orc_cpy.argtypes = [_TP, _TP]
+        lib.orc_allclose.argtypes = [_TP, _TP, C.c_double, C.c_double, C.POINTER(C.c_int)]
+        lib.orc_fill.argtypes = [C.c_void_p, C.c_int, C.c_size_t, C.c_uint64, C.c_int, C.c_double, C.c_double]
+        _port = lib
+    return _port
+
+
+def ref():
+    """The compiled reference kernels, or None if oracle/_ref was never built here."""
+    global _ref
+    if _ref is None and REF_PATH.exists():
+        lib = C.CDLL(str(REF_PATH))
+        for n in BINARY:
+            getattr(lib, f"ref_{n}").argtypes = [_TP, _TP, _TP]
+        for n in UNARY:
+            getattr(lib, f"ref_{n}").argtypes = [_TP, _TP] + ([C.c_float] if n == "rsqrt" else [])
+        lib.ref_scale.argtypes = [_TP, C.POINTER(A.ScalarT), _TP]
+        lib.ref_gemm.argtypes = [_TP, _TP, _TP]
+        lib.ref_conv2d.argtypes = [_TP, _TP, _TP, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
+        lib.ref_conv2d_bias.argtypes = [_TP, _TP, _TP, _TP, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]
+        for n in ("argmax", "argmin", "argsum", "argmean"):
+            getattr(lib, f"ref_{n}").argtypes = [_TP, _TP, C.c_uint8]
+        lib.ref_cpy.argtypes = [_TP, _TP]
+        lib.ref_allclose.argtypes = [_TP, _TP, C.c_double, C.c_double]
+        _ref = lib
+    return _ref
+
+
+# ---------------------------------------------------------------------------------------
+# Convenience layer over CPU torch tensors (torch is used as a typed host buffer only).
+
+from tannic_b200.ops import TN_TO_TORCH, TORCH_TO_TN, broadcast_shape, desc, _matmul_dtype  # noqa: E402
+
+
+class OracleError(RuntimeError):
+    def __init__(self, status):
+        super().__init__(A.STATUS_NAMES[status] if 0 <= status < 5 else str(status))
+        self.status = status
+
+
+def _ok(status):
+    if status != A.SUCCESS:
+        raise OracleError(status)
+
+
+def fill(shape, dtype: torch.dtype, seed: int, kind: str = "uniform", lo: float = 0.0, hi: float = 1.0) -> torch.Tensor:
+    """Seeded host tensor: 'uniform' in [lo, hi) (integers: inclusive range), 'normal'(mean=lo, std=hi)."""
+    t = torch.empty(tuple(shape), dtype=dtype)
+    _ok(port().orc_fill(t.data_ptr(), TORCH_TO_TN[dtype], t.numel(), seed, 0 if kind == "uniform" else 1, lo, hi))
+    return t
+
+
+def _empty(shape, tn):
+    return torch.empty(tuple(shape), dtype=TN_TO_TORCH[tn])
+
+
+def binary(name, a, b, out_dtype=None, impl="port"):
+    dt = out_dtype if out_dtype is not None else max(TORCH_TO_TN[a.dtype], TORCH_TO_TN[b.dtype])
+    out = _empty(broadcast_shape(a.shape, b.shape), dt)
+    da, db, dd = desc(a), desc(b), desc(out)
+    if impl == "port":
+        _ok(port().orc_binary(BINARY[name], C.byref(da), C.byref(db), C.byref(dd)))
+    else:
+        _ok(getattr(ref(), f"ref_{name}")(C.byref(da), C.byref(db), C.byref(dd)))
+    return out
+
+
+def unary(name, x, eps=0.0, impl="port"):
+    out = _empty(x.shape, TORCH_TO_TN[x.dtype])
+    dx, dd = desc(x), desc(out)
+    if impl == "port":
+        _ok(port().orc_unary(UNARY[name], C.byref(dx), C.byref(dd), eps))
+    elif name == "rsqrt":
+        _ok(ref().ref_rsqrt(C.byref(dx), C.byref(dd), eps))
+    else:
+        _ok(getattr(ref(), f"ref_{name}")(C.byref(dx), C.byref(dd)))
+    return out
+
+
+def scale(x, value, impl="port"):
+    out = _empty(x.shape, TORCH_TO_TN[x.dtype])
+    holder = torch.tensor([value], dtype=x.dtype)
+    sc = A.ScalarT(holder.data_ptr(), TORCH_TO_TN[x.dtype])
+    dx, dd = desc(x), desc(out)
+    fn = port().orc_scale if impl == "port" else ref().ref_scale
+    _ok(fn(C.byref(dx), C.byref(sc), C.byref(dd)))
+    return out
+
+
+def matmul(a, b, acc=ACC_WIDE, out_dtype=None, wrap_batch_u8=False, impl="port", out=None):
+    batch = broadcast_shape(a.shape[:-2], b.shape[:-2])
+    dt = out_dtype if out_dtype is not None else _matmul_dtype(TORCH_TO_TN[a.dtype], TORCH_TO_TN[b.dtype])
+    if out is None:
+        out = _empty(batch + (a.shape[-2], b.shape[-1]), dt)
+    da, db, dd = desc(a), desc(b), desc(out)
+    if impl == "port":
+        _ok(port().orc_gemm(C.byref(da), C.byref(db), C.byref(dd), acc, int(wrap_batch_u8)))
+    else:
+        _ok(ref().ref_gemm(C.byref(da), C.byref(db), C.byref(dd)))
+    return out
+
+
+def conv2d(x, w, stride=1, padding=0, bias=None, acc=ACC_WIDE, impl="port"):
+    s = (stride, stride) if isinstance(stride, int) else tuple(stride)
+    p = (padding, padding) if isinstance(padding, int) else tuple(padding)
+    ho = (x.shape[2] + 2 * p[0] - w.shape[2]) // s[0] + 1
+    wo = (x.shape[3] + 2 * p[1] - w.shape[3]) // s[1] + 1
+    out = _empty((x.shape[0], w.shape[0], ho, wo), TORCH_TO_TN[x.dtype])
+    pad, strd = (C.c_size_t * 2)(*p), (C.c_size_t * 2)(*s)
+    dx, dw, dd = desc(x), desc(w), desc(out)
+    db = desc(bias) if bias is not None else None
+    if impl == "port":
+        _ok(port().orc_conv2d(C.byref(dx), C.byref(dw), C.byref(db) if db is not None else None, C.byref(dd), pad, strd, acc))
+    elif bias is None:
+        _ok(ref().ref_conv2d(C.byref(dx), C.byref(dw), C.byref(dd), pad, strd))
+    else:
+        _ok(ref().ref_conv2d_bias(C.byref(dx), C.byref(dw), C.byref(db), C.byref(dd), pad, strd))
+    return out
+
+
+def reduce(kind, x, axis=-1, keepdim=False, acc=ACC_WIDE, impl="port"):
+    ax = axis + x.dim() if axis < 0 else axis
+    shape = list(x.shape)
+    if keepdim:
+        shape[ax] = 1
+    else:
+        del shape[ax]
+    dt = A.INT64 if kind in ("argmax", "argmin") else TORCH_TO_TN[x.dtype]
+    out = _empty(shape, dt)
+    dx, dd = desc(x), desc(out)
+    if impl == "port":
+        _ok(port().orc_reduce(REDUCE[kind], C.byref(dx), C.byref(dd), ax, acc))
+    else:
+        name = {"sum": "argsum", "mean": "argmean"}.get(kind, kind)
+        _ok(getattr(ref(), f"ref_{name}")(C.byref(dx), C.byref(dd), ax))
+    return out

@@ -1,0 +1,436 @@
+"""Parity of the CUDA path (through the C ABI) against the oracle on seeded inputs.
+
+Bit-exact for integer dtypes, index results and half add/sub/mul; rtol 1e-2 / atol 1e-2 for
+fp16 / bf16; rtol 1e-4 (atol 1e-5 for sums that cancel) for fp32; 1e-12 for fp64.
+"""
+import pytest
+import torch
+
+import oracle
+from tannic_b200 import _abi as A
+from tannic_b200 import ops as tb
+
+pytestmark = pytest.mark.gpu
+
+INTS = [torch.int8, torch.int16, torch.int32, torch.int64]
+HALVES = [torch.float16, torch.bfloat16]
+FLOATS = HALVES + [torch.float32, torch.float64]
+TOL = {torch.float16: (1e-2, 1e-2), torch.bfloat16: (1e-2, 1e-2), torch.float32: (1e-4, 1e-5), torch.float64: (1e-12, 1e-12)}
+
+
+def dev(t):
+    return t.cuda()
+
+
+def gen(shape, dtype, seed, lo=-4.0, hi=4.0, kind="uniform"):
+    if dtype in INTS:
+        return oracle.fill(shape, dtype, seed, "uniform", -100, 100)
+    return oracle.fill(shape, dtype, seed, kind, lo, hi)
+
+
+def assert_same(got, want):
+    got = got.cpu()
+    assert got.dtype == want.dtype and got.shape == want.shape
+    if got.dtype in INTS:
+        assert torch.equal(got, want)
+    else:
+        assert torch.equal(got.contiguous().view(torch.int16 if got.element_size() == 2 else torch.int32 if got.element_size() == 4 else torch.int64),
+                           want.contiguous().view(torch.int16 if want.element_size() == 2 else torch.int32 if want.element_size() == 4 else torch.int64))
+
+
+def assert_close(got, want, tol=None):
+    got = got.cpu()
+    assert got.dtype == want.dtype and got.shape == want.shape, (got.dtype, want.dtype, got.shape, want.shape)
+    if got.dtype in INTS:
+        assert torch.equal(got, want)
+        return
+    rtol, atol = tol or TOL[got.dtype]
+    g, w = got.double(), want.double()
+    bad = ~(((g - w).abs() <= atol + rtol * w.abs()) | (torch.isnan(g) & torch.isnan(w)) | ((g == w)))
+    assert not bool(bad.any()), f"{int(bad.sum())} of {bad.numel()} outside tolerance; max abs diff {float((g - w).abs()[~torch.isnan(g - w)].max())}"
+
+
+# ---------------------------------------------------------------- elementwise ----------
+
+@pytest.mark.parametrize("op", ["add", "sub", "mul"])
+@pytest.mark.parametrize("dtype", INTS + FLOATS)
+@pytest.mark.parametrize("shapes", [((64, 96), (64, 96)), ((33, 64), (1, 64)), ((33, 64), (33, 1)), ((2, 1, 3), (1, 4, 3)),
+                                    ((5, 7), (7,)), ((1000,), (1,)), ((), ()), ((3, 197), (3, 197))])
+def test_binary_same_dtype_exact(op, dtype, shapes):
+    a, b = gen(shapes[0], dtype, 1), gen(shapes[1], dtype, 2)
+    want = oracle.binary(op, a, b)
+    got = getattr(tb, op)(dev(a), dev(b))
+    assert_same(got, want)
+
+
+@pytest.mark.parametrize("dtype", FLOATS)
+def test_pow(dtype):
+    a, b = gen((40, 64), dtype, 3, 0.1, 3.0), gen((1, 64), dtype, 4, -2.0, 2.0)
+    assert_close(tb.pow(dev(a), dev(b)), oracle.binary("pow", a, b))
+
+
+@pytest.mark.parametrize("pair", [(torch.float16, torch.float32), (torch.float32, torch.bfloat16), (torch.float16, torch.float64),
+                                  (torch.int32, torch.float32), (torch.float64, torch.int32), (torch.int8, torch.int32),
+                                  (torch.int64, torch.int16), (torch.float32, torch.float64)])
+@pytest.mark.parametrize("op", ["add", "mul", "sub"])
+def test_binary_mixed_dtypes(pair, op):
+    a, b = gen((9, 1, 11), pair[0], 5), gen((6, 11), pair[1], 6)
+    want = oracle.binary(op, a, b)
+    got = getattr(tb, op)(dev(a), dev(b))
+    if want.dtype in INTS:
+        assert_same(got, want)
+    else:
+        assert_close(got, want)
+
+
+def test_binary_half_with_int_writes_result_dtype():
+    """The reference's (float16, int32) entry writes float32 into a float16-sized buffer
+    (src/cpu/ops-binary.cpp:199-206); the device path writes exactly dst->dtype."""
+    a, b = gen((8, 8), torch.float16, 7), oracle.fill((8, 8), torch.int32, 8, "uniform", -20, 20)
+    got = tb.add(dev(a), dev(b))
+    assert got.dtype == torch.float16
+    assert_close(got, (a.float() + b.float()).to(torch.float16))
+
+
+@pytest.mark.parametrize("pair", [(torch.float16, torch.bfloat16), (torch.float32, torch.int8), (torch.float64, torch.int64)])
+def test_binary_unsupported_pairs(pair):
+    a, b = gen((4,), pair[0], 9), gen((4,), pair[1], 10)
+    with pytest.raises(A.TannicError) as e:
+        tb.add(dev(a), dev(b))
+    assert e.value.status == A.UNSUPPORTED_DTYPE
+    with pytest.raises(A.TannicError) as e:
+        tb.pow(dev(gen((4,), torch.int32, 1)), dev(gen((4,), torch.int32, 2)))
+    assert e.value.status == A.UNSUPPORTED_DTYPE
+
+
+def test_binary_strided_views():
+    a0, b0 = gen((48, 40), torch.float32, 11), gen((40, 96), torch.float32, 12)
+    want = oracle.binary("add", a0.t(), b0[:, ::2])
+    assert_same(tb.add(dev(a0).t(), dev(b0)[:, ::2]), want)
+
+
+@pytest.mark.parametrize("name", ["neg", "repack", "log", "exp", "sqrt", "rsqrt", "abs", "sin", "cos", "tan", "sinh", "cosh", "tanh"])
+@pytest.mark.parametrize("dtype", FLOATS)
+@pytest.mark.parametrize("shape", [(64, 128), (3, 197), (1,), ()])
+def test_unary(name, dtype, shape):
+    lo, hi = (0.1, 4.0) if name in ("log", "sqrt", "rsqrt") else (-3.0, 3.0)
+    x = gen(shape, dtype, 13, lo, hi)
+    want = oracle.unary(name, x, eps=1e-5)
+    got = tb.rsqrt(dev(x), 1e-5) if name == "rsqrt" else getattr(tb, name)(dev(x))
+    if name in ("neg", "repack", "abs"):
+        assert_same(got, want)
+    else:
+        assert_close(got, want)
+
+
+@pytest.mark.parametrize("name,dtype", [("neg", torch.int8), ("neg", torch.int64), ("repack", torch.int16), ("abs", torch.int32), ("abs", torch.int64)])
+def test_unary_ints(name, dtype):
+    x = gen((17, 33), dtype, 14)
+    assert_same(getattr(tb, name)(dev(x)), oracle.unary(name, x))
+
+
+def test_unary_rejects_integer_log():
+    with pytest.raises(A.TannicError) as e:
+        tb.log(dev(gen((4,), torch.int32, 1)))
+    assert e.value.status == A.UNSUPPORTED_DTYPE
+
+
+def test_unary_strided_source():
+    x = gen((70, 40), torch.float16, 15, 0.1, 4.0)
+    assert_close(tb.log(dev(x).t()), oracle.unary("log", x.t()))
+    assert_same(tb.repack(dev(x).t()), oracle.unary("repack", x.t()))
+    assert_same(tb.repack(dev(x)[::2, 1::3]), oracle.unary("repack", x[::2, 1::3]))
+
+
+@pytest.mark.parametrize("dtype,value", [(torch.int32, 3), (torch.int8, -7), (torch.float16, 0.125), (torch.bfloat16, 0.125), (torch.float32, 1.7), (torch.float64, -2.5)])
+def test_scale(dtype, value):
+    x = gen((31, 64), dtype, 16)
+    assert_same(tb.scale(dev(x), value), oracle.scale(x, value))
+
+
+def _program_oracle(x, y):
+    t0 = oracle.unary("log", x)
+    t1 = oracle.binary("mul", y, y)
+    t2 = oracle.binary("add", t0, t1)
+    t3 = oracle.unary("exp", x)
+    return oracle.binary("sub", t2, t3)
+
+
+CFG2_NODES = [(A.OP_LOG, 0, 0), (A.OP_MUL, 1, 1), (A.OP_ADD, 4, 5), (A.OP_EXP, 0, 0), (A.OP_SUB, 6, 7)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shapes", [((96, 256), (1, 256)), ((96, 256), (96, 256)), ((96, 256), (96, 1)), ((5, 197), (1, 197)), ((4, 3, 8), (3, 1))])
+def test_fused_program_matches_node_chain(dtype, shapes):
+    """Z = log(X) + Y*Y - exp(X) in one kernel == the reference's five-node chain, node by node
+    rounded to the storage dtype."""
+    x, y = gen(shapes[0], dtype, 17, 0.1, 4.0), gen(shapes[1], dtype, 18, -2.0, 2.0)
+    got = tb.program([dev(x), dev(y)], CFG2_NODES)
+    assert_close(got, _program_oracle(x, y))
+    # and the unfused device chain agrees with the same oracle
+    dx, dy = dev(x), dev(y)
+    chain = tb.sub(tb.add(tb.log(dx), tb.mul(dy, dy)), tb.exp(dx))
+    assert_close(chain, _program_oracle(x, y))
+
+
+def test_fused_program_dynamic_and_other_static_shapes():
+    x, w, b = gen((64, 128), torch.float32, 19), gen((64, 128), torch.float32, 20), gen((128,), torch.float32, 21)
+    want = oracle.binary("add", oracle.binary("mul", x, w), b)
+    assert_same(tb.program([dev(x), dev(w), dev(b)], [(A.OP_MUL, 0, 1), (A.OP_ADD, 4, 2)]), want)
+    # a program that is not in the compiled set runs on the interpreter
+    want = oracle.unary("tanh", oracle.binary("sub", oracle.unary("abs", x), w))
+    got = tb.program([dev(x), dev(w)], [(A.OP_ABS, 0, 0), (A.OP_SUB, 4, 1), (A.OP_TANH, 5, 5)])
+    assert_close(got, want)
+    got = tb.program([dev(x), dev(w)], [(A.OP_SCALE, 0, 0, 0.5), (A.OP_RSQRT, 1, 1, 9.0), (A.OP_MUL, 4, 5)])
+    want = oracle.binary("mul", oracle.scale(x, 0.5), oracle.unary("rsqrt", w, eps=9.0))
+    assert_close(got, want)
+
+
+def test_fused_program_rejects_bad_programs():
+    x = dev(gen((8,), torch.float32, 1))
+    with pytest.raises(A.TannicError):
+        tb.program([x], [(A.OP_ADD, 0, 5)])  # reads a value defined later
+    with pytest.raises(A.TannicError):
+        tb.program([x], [(99, 0, 0)])
+
+
+# ---------------------------------------------------------------- reductions -----------
+
+@pytest.mark.parametrize("kind", ["argmax", "argmin", "sum", "mean", "max"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.float64, torch.int32, torch.int8])
+@pytest.mark.parametrize("shape,axis", [((6, 197), -1), ((33, 7, 5), 1), ((33, 7, 5), 0), ((4, 3, 9000), -1), ((5, 64), -1), ((7,), 0), ((3, 1, 4), 1)])
+def test_reductions(kind, dtype, shape, axis):
+    if kind == "mean" and dtype in INTS:
+        pytest.skip("mean is float-only in the reference")
+    x = gen(shape, dtype, 22, -2.0, 2.0)
+    want = oracle.reduce(kind, x, axis, acc=oracle.ACC_WIDE)
+    got = getattr(tb, kind)(dev(x), axis)
+    if kind in ("argmax", "argmin", "max") or dtype in INTS:
+        assert_same(got, want)
+    else:
+        assert_close(got, want)
+
+
+@pytest.mark.parametrize("kind", ["argmax", "sum", "argmin"])
+def test_reductions_strided_views(kind):
+    x = gen((12, 9, 10), torch.float32, 23)
+    for view in (lambda t: t.transpose(0, 2), lambda t: t[:, ::2, 1:], lambda t: t.permute(1, 2, 0)):
+        for axis in (0, 1, 2):
+            want = oracle.reduce(kind, view(x), axis, acc=oracle.ACC_WIDE)
+            got = getattr(tb, kind)(view(dev(x)), axis)
+            if kind == "sum":
+                assert_close(got, want)
+            else:
+                assert_same(got, want)
+
+
+def test_argmax_ties_nan_infinities():
+    inf, nan = float("inf"), float("nan")
+    rows = [[1, 5, 5], [7, 7, 2], [-inf, -inf, -inf], [nan, -inf, 3], [nan, nan, nan], [nan, -inf, -inf], [inf, inf, 1]]
+    for dtype in (torch.float32, torch.float16, torch.bfloat16):
+        x = torch.tensor(rows, dtype=dtype)
+        assert tb.argmax(dev(x), -1).cpu().tolist() == oracle.reduce("argmax", x, -1).tolist() == [1, 0, 0, 2, 0, 0, 0]
+        assert tb.argmin(dev(x), -1).cpu().tolist() == oracle.reduce("argmin", x, -1).tolist()
+        assert tb.argmax(dev(x), 0).cpu().tolist() == oracle.reduce("argmax", x, 0).tolist()
+    # long rows with the maximum repeated across lanes / segments
+    x = torch.zeros(3, 5000, dtype=torch.bfloat16)
+    x[0, 4999] = 1
+    x[0, 77] = 1
+    x[1, 4096] = 2
+    x[1, 4097] = 2
+    assert tb.argmax(dev(x), -1).cpu().tolist() == [77, 4096, 0]
+
+
+def test_reduce_keepdim_and_stats():
+    x = gen((8, 12, 197), torch.bfloat16, 24, -2.0, 2.0)
+    assert tb.sum(dev(x), -1, keepdim=True).shape == (8, 12, 1)
+    mx, sm, am = tb.reduce_stats(dev(x), -1)
+    assert_same(am, oracle.reduce("argmax", x, -1))
+    assert_same(mx, oracle.reduce("max", x, -1))
+    assert_close(sm, oracle.reduce("sum", x, -1, acc=oracle.ACC_WIDE))
+
+
+def test_reduce_split_path_for_few_long_rows():
+    x = gen((2, 1 << 20), torch.float32, 25, -1.0, 1.0)
+    assert_close(tb.sum(dev(x), -1), oracle.reduce("sum", x, -1, acc=oracle.ACC_WIDE))
+    assert_same(tb.argmax(dev(x), -1), oracle.reduce("argmax", x, -1))
+    assert_close(tb.mean(dev(x), -1), oracle.reduce("mean", x, -1, acc=oracle.ACC_WIDE))
+
+
+# ---------------------------------------------------------------- matmul ---------------
+
+@pytest.mark.parametrize("pair", [(torch.float32, torch.float32), (torch.float64, torch.float64), (torch.int8, torch.int8),
+                                  (torch.int32, torch.int32), (torch.int16, torch.int64), (torch.int32, torch.float32),
+                                  (torch.bfloat16, torch.float32), (torch.float16, torch.float64)])
+def test_matmul_simt_pairs(pair):
+    a, b = gen((3, 37, 50), pair[0], 26, -1, 1), gen((3, 50, 29), pair[1], 27, -1, 1)
+    want = oracle.matmul(a, b, acc=oracle.ACC_WIDE)
+    got = tb.matmul(dev(a), dev(b))
+    if want.dtype in INTS:
+        assert_same(got, want)
+    else:
+        assert_close(got, want)
+
+
+def test_matmul_config1_float32():
+    """BASELINE config 1: float32 [512,1024] x [1024,512], uniform[-1,1], seed 0."""
+    a, b = oracle.fill((512, 1024), torch.float32, 0, "uniform", -1, 1), oracle.fill((1024, 512), torch.float32, 1000, "uniform", -1, 1)
+    want = a.double() @ b.double()
+    got = tb.matmul(dev(a), dev(b)).cpu()
+    # summation order differs from the reference loop: arbitrate with the float64 product
+    assert torch.allclose(got.double(), want, rtol=1e-4, atol=1e-4)
+    sub = oracle.matmul(a[:16], b, acc=oracle.ACC_STORAGE)
+    assert torch.allclose(got[:16], sub, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", HALVES)
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (200, 300, 136), (197, 197, 64), (1, 8, 8), (130, 72, 1000), (384, 512, 4096)])
+def test_matmul_tensor_core_k_major_b(dtype, m, n, k):
+    """matmul(X, W.transpose(-1,-2)) with W [N, K]: both operands K-major."""
+    a, w = gen((m, k), dtype, 28, -1, 1), gen((n, k), dtype, 29, -1, 1)
+    want = oracle.matmul(a, w.t(), acc=oracle.ACC_WIDE)
+    got = tb.matmul(dev(a), dev(w).t())
+    assert_close(got, want)
+    assert tb.device_errors() == 0
+
+
+@pytest.mark.parametrize("dtype", HALVES)
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (100, 264, 200), (64, 3136, 256), (130, 8, 72)])
+def test_matmul_tensor_core_n_major_b(dtype, m, n, k):
+    """plain matmul(A, B) with B [K, N] row-major."""
+    a, b = gen((m, k), dtype, 30, -1, 1), gen((k, n), dtype, 31, -1, 1)
+    assert_close(tb.matmul(dev(a), dev(b)), oracle.matmul(a, b, acc=oracle.ACC_WIDE))
+    assert tb.device_errors() == 0
+
+
+def test_matmul_batched_broadcast_and_more_than_256_batches():
+    """ViT-shaped scores: Q, K [b, 12, 197, 64]; more than 256 batches (the reference wraps there)."""
+    q, k = gen((24, 12, 197, 64), torch.bfloat16, 32, -1, 1), gen((24, 12, 197, 64), torch.bfloat16, 33, -1, 1)
+    got = tb.matmul(dev(q), dev(k).transpose(-1, -2), scale_by=0.125)
+    assert got.shape == (24, 12, 197, 197)
+    for i in (0, 11, 23):
+        s = oracle.matmul(q[i], k[i].transpose(-1, -2), acc=oracle.ACC_WIDE)
+        assert_close(got[i], oracle.scale(s, 0.125))
+    # rank-4 x rank-2 broadcast (tests/cpu/test-matmul.cpp: Rank4Rank2StridedTransposed)
+    x, w = gen((2, 3, 40, 64), torch.float16, 34, -1, 1), gen((48, 64), torch.float16, 35, -1, 1)
+    assert_close(tb.matmul(dev(x), dev(w).t()), oracle.matmul(x, w.t(), acc=oracle.ACC_WIDE))
+    # batch-broadcast first operand: falls back to the SIMT path
+    a, b = gen((1, 40, 64), torch.float16, 36, -1, 1), gen((5, 64, 24), torch.float16, 37, -1, 1)
+    assert_close(tb.matmul(dev(a), dev(b)), oracle.matmul(a, b, acc=oracle.ACC_WIDE))
+    assert tb.device_errors() == 0
+
+
+def test_matmul_half_to_float32_result():
+    a, w = gen((130, 136), torch.bfloat16, 38, -1, 1), gen((72, 136), torch.bfloat16, 39, -1, 1)
+    got = tb.matmul(dev(a), dev(w).t(), out_dtype=A.FLOAT32)
+    want = oracle.matmul(a, w.t(), acc=oracle.ACC_WIDE, out_dtype=A.FLOAT32)
+    assert_close(got, want, tol=(1e-4, 1e-4))
+
+
+def test_matmul_errors():
+    a, b = dev(gen((4, 5), torch.float16, 1)), dev(gen((5, 3), torch.bfloat16, 2))
+    with pytest.raises(A.TannicError) as e:
+        tb.matmul(a, b, out_dtype=A.FLOAT16)
+    assert e.value.status == A.UNSUPPORTED_DTYPE
+
+
+# ---------------------------------------------------------------- conv2d ---------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.float64, torch.int32])
+@pytest.mark.parametrize("stride,padding", [(1, 0), (1, 1), (2, 1), ((2, 1), (0, 2))])
+def test_conv2d_direct(dtype, stride, padding):
+    x, w = gen((2, 5, 9, 8), dtype, 40, -1, 1), gen((6, 5, 3, 2), dtype, 41, -1, 1)
+    bias = gen((6,), dtype, 42, -1, 1)
+    want = oracle.conv2d(x, w, stride, padding, acc=oracle.ACC_WIDE)
+    got = tb.convolve2D(dev(x), dev(w), stride, padding)
+    if dtype in INTS:
+        assert_same(got, want)
+    else:
+        assert_close(got, want)
+    wantb = oracle.conv2d(x, w, stride, padding, bias=bias, acc=oracle.ACC_WIDE)
+    gotb = tb.convolve2D(dev(x), dev(w), stride, padding, bias=dev(bias))
+    assert_same(gotb, wantb) if dtype in INTS else assert_close(gotb, wantb)
+
+
+@pytest.mark.parametrize("dtype", HALVES)
+def test_conv2d_1x1_tensor_core(dtype):
+    x, w = gen((3, 64, 12, 12), dtype, 43, -1, 1), gen((40, 64, 1, 1), dtype, 44, -1, 1)
+    bias = gen((40,), dtype, 45, -1, 1)
+    assert_close(tb.convolve2D(dev(x), dev(w), 1, 0), oracle.conv2d(x, w, 1, 0, acc=oracle.ACC_WIDE))
+    assert_close(tb.convolve2D(dev(x), dev(w), 1, 0, bias=dev(bias)), oracle.conv2d(x, w, 1, 0, bias=bias, acc=oracle.ACC_WIDE))
+    assert tb.device_errors() == 0
+
+
+def test_conv2d_errors():
+    x, w = dev(gen((1, 3, 5, 5), torch.float32, 1)), dev(gen((2, 4, 3, 3), torch.float32, 2))
+    y = torch.empty(1, 2, 3, 3, device="cuda")
+    import ctypes as C
+    dx, dw, dy = tb.desc(x), tb.desc(w), tb.desc(y)
+    pad, strd = (C.c_size_t * 2)(0, 0), (C.c_size_t * 2)(1, 1)
+    assert A.lib().tn_conv2d(C.byref(dx), C.byref(dw), C.byref(dy), tb.current_stream(x), pad, strd) == A.ERROR
+    w16 = dev(gen((2, 3, 3, 3), torch.float16, 2))
+    dw16 = tb.desc(w16)
+    assert A.lib().tn_conv2d(C.byref(dx), C.byref(dw16), C.byref(dy), tb.current_stream(x), pad, strd) == A.UNSUPPORTED_DTYPE
+
+
+# ---------------------------------------------------------------- runtime / utilities ---
+
+def test_cpy_and_allclose():
+    x = gen((20, 30), torch.float32, 46)
+    dst = torch.zeros(30, 20, device="cuda")
+    tb.cpy(dev(x).t(), dst)
+    assert torch.equal(dst.cpu(), x.t().contiguous())
+    dx = dev(x)
+    assert tb.allclose(dx, dx.clone())
+    y = dx.clone()
+    y[3, 4] += 1.0
+    assert not tb.allclose(dx, y)
+    assert tb.allclose(dx, y, rtol=0.0, atol=2.0)
+
+
+def test_allocator_streams_and_copies():
+    import ctypes as C
+    lib = A.lib()
+    n = C.c_int(0)
+    A.check(lib.tn_device_count(C.byref(n)))
+    assert n.value >= 1
+    d = A.DeviceT(0)
+    ptrs = []
+    for _ in range(5):  # tests/cuda/test-cuda-allocations.cpp: five allocations, then frees
+        p = C.c_void_p()
+        A.check(lib.tn_allocate(C.byref(d), 1 << 20, C.byref(p)))
+        assert p.value
+        ptrs.append(p)
+    host = torch.arange(1 << 18, dtype=torch.int32)
+    A.check(lib.tn_copy_from_host(C.byref(d), host.data_ptr(), ptrs[0], host.numel() * 4))
+    back = torch.zeros_like(host)
+    A.check(lib.tn_copy_to_host(C.byref(d), ptrs[0], back.data_ptr(), host.numel() * 4))
+    assert torch.equal(host, back)
+    eq = C.c_int(0)
+    A.check(lib.tn_compare_from_host(C.byref(d), host.data_ptr(), ptrs[0], host.numel() * 4, C.byref(eq)))
+    assert eq.value == 1
+    for p in ptrs:
+        A.check(lib.tn_deallocate(C.byref(d), p))
+    s1, s2 = A.StreamT(), A.StreamT()
+    A.check(lib.tn_stream_pop(C.byref(d), C.byref(s1)))
+    A.check(lib.tn_stream_put(C.byref(d), s1))
+    A.check(lib.tn_stream_pop(C.byref(d), C.byref(s2)))
+    assert s1.address == s2.address and s1.address != 0  # LIFO: the same stream comes back
+    A.check(lib.tn_stream_put(C.byref(d), s2))
+    bad = A.DeviceT(99)
+    p = C.c_void_p()
+    assert lib.tn_allocate(C.byref(bad), 16, C.byref(p)) == A.ERROR
+
+
+def test_host_tensor_is_rejected_without_fallback():
+    a = gen((4,), torch.float32, 1)
+    with pytest.raises(A.TannicError) as e:
+        _add_host(a)
+    assert e.value.status == A.INCOMPATIBLE_DEVICES
+
+
+def _add_host(a):
+    import ctypes as C
+    out = torch.empty_like(a)
+    da, dd = tb.desc(a), tb.desc(out)
+    A.check(A.lib().tn_add(C.byref(da), C.byref(da), C.byref(dd), A.StreamT(0)))
