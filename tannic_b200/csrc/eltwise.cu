@@ -28,10 +28,20 @@ struct Imm {
 template <int OP, bool FAST, typename C>
 __device__ __forceinline__ C apply_op(C a, C b, Imm imm) {
     if constexpr (std::is_floating_point<C>::value) {
-        if constexpr (OP == TN_OP_ADD) return a + b;
-        else if constexpr (OP == TN_OP_SUB) return a - b;
-        else if constexpr (OP == TN_OP_MUL) return a * b;
-        else if constexpr (OP == TN_OP_SCALE) return a * static_cast<C>(imm.f);
+        // Every node rounds on its own: the _rn intrinsics are never contracted into an FMA
+        // with a neighbouring node of a fused program.
+        if constexpr (std::is_same<C, float>::value) {
+            if constexpr (OP == TN_OP_ADD) return __fadd_rn(a, b);
+            else if constexpr (OP == TN_OP_SUB) return __fsub_rn(a, b);
+            else if constexpr (OP == TN_OP_MUL) return __fmul_rn(a, b);
+            else if constexpr (OP == TN_OP_SCALE) return __fmul_rn(a, static_cast<float>(imm.f));
+        } else {
+            if constexpr (OP == TN_OP_ADD) return __dadd_rn(a, b);
+            else if constexpr (OP == TN_OP_SUB) return __dsub_rn(a, b);
+            else if constexpr (OP == TN_OP_MUL) return __dmul_rn(a, b);
+            else if constexpr (OP == TN_OP_SCALE) return __dmul_rn(a, imm.f);
+        }
+        if constexpr (OP == TN_OP_ADD || OP == TN_OP_SUB || OP == TN_OP_MUL || OP == TN_OP_SCALE) return a;
         else if constexpr (OP == TN_OP_NEG) return -a;
         else if constexpr (OP == TN_OP_ABS) return fabs(a);
         else if constexpr (std::is_same<C, float>::value) {
