@@ -253,6 +253,18 @@ tn_status tn_max(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, u
 tn_status tn_reduce_stats(const tn_tensor_t* src, tn_tensor_t* max_out, tn_tensor_t* sum_out,
                           tn_tensor_t* argmax_out, tn_stream_t stream, uint8_t axis);
 
+/* No counterpart in the reference. Sum along the last axis of a dense tensor, like tn_argsum,
+ * for callers that may not allocate device memory when they call in (a server whose HBM is
+ * fully budgeted at start-up; a path that cannot afford an allocator's locks and implicit
+ * synchronisation). The partial sums of its two kernels live in a 192 KiB region that is part of
+ * the library image on every GPU, so no cudaMalloc / cudaMallocAsync / cudaFree is ever issued.
+ * Refused with TN_ERROR: a source that is not dense row-major, an axis other than the last, more
+ * than 8192 rows (192 KiB / 24 B per partial). The first call on a device resolves the region's
+ * address and should be made outside stream capture. All calls on a device share the region:
+ * kernels of two calls that overlap on the GPU race on it, so keep such calls ordered. */
+tn_status tn_argsum_fixed_scratch(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream,
+                                  uint8_t axis);
+
 /* ------------------------------------------------------------------ utilities -------- */
 
 /* reference: cuda::cpy, src/cuda/cpy.cu:55-69 — strided -> strided copy (slice assignment). */

@@ -114,6 +114,7 @@ PROTOTYPES = {
     "tn_conv2d": [_TP, _TP, _TP, StreamT, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)],
     "tn_conv2d_bias": [_TP, _TP, _TP, _TP, StreamT, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)],
     "tn_reduce_stats": [_TP, _TP, _TP, _TP, StreamT, C.c_uint8],
+    "tn_argsum_fixed_scratch": [_TP, _TP, StreamT, C.c_uint8],
     "tn_cpy": [_TP, _TP, StreamT],
     "tn_allclose": [_TP, _TP, StreamT, C.c_double, C.c_double, C.POINTER(C.c_int)],
     "tn_device_errors": [C.POINTER(C.c_uint)],

@@ -16,6 +16,7 @@
 
 #include <cfloat>
 #include <climits>
+#include <mutex>
 
 namespace tnb {
 namespace {
@@ -403,6 +404,58 @@ tn_status check(const tn_tensor_t* src, const tn_tensor_t* dst, uint8_t axis, bo
     return use_device_of(dst);
 }
 
+// ------------------------------------------------------------------ fixed scratch ------
+// Scratch for tn_argsum_fixed_scratch: a region that is part of the loaded module instead of
+// coming from an allocator. Every GPU that loads the library carries these 192 KiB until the
+// process exits. Host code must not hand `g_fixed_scratch` itself to a kernel (on the host the
+// name is only a handle for the symbol); its device address is looked up once per device below.
+constexpr size_t kFixedScratchBytes = 192 * 1024;
+constexpr int kMaxDevices = 64;
+static __device__ __align__(256) unsigned char g_fixed_scratch[kFixedScratchBytes];
+
+std::mutex g_fixed_mutex;
+void* g_fixed_address[kMaxDevices] = {nullptr};
+
+// Device address of the scratch region on `device`, which must be the current device.
+tn_status fixed_scratch_address(int device, void** out) {
+    if (device < 0 || device >= kMaxDevices) return fail(TN_ERROR, "device id %d is beyond the %d this entry point tracks", device, kMaxDevices);
+    std::lock_guard<std::mutex> lock(g_fixed_mutex);
+    if (g_fixed_address[device] == nullptr) {
+        void* ptr = nullptr;
+        cudaError_t err = cudaGetSymbolAddress(&ptr, g_fixed_scratch);
+        if (err != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();
+            return fail(TN_ERROR, "cudaGetSymbolAddress(fixed scratch) failed on device %d: %s", device, cudaGetErrorString(err));
+        }
+        g_fixed_address[device] = ptr;
+    }
+    *out = g_fixed_address[device];
+    return TN_SUCCESS;
+}
+
+template <typename T>
+tn_status launch_sum_fixed(const T* p, int64_t rows, int64_t len, Outputs out, void* scratch, cudaStream_t s) {
+    const size_t capacity = kFixedScratchBytes / sizeof(Partial<T>);
+    if ((size_t)rows > capacity)
+        return fail(TN_ERROR, "argsum_fixed_scratch: %lld rows need more than the %zu-byte fixed scratch region (at most %zu rows of this dtype)",
+                    (long long)rows, kFixedScratchBytes, capacity);
+    const int64_t row_bytes = len * (int64_t)sizeof(T);
+    int64_t splits = ceil_div((int64_t)sm_count() * 4, rows);
+    const int64_t by_length = ceil_div(row_bytes, int64_t(64) << 10);
+    if (splits > by_length) splits = by_length;
+    if (splits > (int64_t)(capacity / (size_t)rows)) splits = (int64_t)(capacity / (size_t)rows);
+    if (splits > 1024) splits = 1024;
+    if (splits < 1) splits = 1;
+    if (rows > 65535) return fail(TN_ERROR, "argsum_fixed_scratch: %lld rows exceed the launch limit of 65535", (long long)rows);
+    Partial<T>* partials = static_cast<Partial<T>*>(scratch);
+    // stage 1 writes every (row, segment) slot that stage 2 reads, so nothing left in the region
+    // by an earlier call is ever consumed and no clearing pass is needed
+    reduce_split_partial<T, true, false, false><<<dim3((unsigned)splits, (unsigned)rows), kThreads, 0, s>>>(p, len, (int)splits, partials);
+    TN_TRY(after_launch("reduce_split_partial (fixed scratch)"));
+    reduce_split_final<T, true, false, false><<<(unsigned)rows, 32, 0, s>>>(p, rows, len, (int)splits, partials, out);
+    return after_launch("reduce_split_final (fixed scratch)");
+}
+
 }  // namespace
 }  // namespace tnb
 
@@ -444,6 +497,57 @@ tn_status tn_reduce_stats(const tn_tensor_t* src, tn_tensor_t* max_out, tn_tenso
     Outputs out{sum_out ? sum_out->address : nullptr, max_out ? max_out->address : nullptr,
                 argmax_out ? static_cast<int64_t*>(argmax_out->address) : nullptr, 0};
     return by_dtype<true, true, false>(src, axis, out, as_cuda(stream));
+}
+
+// Sum along the LAST axis of a dense tensor with the two-kernel split reduction, taking its
+// partial-sum workspace from a fixed region built into the library instead of from an allocator.
+//
+// Who needs this: hosts that are not allowed to allocate device memory at the point where they
+// call in. Typical cases are a serving process that sized every device buffer at start-up and
+// has nothing left for (or forbids) later driver or pool allocations, and callers on a path
+// where the locking and implicit synchronisation of an allocation call are unacceptable.
+// tn_argsum may take scratch from the stream-ordered pool; this entry point never calls
+// cudaMalloc, cudaMallocAsync, cudaFree or any other allocating routine.
+//
+// Limits and rules:
+//   - the workspace is 192 KiB per GPU, resident from library load to process exit;
+//   - the source must be dense row-major and `axis` its last axis; at most
+//     192 KiB / 24 B = 8192 rows (fewer segments per row are used as the row count grows) and
+//     at most 65535 rows per call; anything larger is refused with TN_ERROR and a message;
+//   - the first call on each device looks the region's device address up
+//     (cudaGetSymbolAddress, with that device current) and remembers it; make that first call
+//     outside any stream capture;
+//   - all calls on a device share the one region and it keeps whatever the previous call left
+//     there. Each call overwrites every slot it later reads, so stale contents are harmless,
+//     but two calls whose kernels overlap on the GPU (different streams, no ordering) race on
+//     it: order them on one stream or with events.
+tn_status tn_argsum_fixed_scratch(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, uint8_t axis) {
+    TN_TRY(check(src, dst, axis, false, false));
+    if (axis != src->rank - 1) return fail(TN_ERROR, "argsum_fixed_scratch: axis %d is not the last axis of a rank-%d tensor", (int)axis, (int)src->rank);
+    int64_t expect = 1;
+    for (int d = src->rank - 1; d >= 0; --d) {
+        const int64_t sz = (int64_t)src->shape.sizes[d];
+        if (sz != 1 && src->strides.sizes[d] != expect) return fail(TN_ERROR, "argsum_fixed_scratch: the source must be dense row-major");
+        expect *= sz;
+    }
+    const int64_t len = (int64_t)src->shape.sizes[axis];
+    const int64_t rows = len ? expect / len : 0;
+    if (rows == 0) return TN_SUCCESS;
+    void* scratch = nullptr;
+    TN_TRY(fixed_scratch_address(dst->environment.resource.device.id, &scratch));
+    const Outputs out{dst->address, nullptr, nullptr, 0};
+    cudaStream_t s = as_cuda(stream);
+    switch (src->dtype) {
+        case TN_INT8: return launch_sum_fixed(static_cast<const int8_t*>(src->address), rows, len, out, scratch, s);
+        case TN_INT16: return launch_sum_fixed(static_cast<const int16_t*>(src->address), rows, len, out, scratch, s);
+        case TN_INT32: return launch_sum_fixed(static_cast<const int32_t*>(src->address), rows, len, out, scratch, s);
+        case TN_INT64: return launch_sum_fixed(static_cast<const int64_t*>(src->address), rows, len, out, scratch, s);
+        case TN_FLOAT16: return launch_sum_fixed(static_cast<const __half*>(src->address), rows, len, out, scratch, s);
+        case TN_BFLOAT16: return launch_sum_fixed(static_cast<const __nv_bfloat16*>(src->address), rows, len, out, scratch, s);
+        case TN_FLOAT32: return launch_sum_fixed(static_cast<const float*>(src->address), rows, len, out, scratch, s);
+        case TN_FLOAT64: return launch_sum_fixed(static_cast<const double*>(src->address), rows, len, out, scratch, s);
+        default: return fail(TN_UNSUPPORTED_DTYPE, "argsum_fixed_scratch: dtype %d unsupported", (int)src->dtype);
+    }
 }
 
 }  // extern "C"
