@@ -12,6 +12,7 @@
 #include "common.cuh"
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 namespace tnb {
@@ -177,47 +178,41 @@ __global__ void __launch_bounds__(kThreads) ew_flat(const T* __restrict__ a, con
 }
 
 // ------------------------------------------------------------------ ew_rows -----------
-// dst is [rows, cols] dense. Operand X contributes X[r * x_rs + c * x_in] with x_in in {0, 1}.
-// A thread owns one 16-byte column slot and walks down the rows (blockIdx.y strided), so an
-// operand that does not vary with the row (row-broadcast) is loaded once and kept in registers.
+// dst is [rows, cols] dense. A vector operand X contributes the 16 bytes at X + r * x_rs + c
+// (x_rs == 0 for a row-broadcast operand: the same vector every row, served by L1); a SCALAR
+// operand contributes X[r * x_rs] to the whole row (column-broadcast). A thread owns one column
+// slot and walks down the rows, UNROLL adjacent rows at a time, with every load of the group
+// issued before the first use. The load path has no data-dependent branch: operand kinds are
+// template parameters, so the compiler keeps all loads of a group in flight together.
 struct RowsGeom {
     int64_t rows, cols;
     int64_t a_rs, b_rs;
-    int a_in, b_in;
 };
 
-template <typename T, int OP>
+template <typename T, int OP, bool A_SCALAR, bool B_SCALAR>
 __global__ void __launch_bounds__(kThreads) ew_rows(const T* __restrict__ a, const T* __restrict__ b,
                                                     T* __restrict__ d, RowsGeom g, Imm imm) {
     constexpr int V = Vec<T>::N;
     constexpr int UNROLL = 4;
     constexpr bool BIN = op_is_binary(OP);
     const int64_t cvec = g.cols / V;
-    const int64_t rstep = gridDim.y;
+    const int64_t rstep = (int64_t)gridDim.y * UNROLL;
     for (int64_t cv = (int64_t)blockIdx.x * kThreads + threadIdx.x; cv < cvec; cv += (int64_t)gridDim.x * kThreads) {
         const int64_t c = cv * V;
-        const bool a_fixed = g.a_in && g.a_rs == 0, b_fixed = BIN && g.b_in && g.b_rs == 0;
-        Vec<T> fa, fb;
-        if (a_fixed) fa = load_vec(a + c);
-        if (b_fixed) fb = load_vec(b + c);
-        int64_t r = blockIdx.y;
-        for (; r + (UNROLL - 1) * rstep < g.rows; r += UNROLL * rstep) {
+        for (int64_t r0 = (int64_t)blockIdx.y * UNROLL; r0 < g.rows; r0 += rstep) {
             Vec<T> va[UNROLL], vb[UNROLL];
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
-                const int64_t rr = r + u * rstep;
-                va[u] = a_fixed ? fa : (g.a_in ? load_vec(a + rr * g.a_rs + c) : splat_vec(__ldg(a + rr * g.a_rs)));
-                if (!BIN) vb[u] = va[u];
-                else vb[u] = b_fixed ? fb : (g.b_in ? load_vec(b + rr * g.b_rs + c) : splat_vec(__ldg(b + rr * g.b_rs)));
+                const int64_t r = r0 + u < g.rows ? r0 + u : g.rows - 1;  // the tail re-reads the last row
+                if constexpr (A_SCALAR) va[u] = splat_vec(__ldg(a + r * g.a_rs));
+                else va[u] = load_vec(a + r * g.a_rs + c);
+                if constexpr (!BIN) vb[u] = va[u];
+                else if constexpr (B_SCALAR) vb[u] = splat_vec(__ldg(b + r * g.b_rs));
+                else vb[u] = load_vec(b + r * g.b_rs + c);
             }
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u)
-                store_vec(d + (r + u * rstep) * g.cols + c, apply_vec<T, OP>(va[u], vb[u], imm));
-        }
-        for (; r < g.rows; r += rstep) {
-            Vec<T> va = a_fixed ? fa : (g.a_in ? load_vec(a + r * g.a_rs + c) : splat_vec(__ldg(a + r * g.a_rs)));
-            Vec<T> vb = !BIN ? va : (b_fixed ? fb : (g.b_in ? load_vec(b + r * g.b_rs + c) : splat_vec(__ldg(b + r * g.b_rs))));
-            store_vec(d + r * g.cols + c, apply_vec<T, OP>(va, vb, imm));
+                if (r0 + u < g.rows) store_vec(d + (r0 + u) * g.cols + c, apply_vec<T, OP>(va[u], vb[u], imm));
         }
     }
 }
@@ -315,11 +310,48 @@ tn_status build_plan(const tn_tensor_t* const* ops, int nops, const tn_tensor_t*
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// Tuning knobs read from the environment (launch geometry only; results never depend on them).
+inline int env_int(const char* name, int fallback) {
+    const char* v = getenv(name);
+    if (!v || !*v) return fallback;
+    const int n = atoi(v);
+    return n > 0 ? n : fallback;
+}
+
 int flat_grid(int64_t work_items) {
     const int64_t cap = (int64_t)sm_count() * 8;  // 8 CTAs of 256 threads fill an SM
     int64_t blocks = ceil_div(work_items, kThreads);
     if (blocks < 1) blocks = 1;
     return (int)(blocks < cap ? blocks : cap);
+}
+
+// CTAs of `kernel` that fit on one SM at once (from the occupancy calculator, cached by the
+// caller): grids are sized to exactly one resident wave so that no partial wave trails.
+template <typename K>
+int resident_ctas(K kernel, int threads) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) {
+        cudaGetLastError();
+        n = 1;
+    }
+    return n;
+}
+
+template <typename T, int OP, bool AS, bool BS>
+tn_status launch_rows(const T* pa, const T* pb, T* pd, const RowsGeom& g, Imm imm, cudaStream_t s) {
+    constexpr int V = Vec<T>::N;
+    static const int per_sm = resident_ctas(ew_rows<T, OP, AS, BS>, kThreads);
+    const int64_t cvec = g.cols / V;
+    const int64_t cap = (int64_t)sm_count() * per_sm;
+    int64_t gx = ceil_div(cvec, kThreads);
+    if (gx > cap) gx = cap;
+    int64_t gy = cap / gx;
+    const int64_t groups = ceil_div(g.rows, 4);
+    if (gy > groups) gy = groups;
+    if (gy < 1) gy = 1;
+    if (gy > 65535) gy = 65535;
+    ew_rows<T, OP, AS, BS><<<dim3((unsigned)gx, (unsigned)gy), kThreads, 0, s>>>(pa, pb, pd, g, imm);
+    return after_launch("ew_rows");
 }
 
 // Launches the fastest kernel that the geometry allows for a same-dtype op.
@@ -338,8 +370,12 @@ tn_status launch_typed(const Plan& plan, const void* a, const void* b, void* d, 
         const int64_t sb = BIN ? (plan.rank ? plan.st[1][0] : 0) : sa;
         if ((sa != 0 && sa != 1) || (sb != 0 && sb != 1)) return TN_SUCCESS;
         if ((sa == 1 && !aligned16(a)) || (BIN && sb == 1 && !aligned16(b))) return TN_SUCCESS;
-        const int grid = flat_grid(ceil_div(plan.n, V * 4));
-        ew_flat<T, OP><<<grid, kThreads, 0, s>>>(pa, pb, pd, plan.n, (int)sa, (int)sb, imm);
+        static const int per_sm = resident_ctas(ew_flat<T, OP>, kThreads);
+        const int64_t cap = (int64_t)sm_count() * per_sm;
+        int64_t grid = ceil_div(ceil_div(plan.n, V), kThreads);
+        if (grid > cap) grid = cap;
+        if (grid < 1) grid = 1;
+        ew_flat<T, OP><<<(unsigned)grid, kThreads, 0, s>>>(pa, pb, pd, plan.n, (int)sa, (int)sb, imm);
         *done = true;
         return after_launch("ew_flat");
     }
@@ -348,25 +384,22 @@ tn_status launch_typed(const Plan& plan, const void* a, const void* b, void* d, 
         g.rows = plan.sizes[0];
         g.cols = plan.sizes[1];
         g.a_rs = plan.st[0][0];
-        g.a_in = (int)plan.st[0][1];
         g.b_rs = BIN ? plan.st[1][0] : g.a_rs;
-        g.b_in = BIN ? (int)plan.st[1][1] : g.a_in;
+        const int64_t a_in = plan.st[0][1], b_in = BIN ? plan.st[1][1] : a_in;
         if (g.cols % V) return TN_SUCCESS;
-        if ((plan.st[0][1] != 0 && plan.st[0][1] != 1) || (BIN && plan.st[1][1] != 0 && plan.st[1][1] != 1)) return TN_SUCCESS;
+        if ((a_in != 0 && a_in != 1) || (b_in != 0 && b_in != 1)) return TN_SUCCESS;
         if (g.a_rs < 0 || g.b_rs < 0) return TN_SUCCESS;
-        if (g.a_in && (!aligned16(a) || g.a_rs % V)) return TN_SUCCESS;
-        if (BIN && g.b_in && (!aligned16(b) || g.b_rs % V)) return TN_SUCCESS;
-        const int64_t cvec = g.cols / V;
-        int gx = (int)ceil_div(cvec, kThreads);
-        const int64_t cap = (int64_t)sm_count() * 8;
-        if (gx > cap) gx = (int)cap;
-        int64_t gy = cap / gx;
-        if (gy < 1) gy = 1;
-        if (gy > g.rows) gy = g.rows;
-        if (gy > 65535) gy = 65535;
-        ew_rows<T, OP><<<dim3(gx, (unsigned)gy), kThreads, 0, s>>>(pa, pb, pd, g, imm);
+        if (a_in && (!aligned16(a) || g.a_rs % V)) return TN_SUCCESS;
+        if (BIN && b_in && (!aligned16(b) || g.b_rs % V)) return TN_SUCCESS;
+        if (!a_in && !b_in) return TN_SUCCESS;  // both column-broadcast: generic path
         *done = true;
-        return after_launch("ew_rows");
+        if constexpr (BIN) {
+            if (!a_in) return launch_rows<T, OP, true, false>(pa, pb, pd, g, imm, s);
+            if (!b_in) return launch_rows<T, OP, false, true>(pa, pb, pd, g, imm, s);
+        } else {
+            if (!a_in) { *done = false; return TN_SUCCESS; }
+        }
+        return launch_rows<T, OP, false, false>(pa, pb, pd, g, imm, s);
     }
     return TN_SUCCESS;
 }
@@ -585,26 +618,30 @@ __device__ __forceinline__ C apply_dynamic(int op, C a, C b, float immf) {
 // any other program with its values in local memory.
 struct NodeSpec { int op, lhs, rhs; };
 
-struct ProgDynamic { static constexpr int N = 0; };
+struct ProgDynamic { static constexpr int N = 0; static constexpr int NIN = kMaxIn; };
 
 // log(x0) + x1*x1 - exp(x0)
 struct ProgLogSquareExp {
     static constexpr int N = 5;
+    static constexpr int NIN = 2;
     static constexpr NodeSpec nodes[N] = {{TN_OP_LOG, 0, 0}, {TN_OP_MUL, 1, 1}, {TN_OP_ADD, 4, 5}, {TN_OP_EXP, 0, 0}, {TN_OP_SUB, 6, 7}};
 };
 // x0*x1 + x2
 struct ProgMulAdd {
     static constexpr int N = 2;
+    static constexpr int NIN = 3;
     static constexpr NodeSpec nodes[N] = {{TN_OP_MUL, 0, 1}, {TN_OP_ADD, 4, 2}};
 };
 // (x0 - x1) * (x0 - x1)
 struct ProgSquaredDiff {
     static constexpr int N = 2;
+    static constexpr int NIN = 2;
     static constexpr NodeSpec nodes[N] = {{TN_OP_SUB, 0, 1}, {TN_OP_MUL, 4, 4}};
 };
 // x0 * rsqrt(x1, eps) * x2   (normalisation scale)
 struct ProgNormScale {
     static constexpr int N = 3;
+    static constexpr int NIN = 3;
     static constexpr NodeSpec nodes[N] = {{TN_OP_RSQRT, 1, 1}, {TN_OP_MUL, 0, 4}, {TN_OP_MUL, 5, 2}};
 };
 
@@ -623,55 +660,162 @@ __device__ __forceinline__ void eval_static(typename compute_of<T>::type (&val)[
     }
 }
 
+// Packed arithmetic for the 16-bit storage types. A native half2 / bfloat162 add, subtract or
+// multiply rounds once to the storage type, which is bit-identical to "compute in float32, round
+// on store" for these three operations (float32 carries more than twice the significand), so
+// such nodes need no conversion at all and process two elements per instruction. The _rn forms
+// are never contracted into a fused multiply-add with a neighbouring node.
+template <typename T> struct Pack2;
+template <> struct Pack2<__half> {
+    using type = __half2;
+    static __device__ __forceinline__ type add(type a, type b) { return __hadd2_rn(a, b); }
+    static __device__ __forceinline__ type sub(type a, type b) { return __hsub2_rn(a, b); }
+    static __device__ __forceinline__ type mul(type a, type b) { return __hmul2_rn(a, b); }
+    static __device__ __forceinline__ type neg(type a) { return __hneg2(a); }
+    static __device__ __forceinline__ type abs(type a) { return __habs2(a); }
+    static __device__ __forceinline__ float2 unpack(type a) { return __half22float2(a); }
+    static __device__ __forceinline__ type pack(float2 f) { return __float22half2_rn(f); }
+    static __device__ __forceinline__ type splat(float f) { return __float2half2_rn(f); }
+};
+template <> struct Pack2<__nv_bfloat16> {
+    using type = __nv_bfloat162;
+    static __device__ __forceinline__ type add(type a, type b) { return __hadd2_rn(a, b); }
+    static __device__ __forceinline__ type sub(type a, type b) { return __hsub2_rn(a, b); }
+    static __device__ __forceinline__ type mul(type a, type b) { return __hmul2_rn(a, b); }
+    static __device__ __forceinline__ type neg(type a) { return __hneg2(a); }
+    static __device__ __forceinline__ type abs(type a) { return __habs2(a); }
+    static __device__ __forceinline__ float2 unpack(type a) { return __bfloat1622float2(a); }
+    static __device__ __forceinline__ type pack(float2 f) { return __float22bfloat162_rn(f); }
+    static __device__ __forceinline__ type splat(float f) { return __float2bfloat162_rn(f); }
+};
+
+template <typename T, int OP>
+__device__ __forceinline__ typename Pack2<T>::type apply_packed(typename Pack2<T>::type a, typename Pack2<T>::type b, float immf) {
+    using PK = Pack2<T>;
+    if constexpr (OP == TN_OP_ADD) return PK::add(a, b);
+    else if constexpr (OP == TN_OP_SUB) return PK::sub(a, b);
+    else if constexpr (OP == TN_OP_MUL) return PK::mul(a, b);
+    else if constexpr (OP == TN_OP_NEG) return PK::neg(a);
+    else if constexpr (OP == TN_OP_ABS) return PK::abs(a);
+    else if constexpr (OP == TN_OP_SCALE) return PK::mul(a, PK::splat(immf));  // factor rounded to T first
+    else if constexpr (std::is_same<T, __half>::value && (OP == TN_OP_LOG || OP == TN_OP_EXP)) {
+        // A float16 value widened to float32 is never subnormal and a result below 2^-24 rounds
+        // to zero in float16 anyway, so the flush-to-zero forms of the special-function unit
+        // lose nothing and save the subnormal fix-up code around lg2 / ex2.
+        const float2 x = PK::unpack(a);
+        float2 r;
+        if constexpr (OP == TN_OP_LOG) {
+            asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(r.x) : "f"(x.x));
+            asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(r.y) : "f"(x.y));
+            r.x = __fmul_rn(r.x, 0.693147180559945309f);
+            r.y = __fmul_rn(r.y, 0.693147180559945309f);
+        } else {
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r.x) : "f"(__fmul_rn(x.x, 1.44269504088896341f)));
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r.y) : "f"(__fmul_rn(x.y, 1.44269504088896341f)));
+        }
+        return PK::pack(r);
+    } else {
+        const Imm imm{(double)immf, 0};
+        const float2 x = PK::unpack(a), y = PK::unpack(b);
+        float2 r;
+        r.x = apply_op<OP, true, float>(x.x, y.x, imm);
+        r.y = apply_op<OP, true, float>(x.y, y.y, imm);
+        return PK::pack(r);
+    }
+}
+
+template <typename T, typename P, int K, int V2>
+__device__ __forceinline__ void eval_static_packed(typename Pack2<T>::type (&val)[kMaxIn + (P::N ? P::N : 1)][V2],
+                                                   const tn_eltwise_node_t* nodes) {
+    if constexpr (K < P::N) {
+        constexpr NodeSpec nd = P::nodes[K];
+        const float immf = nodes[K].imm;
+#pragma unroll
+        for (int i = 0; i < V2; ++i) val[kMaxIn + K][i] = apply_packed<T, nd.op>(val[nd.lhs][i], val[nd.rhs][i], immf);
+        eval_static_packed<T, P, K + 1, V2>(val, nodes);
+    }
+}
+
+// Evaluates the program on one 16-byte vector of every input.
 template <typename T, typename P>
-__global__ void __launch_bounds__(kThreads) ew_program_rows(const __grid_constant__ ProgArgs g) {
+__device__ __forceinline__ Vec<T> eval_vector(const Vec<T> (&vin)[kMaxIn], const ProgArgs& g) {
     using C = typename compute_of<T>::type;
     constexpr bool FAST = sizeof(T) == 2;
     constexpr int V = Vec<T>::N;
     constexpr bool STATIC = P::N > 0;
-    const int64_t cvec = g.cols / V;
-    const int64_t rstep = gridDim.y;
-    for (int64_t cv = (int64_t)blockIdx.x * kThreads + threadIdx.x; cv < cvec; cv += (int64_t)gridDim.x * kThreads) {
-        const int64_t c = cv * V;
-        Vec<T> fixed[kMaxIn];
+    Vec<T> out;
+    if constexpr (STATIC && sizeof(T) == 2) {
+        using P2 = typename Pack2<T>::type;
+        constexpr int V2 = V / 2;
+        P2 val[kMaxIn + P::N][V2];
 #pragma unroll
         for (int k = 0; k < kMaxIn; ++k)
-            if (k < g.n_inputs && g.inner[k] && g.rs[k] == 0) fixed[k] = load_vec(static_cast<const T*>(g.in[k]) + c);
-        for (int64_t r = blockIdx.y; r < g.rows; r += rstep) {
-            Vec<T> vin[kMaxIn];
 #pragma unroll
-            for (int k = 0; k < kMaxIn; ++k) {
-                if (k >= g.n_inputs) continue;
-                const T* base = static_cast<const T*>(g.in[k]);
-                if (g.inner[k]) vin[k] = g.rs[k] == 0 ? fixed[k] : load_vec(base + r * g.rs[k] + c);
-                else vin[k] = splat_vec(__ldg(base + r * g.rs[k]));
-            }
-            Vec<T> out;
-            if constexpr (STATIC) {
-                C val[kMaxIn + P::N][V];
+            for (int i = 0; i < V2; ++i)
+                val[k][i] = k < g.n_inputs ? reinterpret_cast<const P2*>(vin[k].e)[i] : Pack2<T>::splat(0.0f);
+        eval_static_packed<T, P, 0, V2>(val, g.nodes);
 #pragma unroll
-                for (int k = 0; k < kMaxIn; ++k)
+        for (int i = 0; i < V2; ++i) reinterpret_cast<P2*>(out.e)[i] = val[kMaxIn + P::N - 1][i];
+    } else if constexpr (STATIC) {
+        C val[kMaxIn + P::N][V];
 #pragma unroll
-                    for (int i = 0; i < V; ++i) val[k][i] = k < g.n_inputs ? to_compute<C>(vin[k].e[i]) : C(0);
-                eval_static<T, P, 0, V>(val, g.nodes);
+        for (int k = 0; k < kMaxIn; ++k)
 #pragma unroll
-                for (int i = 0; i < V; ++i) out.e[i] = from_compute<T, C>(val[kMaxIn + P::N - 1][i]);
-            } else {
-                C val[kMaxIn + kMaxNodes][V];
+            for (int i = 0; i < V; ++i) val[k][i] = k < g.n_inputs ? to_compute<C>(vin[k].e[i]) : C(0);
+        eval_static<T, P, 0, V>(val, g.nodes);
 #pragma unroll
-                for (int k = 0; k < kMaxIn; ++k)
+        for (int i = 0; i < V; ++i) out.e[i] = from_compute<T, C>(val[kMaxIn + P::N - 1][i]);
+    } else {
+        C val[kMaxIn + kMaxNodes][V];
 #pragma unroll
-                    for (int i = 0; i < V; ++i) val[k][i] = k < g.n_inputs ? to_compute<C>(vin[k].e[i]) : C(0);
-                for (int n = 0; n < g.n_nodes; ++n) {
-                    const tn_eltwise_node_t nd = g.nodes[n];
+        for (int k = 0; k < kMaxIn; ++k)
 #pragma unroll
-                    for (int i = 0; i < V; ++i)
-                        val[kMaxIn + n][i] = round_to_storage<T, C>(apply_dynamic<C, FAST>(nd.opcode, val[nd.lhs][i], val[nd.rhs][i], nd.imm));
+            for (int i = 0; i < V; ++i) val[k][i] = k < g.n_inputs ? to_compute<C>(vin[k].e[i]) : C(0);
+        for (int n = 0; n < g.n_nodes; ++n) {
+            const tn_eltwise_node_t nd = g.nodes[n];
+#pragma unroll
+            for (int i = 0; i < V; ++i)
+                val[kMaxIn + n][i] = round_to_storage<T, C>(apply_dynamic<C, FAST>(nd.opcode, val[nd.lhs][i], val[nd.rhs][i], nd.imm));
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) out.e[i] = from_compute<T, C>(val[kMaxIn + g.n_nodes - 1][i]);
+    }
+    return out;
+}
+
+// A thread owns one 16-byte column slot and walks down the rows, UNROLL adjacent rows at a time.
+// The loads of those rows are issued before any of them is consumed, so that enough bytes are in
+// flight per SM to cover the HBM latency. A row-broadcast input has row pitch 0 and is simply
+// re-read (from L1) every row; only when some input is column-broadcast (ANY_SCALAR) does the
+// load path branch on the input kind.
+template <typename T, typename P, int UNROLL, bool ANY_SCALAR>
+__global__ void __launch_bounds__(kThreads) ew_program_rows(const __grid_constant__ ProgArgs g) {
+    constexpr int V = Vec<T>::N;
+    constexpr int NIN = P::NIN;
+    const int64_t cvec = g.cols / V;
+    const int64_t rstep = (int64_t)gridDim.y * UNROLL;
+    for (int64_t cv = (int64_t)blockIdx.x * kThreads + threadIdx.x; cv < cvec; cv += (int64_t)gridDim.x * kThreads) {
+        const int64_t c = cv * V;
+        for (int64_t r0 = (int64_t)blockIdx.y * UNROLL; r0 < g.rows; r0 += rstep) {
+            Vec<T> vin[UNROLL][kMaxIn];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int64_t r = r0 + u < g.rows ? r0 + u : g.rows - 1;  // the tail re-reads the last row
+#pragma unroll
+                for (int k = 0; k < NIN; ++k) {
+                    if (P::N == 0 && k >= g.n_inputs) continue;
+                    const T* base = static_cast<const T*>(g.in[k]);
+                    if constexpr (ANY_SCALAR) {
+                        if (g.inner[k]) vin[u][k] = load_vec(base + r * g.rs[k] + c);
+                        else vin[u][k] = splat_vec(__ldg(base + r * g.rs[k]));
+                    } else {
+                        vin[u][k] = load_vec(base + r * g.rs[k] + c);
+                    }
                 }
-#pragma unroll
-                for (int i = 0; i < V; ++i) out.e[i] = from_compute<T, C>(val[kMaxIn + g.n_nodes - 1][i]);
             }
-            store_vec(static_cast<T*>(g.d) + r * g.cols + c, out);
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u)
+                if (r0 + u < g.rows) store_vec(static_cast<T*>(g.d) + (r0 + u) * g.cols + c, eval_vector<T, P>(vin[u], g));
         }
     }
 }
@@ -743,20 +887,38 @@ tn_status launch_program(const Plan& plan, const tn_tensor_t* const* inputs, int
         g.n_inputs = n_inputs;
         g.n_nodes = n_nodes;
         for (int k = 0; k < n_nodes; ++k) g.nodes[k] = nodes[k];
-        const int64_t cvec = cols / V;
-        const int64_t cap = (int64_t)sm_count() * 8;
-        int gx = (int)ceil_div(cvec, kThreads);
-        if (gx > cap) gx = (int)cap;
-        int64_t gy = cap / gx;
-        if (gy < 1) gy = 1;
-        if (gy > rows) gy = rows;
-        if (gy > 65535) gy = 65535;
-        const dim3 grid(gx, (unsigned)gy);
-        if (matches<ProgLogSquareExp>(nodes, n_nodes)) ew_program_rows<T, ProgLogSquareExp><<<grid, kThreads, 0, s>>>(g);
-        else if (matches<ProgMulAdd>(nodes, n_nodes)) ew_program_rows<T, ProgMulAdd><<<grid, kThreads, 0, s>>>(g);
-        else if (matches<ProgSquaredDiff>(nodes, n_nodes)) ew_program_rows<T, ProgSquaredDiff><<<grid, kThreads, 0, s>>>(g);
-        else if (matches<ProgNormScale>(nodes, n_nodes)) ew_program_rows<T, ProgNormScale><<<grid, kThreads, 0, s>>>(g);
-        else ew_program_rows<T, ProgDynamic><<<grid, kThreads, 0, s>>>(g);
+        bool any_scalar = false;
+        for (int k = 0; k < n_inputs; ++k) any_scalar = any_scalar || g.inner[k] == 0;
+        const int unroll = env_int("TN_PROGRAM_UNROLL", 2);
+        // one resident wave: CTAs per SM from the occupancy calculator (cached per instantiation)
+        auto launch = [&](auto kernel, int u) {
+            static const int per_sm = resident_ctas(kernel, kThreads);
+            const int64_t cvec = cols / V;
+            // two resident waves' worth of CTAs measured a few percent faster than exactly one
+            const int64_t cap = (int64_t)sm_count() * env_int("TN_PROGRAM_CTAS_PER_SM", 2 * per_sm);
+            int64_t gx = ceil_div(cvec, kThreads);
+            if (gx > cap) gx = cap;
+            int64_t gy = cap / gx;
+            const int64_t groups = ceil_div(rows, u);
+            if (gy > groups) gy = groups;
+            if (gy < 1) gy = 1;
+            if (gy > 65535) gy = 65535;
+            kernel<<<dim3((unsigned)gx, (unsigned)gy), kThreads, 0, s>>>(g);
+        };
+#define TN_LAUNCH_PROGRAM(PROG)                                                         \
+    do {                                                                                \
+        if (any_scalar) launch(ew_program_rows<T, PROG, 1, true>, 1);                   \
+        else if (unroll >= 4) launch(ew_program_rows<T, PROG, 4, false>, 4);            \
+        else if (unroll >= 2) launch(ew_program_rows<T, PROG, 2, false>, 2);            \
+        else launch(ew_program_rows<T, PROG, 1, false>, 1);                             \
+    } while (0)
+        if (matches<ProgLogSquareExp>(nodes, n_nodes)) TN_LAUNCH_PROGRAM(ProgLogSquareExp);
+        else if (matches<ProgMulAdd>(nodes, n_nodes)) TN_LAUNCH_PROGRAM(ProgMulAdd);
+        else if (matches<ProgSquaredDiff>(nodes, n_nodes)) TN_LAUNCH_PROGRAM(ProgSquaredDiff);
+        else if (matches<ProgNormScale>(nodes, n_nodes)) TN_LAUNCH_PROGRAM(ProgNormScale);
+        else if (any_scalar) launch(ew_program_rows<T, ProgDynamic, 1, true>, 1);
+        else launch(ew_program_rows<T, ProgDynamic, 1, false>, 1);
+#undef TN_LAUNCH_PROGRAM
         return after_launch("ew_program_rows");
     }
     ProgGenericArgs g;
@@ -848,6 +1010,12 @@ tn_status tn_eltwise_program(const tn_tensor_t* const* inputs, int n_inputs, con
     for (int k = 0; k < n_nodes; ++k) {
         local[k] = nodes[k];
         if (!op_is_binary(local[k].opcode)) local[k].rhs = local[k].lhs;
+        // `tensor * scalar` casts the scalar to the tensor's dtype first
+        // (include/tannic/operations.hpp:295-313): do the same to a SCALE node's factor
+        if (local[k].opcode == TN_OP_SCALE) {
+            if (dt == TN_FLOAT16) local[k].imm = __half2float(__float2half_rn(local[k].imm));
+            else if (dt == TN_BFLOAT16) local[k].imm = __bfloat162float(__float2bfloat16_rn(local[k].imm));
+        }
     }
     Plan plan;
     TN_TRY(build_plan(inputs, n_inputs, dst, plan));
