@@ -176,11 +176,14 @@ def time_device(fn, steps, warmup, torch):
     return start.elapsed_time(stop) / steps
 
 
-def secondary_workloads(torch, tb, A, hbm_peak, tf_peak):
+def secondary_workloads(torch, tb, A, hbm_peak, tf_peak, only=None, small=False):
     """Device-timed figures for the other BASELINE configs (rank 0 only). Inputs are seeded
-    synthetic tensors of the named shapes and distributions, created on the device."""
+    synthetic tensors of the named shapes and distributions, created on the device. `only` runs a
+    single workload (used for profiling); `small` shrinks the leading dimension so that a
+    profiler capture stays short (inputs still exceed L2 where the workload is HBM-bound)."""
     out = {}
     g = torch.Generator(device="cuda")
+    iters, warm = (2, 1) if small else (10, 3)
 
     def record(name, ms, bytes_=None, flops=None, bound="hbm", note=None):
         e = {"ms": ms, "bound": bound}
@@ -196,48 +199,57 @@ def secondary_workloads(torch, tb, A, hbm_peak, tf_peak):
             e["note"] = note
         out[name] = e
 
-    try:
-        # config 2b: int32 A[8192,8192] + B[8192,1]
+    def config2b():
         g.manual_seed(1)
         a = torch.randint(-1000, 1001, (8192, 8192), dtype=torch.int32, device="cuda", generator=g)
         b = torch.randint(-1000, 1001, (8192, 1), dtype=torch.int32, device="cuda", generator=g)
-        ms = time_device(lambda: tb.add(a, b), 10, 3, torch)
+        ms = time_device(lambda: tb.add(a, b), iters, warm, torch)
         record("config2b_int32_add_colbroadcast", ms, bytes_=2 * 8192 * 8192 * 4 + 8192 * 4)
-        del a, b
-        # config 3: bf16 X[8,2048,4096] x W[14336,4096]^T
+
+    def config3():
+        batch = 2 if small else 8
         g.manual_seed(2)
-        x = torch.randn((8, 2048, 4096), device="cuda", generator=g).to(torch.bfloat16)
+        x = torch.randn((batch, 2048, 4096), device="cuda", generator=g).to(torch.bfloat16)
         w = (torch.randn((14336, 4096), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
-        ms = time_device(lambda: tb.matmul(x, w.transpose(-1, -2)), 10, 3, torch)
-        record("config3_llama_mlp_gemm_bf16", ms, flops=2 * 16384 * 14336 * 4096, bound="tensor")
-        del x, w
-        # config 5: ViT scores + row statistics
+        ms = time_device(lambda: tb.matmul(x, w.transpose(-1, -2)), iters, warm, torch)
+        record("config3_llama_mlp_gemm_bf16", ms, flops=2 * batch * 2048 * 14336 * 4096, bound="tensor",
+               note=f"X[{batch},2048,4096] . W[14336,4096]^T")
+
+    def config5():
+        batch = 64 if small else 256
         g.manual_seed(4)
-        q = torch.randn((256, 12, 197, 64), device="cuda", generator=g).to(torch.bfloat16)
-        k = torch.randn((256, 12, 197, 64), device="cuda", generator=g).to(torch.bfloat16)
-        ms = time_device(lambda: tb.matmul(q, k.transpose(-1, -2), scale_by=0.125), 10, 3, torch)
-        s_bytes = 256 * 12 * 197 * 197 * 2
-        record("config5_vit_scores_gemm_scaled_bf16", ms, bytes_=2 * q.numel() * 2 + s_bytes, flops=2 * 256 * 12 * 197 * 197 * 64)
+        q = torch.randn((batch, 12, 197, 64), device="cuda", generator=g).to(torch.bfloat16)
+        k = torch.randn((batch, 12, 197, 64), device="cuda", generator=g).to(torch.bfloat16)
+        ms = time_device(lambda: tb.matmul(q, k.transpose(-1, -2), scale_by=0.125), iters, warm, torch)
+        s_bytes = batch * 12 * 197 * 197 * 2
+        record("config5_vit_scores_gemm_scaled_bf16", ms, bytes_=2 * q.numel() * 2 + s_bytes, flops=2 * batch * 12 * 197 * 197 * 64,
+               note=f"Q,K[{batch},12,197,64]")
         s = tb.matmul(q, k.transpose(-1, -2), scale_by=0.125)
-        ms = time_device(lambda: tb.reduce_stats(s, -1), 10, 3, torch)
-        record("config5_row_max_sum_argmax_bf16", ms, bytes_=s_bytes + 256 * 12 * 197 * (8 + 2 + 2))
-        del q, k, s
-        # config 4b: 1x1 convolution 256 -> 1024 on [128,256,56,56] fp16
+        ms = time_device(lambda: tb.reduce_stats(s, -1), iters, warm, torch)
+        record("config5_row_max_sum_argmax_bf16", ms, bytes_=s_bytes + batch * 12 * 197 * (8 + 2 + 2))
+
+    def config4():
+        n = 16 if small else 128
         g.manual_seed(3)
-        xin = torch.randn((128, 256, 56, 56), device="cuda", generator=g).to(torch.float16)
+        xin = torch.randn((n, 256, 56, 56), device="cuda", generator=g).to(torch.float16)
         w1 = (torch.randn((1024, 256, 1, 1), device="cuda", generator=g) * (2.0 / 256) ** 0.5).to(torch.float16)
-        ms = time_device(lambda: tb.convolve2D(xin, w1, 1, 0), 5, 2, torch)
-        record("config4b_conv1x1_fp16", ms, bytes_=xin.numel() * 2 + w1.numel() * 2 + 128 * 1024 * 3136 * 2,
-               flops=2 * 128 * 1024 * 3136 * 256)
+        ms = time_device(lambda: tb.convolve2D(xin, w1, 1, 0), max(2, iters // 2), max(1, warm - 1), torch)
+        record("config4b_conv1x1_fp16", ms, bytes_=xin.numel() * 2 + w1.numel() * 2 + n * 1024 * 3136 * 2,
+               flops=2 * n * 1024 * 3136 * 256, note=f"x[{n},256,56,56]")
         del w1
-        # config 4a: 3x3 convolution 256 -> 256, stride 1, pad 1
         w3 = (torch.randn((256, 256, 3, 3), device="cuda", generator=g) * (2.0 / 2304) ** 0.5).to(torch.float16)
-        ms = time_device(lambda: tb.convolve2D(xin, w3, 1, 1), 2, 1, torch)
-        record("config4a_conv3x3_fp16", ms, flops=2 * 128 * 256 * 3136 * 256 * 9, bound="tensor")
-        del xin, w3
+        ms = time_device(lambda: tb.convolve2D(xin, w3, 1, 1), max(2, iters // 2), max(1, warm - 1), torch)
+        record("config4a_conv3x3_fp16", ms, flops=2 * n * 256 * 3136 * 256 * 9, bound="tensor", note=f"x[{n},256,56,56]")
+
+    table = {"config2b": config2b, "config3": config3, "config5": config5, "config4": config4}
+    for name, fn in table.items():
+        if only is not None and only != name:
+            continue
+        try:
+            fn()
+        except Exception as exc:  # a failing secondary workload must not hide the headline number
+            out[name + "_error"] = f"{type(exc).__name__}: {exc}"
         torch.cuda.empty_cache()
-    except Exception as exc:  # a failing secondary workload must not hide the headline number
-        out["error"] = f"{type(exc).__name__}: {exc}"
     return out
 
 
@@ -257,6 +269,12 @@ def ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     hbm_peak, tf_peak, peak_kind = peaks()
+    if args.only:
+        # a single secondary workload, for profiling (one GPU; prints its own JSON line)
+        if rank == 0:
+            print(json.dumps({"workloads": secondary_workloads(torch, tb, A, hbm_peak, tf_peak, only=args.only, small=args.small),
+                              "device_errors": tb.device_errors()}), flush=True)
+        return 0
 
     import oracle  # input generator only (seeded, shared with the tests)
     x_host = oracle.fill((ROWS, COLS), torch.float16, 1 + 7919 * rank, "uniform", 0.1, 4.0).pin_memory()
@@ -380,6 +398,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--headline-only", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default=None, choices=["config2b", "config3", "config4", "config5"],
+                    help="run one secondary workload alone (profiling aid)")
+    ap.add_argument("--small", action="store_true", help="with --only: shrink the leading dimension for a short profiler capture")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
