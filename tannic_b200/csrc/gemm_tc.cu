@@ -5,7 +5,18 @@
 //   warp 0      TMA producer   (one elected lane issues cp.async.bulk.tensor loads)
 //   warp 1      MMA issuer     (one elected lane issues tcgen05.mma / tcgen05.commit)
 //   warps 2..5  epilogue       (tcgen05.ld -> convert -> transposed through smem -> coalesced
-//                               stores; each warp owns the TMEM lane quarter (warp % 4))
+//                               stores, 16 bytes per lane where the result is aligned; each warp
+//                               owns the TMEM lane quarter (warp % 4))
+//
+// Three operand modes share the main loop:
+//   MODE_K  B is K-major ([N, K]: `matmul(X, W.transpose(-1,-2))`), one 64x256 TMA box per stage;
+//   MODE_N  B is N-major ([K, N]: plain matmul, the [Cin, H*W] matrix of a 1x1 convolution),
+//           four 64-column boxes per stage and MN-major shared-memory descriptors;
+//   MODE_CONV  implicit-GEMM convolution: A = weights repacked to [tap][Cout][Cin], B = the
+//           activation in NHWC, fetched per (tap, channel block) as a 4-D box
+//           {64 channels, Wout, Hbox, 1} whose W/H coordinates are shifted by the tap and may
+//           run out of range (TMA zero fill = zero padding). A tile is Hbox full output rows,
+//           so the accumulator [Cout tile, Hbox*Wout pixels] stores straight into NCHW.
 //
 // CTA tile 128 x 256 x 64: one UMMA is M=128, N=256, K=16, so a K-block is four MMAs. The
 // 512 TMEM columns hold two 128x256 fp32 accumulators, so the epilogue of tile i overlaps the
@@ -35,8 +46,9 @@ constexpr uint32_t A_BYTES = BM * BK * 2;        // 16 KiB
 constexpr uint32_t B_BYTES = BN * BK * 2;        // 32 KiB
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr uint32_t TMEM_COLS = 512;              // two accumulators of BN fp32 columns
-constexpr int STAGING_PITCH = 33;                // words per staged row (conflict-free transpose)
-constexpr uint32_t STAGING_BYTES = kEpilogueWarps * 32 * STAGING_PITCH * 4;
+constexpr int STAGING_PITCH = 33;                // words per staged row of the element-wise path (conflict-free transpose)
+constexpr uint32_t STAGING_WARP_BYTES = 32 * 144; // per epilogue warp: 32 rows x (128 B of fp32 + 16 B pad)
+constexpr uint32_t STAGING_BYTES = kEpilogueWarps * STAGING_WARP_BYTES;
 constexpr uint32_t SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + STAGING_BYTES + 256 /*barriers*/;
 
 constexpr uint32_t kSpinFast = 2048;      // polls without sleeping
@@ -87,6 +99,13 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -129,18 +148,27 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
     return d;
 }
 
+enum { MODE_K = 0, MODE_N = 1, MODE_CONV = 2 };
+
 struct KernelArgs {
     void* d;
     const void* bias;
-    int64_t M, N, K;
+    int64_t M, N;              // result rows / columns per batch (conv: Cout, Hout*Wout)
     int64_t ldd, d_batch;
     int m_tiles, n_tiles;
     int64_t total_tiles;
+    int k_blocks;              // 64-wide K blocks per tile (conv: taps * channel blocks)
+    int tile_n;                // result columns per tile (256; conv: Hbox * Wout)
+    int umma_n;                // N of the MMA instruction (multiple of 16, >= tile_n)
+    uint32_t stage_tx;         // bytes TMA delivers per stage
     int a_batched, b_batched;  // 0: operand shared by all batches (batch coordinate pinned to 0)
     int is_bf16;               // operand format: 1 = bf16, 0 = fp16
     int d_is_f32;
+    int vec_store;             // result rows can be written with 16-byte stores
     int has_scale;
     float scale;
+    // convolution geometry
+    int cblocks, kw, pad_h, pad_w, hbox;
 };
 
 // Tiles are walked in groups of 16 row-tiles so that the CTAs running at the same time share
@@ -158,19 +186,122 @@ __device__ __forceinline__ void tile_coords(int64_t t, int m_tiles, int n_tiles,
     mt = g * kGroupM + (r - nt * rows_in_group);
 }
 
-template <typename OutT>
-__device__ __forceinline__ OutT finish(float acc, const KernelArgs& g, float bias) {
-    float v = acc + bias;
+// Accumulator -> result element: bias, rounding to the result type, optional scalar factor
+// (applied to the rounded value and rounded again, like `matmul(...) * scalar` in two kernels).
+template <typename OutT, bool SCALE>
+__device__ __forceinline__ OutT finish(float acc, float scale, float bias) {
+    const float v = acc + bias;
     if constexpr (std::is_same<OutT, float>::value) {
-        return g.has_scale ? v * g.scale : v;
+        return SCALE ? v * scale : v;
     } else {
         OutT r = from_compute<OutT, float>(v);
-        if (g.has_scale) r = from_compute<OutT, float>(to_compute<float>(r) * g.scale);
+        if constexpr (SCALE) r = from_compute<OutT, float>(to_compute<float>(r) * scale);
         return r;
     }
 }
 
-template <bool B_N_MAJOR>
+template <typename OutT> __device__ __forceinline__ uint32_t bits16(OutT v);
+template <> __device__ __forceinline__ uint32_t bits16<__half>(__half v) { return __half_as_ushort(v); }
+template <> __device__ __forceinline__ uint32_t bits16<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat16_as_ushort(v); }
+
+struct EpilogueTile {
+    uint8_t* dbase;      // result of this batch
+    int64_t ldd;
+    int64_t row0;        // first result row of this warp
+    int rows;            // valid rows (<= 32)
+    int64_t col_base;    // first result column of the tile
+    int64_t col_end;     // one past the last column this tile owns
+    uint32_t taddr0;     // TMEM address of (lane quarter, accumulator buffer)
+    float bias, scale;
+    int vec_store;
+};
+
+// Drains one warp's 32 x tile_n slice of the accumulator. OutT and SCALE are compile-time so
+// that the per-element conversion code has no branches.
+template <typename OutT, bool SCALE>
+__device__ __forceinline__ void drain_tile(const EpilogueTile& e, uint8_t* stage, int lane) {
+    uint32_t* stage_words = reinterpret_cast<uint32_t*>(stage);
+    for (int c = 0; c < BN / 32; ++c) {
+        const int64_t col0 = e.col_base + c * 32;
+        if (col0 >= e.col_end || e.rows <= 0) break;  // warp-uniform
+        uint32_t v[32];
+        tmem_load_32x32(e.taddr0 + c * 32, v);
+        // lane owns row (row0 + lane), columns col0 .. col0+31: stage the 32x32 block in shared
+        // memory, then write it out with lanes running along the columns of a row
+        __syncwarp();
+        if constexpr (!std::is_same<OutT, float>::value) {
+            if (e.vec_store) {
+                // 16-bit result, rows of 64 bytes staged at an 80-byte pitch (conflict-free for
+                // 16-byte accesses), written as 8 rows x 4 lanes x 16 bytes per instruction
+                uint4* mine = reinterpret_cast<uint4*>(stage + lane * 80);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        w[j] = bits16(finish<OutT, SCALE>(__uint_as_float(v[8 * q + 2 * j]), e.scale, e.bias)) |
+                               (bits16(finish<OutT, SCALE>(__uint_as_float(v[8 * q + 2 * j + 1]), e.scale, e.bias)) << 16);
+                    mine[q] = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                __syncwarp();
+                const int seg = lane & 3;
+                const int64_t col = col0 + seg * 8;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int r = i * 8 + (lane >> 2);
+                    if (r < e.rows && col < e.col_end)
+                        *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(e.dbase) + (e.row0 + r) * e.ldd + col) =
+                            *reinterpret_cast<const uint4*>(stage + r * 80 + seg * 16);
+                }
+            } else {
+                // any alignment: one element per lane per row
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    stage_words[lane * STAGING_PITCH + j] = bits16(finish<OutT, SCALE>(__uint_as_float(v[j]), e.scale, e.bias));
+                __syncwarp();
+                const int64_t col = col0 + lane;
+                if (col < e.col_end) {
+                    uint16_t* out = reinterpret_cast<uint16_t*>(e.dbase) + e.row0 * e.ldd + col;
+                    for (int r = 0; r < e.rows; ++r) out[r * e.ldd] = static_cast<uint16_t>(stage_words[r * STAGING_PITCH + lane]);
+                }
+            }
+        } else {
+            if (e.vec_store) {
+                // fp32 result, rows of 128 bytes at a 144-byte pitch, 4 rows x 8 lanes x 16 bytes
+                uint4* mine = reinterpret_cast<uint4*>(stage + lane * 144);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) w[j] = __float_as_uint(finish<float, SCALE>(__uint_as_float(v[4 * q + j]), e.scale, e.bias));
+                    mine[q] = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                __syncwarp();
+                const int seg = lane & 7;
+                const int64_t col = col0 + seg * 4;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int r = i * 4 + (lane >> 3);
+                    if (r < e.rows && col < e.col_end)
+                        *reinterpret_cast<uint4*>(reinterpret_cast<float*>(e.dbase) + (e.row0 + r) * e.ldd + col) =
+                            *reinterpret_cast<const uint4*>(stage + r * 144 + seg * 16);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    stage_words[lane * STAGING_PITCH + j] = __float_as_uint(finish<float, SCALE>(__uint_as_float(v[j]), e.scale, e.bias));
+                __syncwarp();
+                const int64_t col = col0 + lane;
+                if (col < e.col_end) {
+                    float* out = reinterpret_cast<float*>(e.dbase) + e.row0 * e.ldd + col;
+                    for (int r = 0; r < e.rows; ++r) out[r * e.ldd] = __uint_as_float(stage_words[r * STAGING_PITCH + lane]);
+                }
+            }
+        }
+    }
+}
+
+template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KernelArgs g) {
     extern __shared__ uint8_t smem_raw[];
@@ -178,7 +309,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
     uint8_t* base_ptr = smem_raw + (base - raw);
     const uint32_t staging = base + STAGES * STAGE_BYTES;
-    uint32_t* staging_ptr = reinterpret_cast<uint32_t*>(base_ptr + STAGES * STAGE_BYTES);
+    uint8_t* staging_ptr = base_ptr + STAGES * STAGE_BYTES;
     const uint32_t bars = staging + STAGING_BYTES;
     // barrier layout (8 bytes each): full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
     const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, accf0 = bars + 16 * STAGES, acce0 = accf0 + 16;
@@ -186,7 +317,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int k_blocks = static_cast<int>((g.K + BK - 1) / BK);
+    const int k_blocks = g.k_blocks;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -222,15 +353,24 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t parity = ((it / STAGES) & 1) ^ 1;
                     if (!mbar_wait(empty0 + 8 * s, parity, abort_flag)) { ok = false; break; }
                     const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
-                    mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
-                    tma_load_3d(sa, &map_a, full0 + 8 * s, kb * BK, mt * BM, g.a_batched ? batch : 0);
-                    if constexpr (B_N_MAJOR) {
-                        // four boxes of 64 columns x BK rows, 8 KiB each
-#pragma unroll
-                        for (int c = 0; c < BN / 64; ++c)
-                            tma_load_3d(sb + c * (64 * BK * 2), &map_b, full0 + 8 * s, nt * BN + c * 64, kb * BK, g.b_batched ? batch : 0);
+                    mbar_expect_tx(full0 + 8 * s, g.stage_tx);
+                    if constexpr (MODE == MODE_CONV) {
+                        const int tap = kb / g.cblocks, cb = kb - tap * g.cblocks;
+                        const int kh = tap / g.kw, kwi = tap - kh * g.kw;
+                        tma_load_3d(sa, &map_a, full0 + 8 * s, cb * BK, mt * BM, tap);
+                        // innermost coordinate (channels) is a multiple of 64; the W and H coordinates
+                        // carry the tap shift and may be negative or past the edge (zero fill)
+                        tma_load_4d(sb, &map_b, full0 + 8 * s, cb * BK, kwi - g.pad_w, nt * g.hbox + kh - g.pad_h, batch);
                     } else {
-                        tma_load_3d(sb, &map_b, full0 + 8 * s, kb * BK, nt * BN, g.b_batched ? batch : 0);
+                        tma_load_3d(sa, &map_a, full0 + 8 * s, kb * BK, mt * BM, g.a_batched ? batch : 0);
+                        if constexpr (MODE == MODE_N) {
+                            // four boxes of 64 columns x BK rows, 8 KiB each
+#pragma unroll
+                            for (int c = 0; c < BN / 64; ++c)
+                                tma_load_3d(sb + c * (64 * BK * 2), &map_b, full0 + 8 * s, nt * BN + c * 64, kb * BK, g.b_batched ? batch : 0);
+                        } else {
+                            tma_load_3d(sb, &map_b, full0 + 8 * s, kb * BK, nt * BN, g.b_batched ? batch : 0);
+                        }
                     }
                 }
             }
@@ -245,8 +385,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // instruction descriptor: D = F32 (bits 4-5 = 1), A/B format (bits 7-9, 10-12:
             // 0 = F16, 1 = BF16), B major (bit 16), N >> 3 (bits 17-22), M >> 4 (bits 24-28)
             const uint32_t fmt = g.is_bf16 ? 1u : 0u;
-            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((B_N_MAJOR ? 1u : 0u) << 16) |
-                                   (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((MODE == MODE_N ? 1u : 0u) << 16) |
+                                   (static_cast<uint32_t>(g.umma_n >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
             uint32_t it = 0, local_tile = 0;
             bool ok = true;
             for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x, ++local_tile) {
@@ -266,8 +406,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         // K-major: 16 elements = 32 bytes further along the swizzled row.
                         const uint64_t da = smem_desc(sa + k * UMMA_K * 2, 16, 1024);
                         // N-major: 16 k-rows of 128 bytes further; 64-column boxes are 8 KiB apart.
-                        const uint64_t db = B_N_MAJOR ? smem_desc(sb + k * UMMA_K * 128, 64 * BK * 2, 1024)
-                                                      : smem_desc(sb + k * UMMA_K * 2, 16, 1024);
+                        const uint64_t db = MODE == MODE_N ? smem_desc(sb + k * UMMA_K * 128, 64 * BK * 2, 1024)
+                                                           : smem_desc(sb + k * UMMA_K * 2, 16, 1024);
                         umma_f16(tmem_acc, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
@@ -279,7 +419,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ------------------------------------------------------------ epilogue --------
         const int ew = warp - 2;                 // staging slot
         const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter+32)
-        uint32_t* stage_rows = staging_ptr + ew * 32 * STAGING_PITCH;
+        uint8_t* stage = staging_ptr + ew * STAGING_WARP_BYTES;
         uint32_t local_tile = 0;
         bool ok = true;
         for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x, ++local_tile) {
@@ -290,51 +430,34 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!mbar_wait(accf0 + 8 * buf, parity, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int64_t row0 = static_cast<int64_t>(mt) * BM + quarter * 32;
-            const int64_t col_base = static_cast<int64_t>(nt) * BN;
+            const int64_t col_base = static_cast<int64_t>(nt) * g.tile_n;
+            const int64_t col_end = min(g.N, col_base + g.tile_n);  // first column this tile does not own
             const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             float bias = 0.0f;
             if (g.bias != nullptr && row0 + lane < g.M) {
                 bias = g.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(g.bias)[row0 + lane])
                                  : __half2float(static_cast<const __half*>(g.bias)[row0 + lane]);
             }
-            uint8_t* dbase = static_cast<uint8_t*>(g.d) + static_cast<size_t>(batch) * g.d_batch * (g.d_is_f32 ? 4 : 2);
-            for (int c = 0; c < BN / 32; ++c) {
-                const int64_t col0 = col_base + c * 32;
-                if (col0 >= g.N || row0 >= g.M) break;  // warp-uniform
-                uint32_t v[32];
-                tmem_load_32x32(taddr0 + c * 32, v);
-                // lane owns row (row0 + lane), columns col0 .. col0+31: stage, then write rows
-                // out with lanes across columns so that every store instruction is contiguous
-                __syncwarp();
-                if (g.d_is_f32) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        stage_rows[lane * STAGING_PITCH + j] = __float_as_uint(finish<float>(__uint_as_float(v[j]), g, bias));
-                } else if (g.is_bf16) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const __nv_bfloat16 h = finish<__nv_bfloat16>(__uint_as_float(v[j]), g, bias);
-                        stage_rows[lane * STAGING_PITCH + j] = static_cast<uint32_t>(__bfloat16_as_ushort(h));
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const __half h = finish<__half>(__uint_as_float(v[j]), g, bias);
-                        stage_rows[lane * STAGING_PITCH + j] = static_cast<uint32_t>(__half_as_ushort(h));
-                    }
-                }
-                __syncwarp();
-                const int64_t col = col0 + lane;
-                if (col < g.N) {
-                    const int rows = static_cast<int>(min(static_cast<int64_t>(32), g.M - row0));
-                    if (g.d_is_f32) {
-                        float* out = reinterpret_cast<float*>(dbase) + row0 * g.ldd + col;
-                        for (int r = 0; r < rows; ++r) out[r * g.ldd] = __uint_as_float(stage_rows[r * STAGING_PITCH + lane]);
-                    } else {
-                        uint16_t* out = reinterpret_cast<uint16_t*>(dbase) + row0 * g.ldd + col;
-                        for (int r = 0; r < rows; ++r) out[r * g.ldd] = static_cast<uint16_t>(stage_rows[r * STAGING_PITCH + lane]);
-                    }
-                }
+            EpilogueTile e;
+            e.dbase = static_cast<uint8_t*>(g.d) + static_cast<size_t>(batch) * g.d_batch * (g.d_is_f32 ? 4 : 2);
+            e.ldd = g.ldd;
+            e.row0 = row0;
+            e.rows = static_cast<int>(min(static_cast<int64_t>(32), g.M - row0));
+            e.col_base = col_base;
+            e.col_end = col_end;
+            e.taddr0 = taddr0;
+            e.bias = bias;
+            e.scale = g.scale;
+            e.vec_store = g.vec_store;
+            if (g.d_is_f32) {
+                if (g.has_scale) drain_tile<float, true>(e, stage, lane);
+                else drain_tile<float, false>(e, stage, lane);
+            } else if (g.is_bf16) {
+                if (g.has_scale) drain_tile<__nv_bfloat16, true>(e, stage, lane);
+                else drain_tile<__nv_bfloat16, false>(e, stage, lane);
+            } else {
+                if (g.has_scale) drain_tile<__half, true>(e, stage, lane);
+                else drain_tile<__half, false>(e, stage, lane);
             }
             // this warp has finished reading the accumulator
             tc_fence_before();
@@ -370,11 +493,22 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// 3-D map (inner, rows, batch) over a 16-bit matrix; box = box_inner x box_rows x 1, 128B swizzle.
-tn_status make_map(CUtensorMap* map, const void* ptr, bool bf16, int64_t inner, int64_t rows, int64_t batches,
-                   int64_t row_pitch, int64_t batch_pitch, int box_inner, int box_rows) {
+// Tiled map of rank `rank` over 16-bit elements, 128-byte swizzle, zero fill outside the tensor.
+tn_status encode(CUtensorMap* map, const void* ptr, bool bf16, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
+                 const cuuint32_t* box) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(TN_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank,
+                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(TN_ERROR, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return TN_SUCCESS;
+}
+
+// 3-D map (inner, rows, batch) over a 16-bit matrix; box = box_inner x box_rows x 1.
+tn_status make_map(CUtensorMap* map, const void* ptr, bool bf16, int64_t inner, int64_t rows, int64_t batches,
+                   int64_t row_pitch, int64_t batch_pitch, int box_inner, int box_rows) {
     cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)(batches > 0 ? batches : 1)};
     // a pitch is irrelevant for an extent of 1 but must still be a non-zero multiple of 16 bytes
     cuuint64_t pitch_rows = (cuuint64_t)row_pitch * 2;
@@ -383,16 +517,27 @@ tn_status make_map(CUtensorMap* map, const void* ptr, bool bf16, int64_t inner, 
     if (pitch_batch == 0) pitch_batch = pitch_rows;
     cuuint64_t strides[2] = {pitch_rows, pitch_batch};
     cuuint32_t box[3] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(TN_ERROR, "cuTensorMapEncodeTiled failed with code %d", (int)r);
-    return TN_SUCCESS;
+    return encode(map, ptr, bf16, 3, dims, strides, box);
 }
 
 bool mult8(int64_t v) { return (v & 7) == 0; }
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <int MODE>
+tn_status launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const KernelArgs& g, cudaStream_t stream) {
+    // the opt-in shared-memory size is a per-device attribute of the kernel
+    static thread_local int attr_device = -1;
+    int dev = 0;
+    TN_CUDA(cudaGetDevice(&dev));
+    if (attr_device != dev) {
+        TN_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_device = dev;
+    }
+    const int64_t sms = sm_count();
+    const int grid = (int)(g.total_tiles < sms ? g.total_tiles : sms);
+    tc_gemm_kernel<MODE><<<grid, kThreads, SMEM_BYTES, stream>>>(map_a, map_b, g);
+    return after_launch("tc_gemm_kernel");
+}
 
 }  // namespace
 
@@ -410,53 +555,93 @@ bool tc_gemm_eligible(const TcGemm& p) {
     return tiles < (int64_t(1) << 40);
 }
 
-tn_status tc_gemm(const TcGemm& p, cudaStream_t stream) {
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(tc_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (attr_err == cudaSuccess)
-            attr_err = cudaFuncSetAttribute(tc_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    });
-    // the attribute is per device: set again when the current device changes
-    static thread_local int attr_device = -1;
-    int dev = 0;
-    TN_CUDA(cudaGetDevice(&dev));
-    if (attr_device != dev) {
-        TN_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        TN_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-        attr_device = dev;
-    }
-    if (attr_err != cudaSuccess) return fail(TN_ERROR, "cannot reserve %u bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(attr_err));
+static bool can_vector_store(const void* d, int64_t ldd, int64_t d_batch, int64_t n, int64_t tile_n, bool f32) {
+    const int64_t per16 = f32 ? 4 : 8;  // elements per 16 bytes
+    return aligned16(d) && ldd % per16 == 0 && d_batch % per16 == 0 && n % per16 == 0 && tile_n % per16 == 0;
+}
 
+tn_status tc_gemm(const TcGemm& p, cudaStream_t stream) {
     const bool bf16 = p.ab_dtype == TN_BFLOAT16;
     CUtensorMap map_a, map_b;
     TN_TRY(make_map(&map_a, p.a, bf16, p.K, p.M, p.a_batch ? p.batches : 1, p.lda, p.a_batch, BK, BM));
     if (p.b_n_major) TN_TRY(make_map(&map_b, p.b, bf16, p.N, p.K, p.b_batch ? p.batches : 1, p.ldb, p.b_batch, 64, BK));
     else TN_TRY(make_map(&map_b, p.b, bf16, p.K, p.N, p.b_batch ? p.batches : 1, p.ldb, p.b_batch, BK, BN));
 
-    KernelArgs g;
+    KernelArgs g = {};
     g.d = p.d;
     g.bias = p.bias;
     g.M = p.M;
     g.N = p.N;
-    g.K = p.K;
     g.ldd = p.ldd;
     g.d_batch = p.d_batch;
     g.m_tiles = (int)ceil_div(p.M, BM);
     g.n_tiles = (int)ceil_div(p.N, BN);
     g.total_tiles = (int64_t)g.m_tiles * g.n_tiles * p.batches;
+    g.k_blocks = (int)ceil_div(p.K, BK);
+    g.tile_n = BN;
+    g.umma_n = BN;
+    g.stage_tx = STAGE_BYTES;
     g.a_batched = p.a_batch != 0;
     g.b_batched = p.b_batch != 0;
     g.is_bf16 = bf16;
     g.d_is_f32 = p.d_dtype == TN_FLOAT32;
+    g.vec_store = can_vector_store(p.d, p.ldd, p.d_batch, p.N, BN, g.d_is_f32 != 0);
     g.has_scale = p.has_scale;
     g.scale = p.scale;
-    const int64_t sms = sm_count();
-    const int grid = (int)(g.total_tiles < sms ? g.total_tiles : sms);
-    if (p.b_n_major) tc_gemm_kernel<true><<<grid, kThreads, SMEM_BYTES, stream>>>(map_a, map_b, g);
-    else tc_gemm_kernel<false><<<grid, kThreads, SMEM_BYTES, stream>>>(map_a, map_b, g);
-    return after_launch("tc_gemm_kernel");
+    return p.b_n_major ? launch<MODE_N>(map_a, map_b, g, stream) : launch<MODE_K>(map_a, map_b, g, stream);
+}
+
+bool tc_conv_eligible(const TcConv& p) {
+    if (p.dtype != TN_FLOAT16 && p.dtype != TN_BFLOAT16) return false;
+    if (p.N <= 0 || p.C <= 0 || p.Cout <= 0 || p.Ho <= 0 || p.Wo <= 0) return false;
+    if (!mult8(p.C)) return false;                       // NHWC pixel pitch must be a multiple of 16 bytes
+    if (p.Wo > 256 || p.W > 65535 || p.H > 65535) return false;
+    if (p.Kh * p.Kw > 1024 || p.N >= (int64_t(1) << 31)) return false;
+    return aligned16(p.x_nhwc) && aligned16(p.w_packed);
+}
+
+tn_status tc_conv(const TcConv& p, cudaStream_t stream) {
+    const bool bf16 = p.dtype == TN_BFLOAT16;
+    const int taps = (int)(p.Kh * p.Kw);
+    int hbox = (int)(256 / p.Wo);
+    if (hbox > p.Ho) hbox = (int)p.Ho;
+    if (hbox < 1) hbox = 1;
+    CUtensorMap map_a, map_b;
+    // weights [tap][Cout][Cin]
+    TN_TRY(make_map(&map_a, p.w_packed, bf16, p.C, p.Cout, taps, p.C, p.Cout * p.C, BK, BM));
+    // activation [N][H][W][C]: box = 64 channels x Wout x hbox rows x 1 image
+    {
+        cuuint64_t dims[4] = {(cuuint64_t)p.C, (cuuint64_t)p.W, (cuuint64_t)p.H, (cuuint64_t)p.N};
+        cuuint64_t strides[3] = {(cuuint64_t)p.C * 2, (cuuint64_t)p.W * p.C * 2, (cuuint64_t)p.H * p.W * p.C * 2};
+        cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)p.Wo, (cuuint32_t)hbox, 1};
+        TN_TRY(encode(&map_b, p.x_nhwc, bf16, 4, dims, strides, box));
+    }
+    KernelArgs g = {};
+    g.d = p.y;
+    g.bias = p.bias;
+    g.M = p.Cout;
+    g.N = p.Ho * p.Wo;
+    g.ldd = g.N;
+    g.d_batch = p.Cout * g.N;
+    g.m_tiles = (int)ceil_div(p.Cout, BM);
+    g.n_tiles = (int)ceil_div(p.Ho, hbox);
+    g.total_tiles = (int64_t)g.m_tiles * g.n_tiles * p.N;
+    g.cblocks = (int)ceil_div(p.C, BK);
+    g.k_blocks = taps * g.cblocks;
+    g.tile_n = hbox * (int)p.Wo;
+    g.umma_n = (g.tile_n + 15) & ~15;
+    g.stage_tx = A_BYTES + (uint32_t)(hbox * p.Wo) * BK * 2;
+    g.a_batched = g.b_batched = 1;
+    g.is_bf16 = bf16;
+    g.d_is_f32 = 0;
+    g.vec_store = can_vector_store(p.y, g.ldd, g.d_batch, g.N, g.tile_n, false);
+    g.has_scale = 0;
+    g.scale = 1.0f;
+    g.kw = (int)p.Kw;
+    g.pad_h = (int)p.pad_h;
+    g.pad_w = (int)p.pad_w;
+    g.hbox = hbox;
+    return launch<MODE_CONV>(map_a, map_b, g, stream);
 }
 
 tn_status tc_abort_count(unsigned int* count) {

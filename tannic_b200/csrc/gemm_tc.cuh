@@ -25,6 +25,20 @@ struct TcGemm {
     float scale = 1.0f;
 };
 
+// Implicit-GEMM convolution (stride 1) on the same main loop. `x_nhwc` is the activation in
+// [N, H, W, C] order and `w_packed` the weights in [Kh*Kw, Cout, Cin] order (both produced by the
+// caller in scratch memory); the result is written as dense NCHW.
+struct TcConv {
+    const void* x_nhwc = nullptr;
+    const void* w_packed = nullptr;
+    const void* bias = nullptr;  // optional [Cout]
+    void* y = nullptr;
+    int dtype = 0;
+    int64_t N = 0, C = 0, H = 0, W = 0, Cout = 0, Kh = 0, Kw = 0, Ho = 0, Wo = 0, pad_h = 0, pad_w = 0;
+};
+bool tc_conv_eligible(const TcConv& p);
+tn_status tc_conv(const TcConv& p, cudaStream_t stream);
+
 // True when TMA can address the operands (16-byte aligned bases and pitches).
 bool tc_gemm_eligible(const TcGemm& p);
 tn_status tc_gemm(const TcGemm& p, cudaStream_t stream);

@@ -361,6 +361,35 @@ def test_conv2d_1x1_tensor_core(dtype):
     assert tb.device_errors() == 0
 
 
+@pytest.mark.parametrize("dtype", HALVES)
+@pytest.mark.parametrize("shape", [
+    # (N, Cin, H, W, Cout, Kh, Kw, pad)
+    (2, 64, 14, 14, 32, 3, 3, 1),       # one pixel tile per image, one channel block
+    (3, 72, 20, 24, 136, 3, 3, 1),      # ragged channel block (72 = 64 + 8), two Cout tiles, ragged last row tile
+    (1, 128, 56, 56, 64, 3, 3, 1),      # ResNet-stage geometry: 4 output rows (224 pixels) per tile
+    (2, 16, 9, 40, 8, 3, 5, 0),         # no padding, rectangular kernel
+    (2, 32, 12, 12, 16, 5, 5, 2),       # 25 taps
+    (1, 8, 70, 250, 24, 3, 3, 2),       # one output row per tile (Wout = 252), padding 2
+])
+def test_conv2d_implicit_gemm_tensor_core(dtype, shape):
+    n, cin, h, w, cout, kh, kw, pad = shape
+    x = gen((n, cin, h, w), dtype, 47, -1, 1)
+    wt = gen((cout, cin, kh, kw), dtype, 48, -0.2, 0.2)
+    bias = gen((cout,), dtype, 49, -1, 1)
+    want = oracle.conv2d(x, wt, 1, pad, acc=oracle.ACC_WIDE)
+    assert_close(tb.convolve2D(dev(x), dev(wt), 1, pad), want)
+    assert_close(tb.convolve2D(dev(x), dev(wt), 1, pad, bias=dev(bias)), oracle.conv2d(x, wt, 1, pad, bias=bias, acc=oracle.ACC_WIDE))
+    assert tb.device_errors() == 0
+
+
+def test_conv2d_implicit_gemm_strided_input_view():
+    x = gen((2, 12, 10, 64), torch.float16, 50, -1, 1)            # [N, H, W, C] storage
+    xv = x.permute(0, 3, 1, 2)                                     # NCHW view with channel stride 1
+    wt = gen((16, 64, 3, 3), torch.float16, 51, -0.2, 0.2)
+    want = oracle.conv2d(xv, wt, 1, 1, acc=oracle.ACC_WIDE)
+    assert_close(tb.convolve2D(dev(x).permute(0, 3, 1, 2), dev(wt), 1, 1), want)
+
+
 def test_conv2d_errors():
     x, w = dev(gen((1, 3, 5, 5), torch.float32, 1)), dev(gen((2, 4, 3, 3), torch.float32, 2))
     y = torch.empty(1, 2, 3, 3, device="cuda")
