@@ -30,6 +30,7 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 namespace tnb {
@@ -40,14 +41,14 @@ constexpr int BN = 256;
 constexpr int BK = 64;            // 64 x 2 bytes = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int STAGES = 4;
-constexpr int kThreads = 192;
-constexpr int kEpilogueWarps = 4;
+constexpr int kEpilogueWarps = 8;                // two per TMEM lane quarter, interleaved over 32-column chunks
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr uint32_t A_BYTES = BM * BK * 2;        // 16 KiB
 constexpr uint32_t B_BYTES = BN * BK * 2;        // 32 KiB
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr uint32_t TMEM_COLS = 512;              // two accumulators of BN fp32 columns
-constexpr int STAGING_PITCH = 33;                // words per staged row of the element-wise path (conflict-free transpose)
-constexpr uint32_t STAGING_WARP_BYTES = 32 * 144; // per epilogue warp: 32 rows x (128 B of fp32 + 16 B pad)
+constexpr int STAGING_PITCH = 17;                // words per staged row of the element-wise path (conflict-free transpose)
+constexpr uint32_t STAGING_WARP_BYTES = 32 * 80; // per epilogue warp: 32 rows x (64 B of data + 16 B pad)
 constexpr uint32_t STAGING_BYTES = kEpilogueWarps * STAGING_WARP_BYTES;
 constexpr uint32_t SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + STAGING_BYTES + 256 /*barriers*/;
 
@@ -121,7 +122,10 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ void tmem_load_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+// tcgen05.ld is asynchronous: the registers are valid only after tcgen05.wait::ld. The wait
+// below names the registers as read-write operands so that no use of them can be scheduled
+// ahead of it.
+__device__ __forceinline__ void tmem_load_issue(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32"
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
@@ -132,7 +136,15 @@ __device__ __forceinline__ void tmem_load_32x32(uint32_t taddr, uint32_t (&v)[32
           "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(taddr)
         : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_load_wait(uint32_t (&v)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+        : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+          "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]),
+          "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]),
+          "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+        :
+        : "memory");
 }
 
 // Shared-memory matrix descriptor of a 128-byte-swizzled tile (sm_100 format: start address,
@@ -169,6 +181,7 @@ struct KernelArgs {
     float scale;
     // convolution geometry
     int cblocks, kw, pad_h, pad_w, hbox;
+    int epi_warps;             // 4 or 8 epilogue warps take part (the others exit at once)
 };
 
 // Tiles are walked in groups of 16 row-tiles so that the CTAs running at the same time share
@@ -212,96 +225,133 @@ struct EpilogueTile {
     int64_t col_base;    // first result column of the tile
     int64_t col_end;     // one past the last column this tile owns
     uint32_t taddr0;     // TMEM address of (lane quarter, accumulator buffer)
+    int chunk0;          // first 32-column chunk of this warp
+    int chunk_step;      // 1: this warp takes every chunk, 2: every second one
     float bias, scale;
     int vec_store;
 };
 
-// Drains one warp's 32 x tile_n slice of the accumulator. OutT and SCALE are compile-time so
-// that the per-element conversion code has no branches.
+// Writes one 32 x 32 block (lane = row, v = 32 consecutive columns starting at col0) through a
+// per-warp staging area so that the global stores run along rows. OutT and SCALE are
+// compile-time so that the per-element conversion code has no branches.
 template <typename OutT, bool SCALE>
-__device__ __forceinline__ void drain_tile(const EpilogueTile& e, uint8_t* stage, int lane) {
+__device__ __forceinline__ void store_block(const EpilogueTile& e, const uint32_t (&v)[32], int64_t col0, uint8_t* stage, int lane) {
     uint32_t* stage_words = reinterpret_cast<uint32_t*>(stage);
-    for (int c = 0; c < BN / 32; ++c) {
-        const int64_t col0 = e.col_base + c * 32;
-        if (col0 >= e.col_end || e.rows <= 0) break;  // warp-uniform
-        uint32_t v[32];
-        tmem_load_32x32(e.taddr0 + c * 32, v);
-        // lane owns row (row0 + lane), columns col0 .. col0+31: stage the 32x32 block in shared
-        // memory, then write it out with lanes running along the columns of a row
-        __syncwarp();
-        if constexpr (!std::is_same<OutT, float>::value) {
+    __syncwarp();  // the previous block's readers are done with the staging area
+    if constexpr (!std::is_same<OutT, float>::value) {
+        if (e.vec_store) {
+            // rows of 64 bytes at an 80-byte pitch (conflict-free for 16-byte accesses), written
+            // out as 8 rows x 4 lanes x 16 bytes per instruction
+            uint4* mine = reinterpret_cast<uint4*>(stage + lane * 80);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    w[j] = bits16(finish<OutT, SCALE>(__uint_as_float(v[8 * q + 2 * j]), e.scale, e.bias)) |
+                           (bits16(finish<OutT, SCALE>(__uint_as_float(v[8 * q + 2 * j + 1]), e.scale, e.bias)) << 16);
+                mine[q] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            __syncwarp();
+            const int seg = lane & 3;
+            const int64_t col = col0 + seg * 8;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = i * 8 + (lane >> 2);
+                if (r < e.rows && col < e.col_end)
+                    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(e.dbase) + (e.row0 + r) * e.ldd + col) =
+                        *reinterpret_cast<const uint4*>(stage + r * 80 + seg * 16);
+            }
+        } else {
+            // any alignment: column pairs packed into words at a 17-word pitch, one element per
+            // lane per row on the way out
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                stage_words[lane * STAGING_PITCH + j] = bits16(finish<OutT, SCALE>(__uint_as_float(v[2 * j]), e.scale, e.bias)) |
+                                                        (bits16(finish<OutT, SCALE>(__uint_as_float(v[2 * j + 1]), e.scale, e.bias)) << 16);
+            __syncwarp();
+            const int64_t col = col0 + lane;
+            if (col < e.col_end) {
+                uint16_t* out = reinterpret_cast<uint16_t*>(e.dbase) + e.row0 * e.ldd + col;
+                const int word = lane >> 1, shift = (lane & 1) * 16;
+#pragma unroll 4
+                for (int r = 0; r < e.rows; ++r) out[r * e.ldd] = static_cast<uint16_t>(stage_words[r * STAGING_PITCH + word] >> shift);
+            }
+        }
+    } else {
+        // fp32 result: two passes of 16 columns through the same staging area
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (h) __syncwarp();
+            const int64_t colh = col0 + h * 16;
             if (e.vec_store) {
-                // 16-bit result, rows of 64 bytes staged at an 80-byte pitch (conflict-free for
-                // 16-byte accesses), written as 8 rows x 4 lanes x 16 bytes per instruction
                 uint4* mine = reinterpret_cast<uint4*>(stage + lane * 80);
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     uint32_t w[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        w[j] = bits16(finish<OutT, SCALE>(__uint_as_float(v[8 * q + 2 * j]), e.scale, e.bias)) |
-                               (bits16(finish<OutT, SCALE>(__uint_as_float(v[8 * q + 2 * j + 1]), e.scale, e.bias)) << 16);
+                    for (int j = 0; j < 4; ++j) w[j] = __float_as_uint(finish<float, SCALE>(__uint_as_float(v[h * 16 + 4 * q + j]), e.scale, e.bias));
                     mine[q] = make_uint4(w[0], w[1], w[2], w[3]);
                 }
                 __syncwarp();
                 const int seg = lane & 3;
-                const int64_t col = col0 + seg * 8;
+                const int64_t col = colh + seg * 4;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int r = i * 8 + (lane >> 2);
                     if (r < e.rows && col < e.col_end)
-                        *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(e.dbase) + (e.row0 + r) * e.ldd + col) =
+                        *reinterpret_cast<uint4*>(reinterpret_cast<float*>(e.dbase) + (e.row0 + r) * e.ldd + col) =
                             *reinterpret_cast<const uint4*>(stage + r * 80 + seg * 16);
                 }
             } else {
-                // any alignment: one element per lane per row
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    stage_words[lane * STAGING_PITCH + j] = bits16(finish<OutT, SCALE>(__uint_as_float(v[j]), e.scale, e.bias));
+                for (int j = 0; j < 16; ++j)
+                    stage_words[lane * STAGING_PITCH + j] = __float_as_uint(finish<float, SCALE>(__uint_as_float(v[h * 16 + j]), e.scale, e.bias));
                 __syncwarp();
-                const int64_t col = col0 + lane;
-                if (col < e.col_end) {
-                    uint16_t* out = reinterpret_cast<uint16_t*>(e.dbase) + e.row0 * e.ldd + col;
-                    for (int r = 0; r < e.rows; ++r) out[r * e.ldd] = static_cast<uint16_t>(stage_words[r * STAGING_PITCH + lane]);
-                }
-            }
-        } else {
-            if (e.vec_store) {
-                // fp32 result, rows of 128 bytes at a 144-byte pitch, 4 rows x 8 lanes x 16 bytes
-                uint4* mine = reinterpret_cast<uint4*>(stage + lane * 144);
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) w[j] = __float_as_uint(finish<float, SCALE>(__uint_as_float(v[4 * q + j]), e.scale, e.bias));
-                    mine[q] = make_uint4(w[0], w[1], w[2], w[3]);
-                }
-                __syncwarp();
-                const int seg = lane & 7;
-                const int64_t col = col0 + seg * 4;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int r = i * 4 + (lane >> 3);
-                    if (r < e.rows && col < e.col_end)
-                        *reinterpret_cast<uint4*>(reinterpret_cast<float*>(e.dbase) + (e.row0 + r) * e.ldd + col) =
-                            *reinterpret_cast<const uint4*>(stage + r * 144 + seg * 16);
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    stage_words[lane * STAGING_PITCH + j] = __float_as_uint(finish<float, SCALE>(__uint_as_float(v[j]), e.scale, e.bias));
-                __syncwarp();
-                const int64_t col = col0 + lane;
+                const int64_t col = colh + (lane & 15);
                 if (col < e.col_end) {
                     float* out = reinterpret_cast<float*>(e.dbase) + e.row0 * e.ldd + col;
-                    for (int r = 0; r < e.rows; ++r) out[r * e.ldd] = __uint_as_float(stage_words[r * STAGING_PITCH + lane]);
+                    for (int r = lane >> 4; r < e.rows; r += 2) out[r * e.ldd] = __uint_as_float(stage_words[r * STAGING_PITCH + (lane & 15)]);
                 }
             }
         }
     }
 }
 
-template <int MODE>
+// Drains this warp's share of the accumulator: 32 rows, every second 32-column chunk. The
+// TMEM load of the next chunk is in flight while the current one is converted and stored.
+template <typename OutT, bool SCALE>
+__device__ __forceinline__ void drain_tile(const EpilogueTile& e, uint8_t* stage, int lane) {
+    if (e.rows <= 0) return;  // warp-uniform
+    auto valid = [&](int c) { return c < BN / 32 && e.col_base + c * 32 < e.col_end; };
+    uint32_t va[32], vb[32];
+    int c = e.chunk0;
+    if (!valid(c)) return;
+    tmem_load_issue(e.taddr0 + c * 32, va);
+    while (true) {
+        tmem_load_wait(va);
+        const int c2 = c + e.chunk_step;
+        const bool more2 = valid(c2);
+        if (more2) tmem_load_issue(e.taddr0 + c2 * 32, vb);
+        store_block<OutT, SCALE>(e, va, e.col_base + c * 32, stage, lane);
+        if (!more2) break;
+        tmem_load_wait(vb);
+        c = c2 + e.chunk_step;
+        const bool more = valid(c);
+        if (more) tmem_load_issue(e.taddr0 + c * 32, va);
+        store_block<OutT, SCALE>(e, vb, e.col_base + c2 * 32, stage, lane);
+        if (!more) break;
+    }
+}
+
+enum { OUT_F16 = 0, OUT_BF16 = 1, OUT_F32 = 2 };
+template <int OUT> struct out_type { using type = __half; };
+template <> struct out_type<OUT_BF16> { using type = __nv_bfloat16; };
+template <> struct out_type<OUT_F32> { using type = float; };
+
+// MODE: operand layout (see the top of the file); OUT: result element type; SCALE: multiply the
+// rounded result by a scalar. All three are compile-time so that the epilogue is branch-free.
+template <int MODE, int OUT, bool SCALE>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KernelArgs g) {
     extern __shared__ uint8_t smem_raw[];
@@ -326,7 +376,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(accf0 + 8 * b, 1);
-            mbar_init(acce0 + 8 * b, kEpilogueWarps);
+            mbar_init(acce0 + 8 * b, g.epi_warps);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -415,7 +465,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (ok) umma_commit(accf0 + 8 * buf);  // accumulator complete
             }
         }
-    } else {
+    } else if (warp - 2 < g.epi_warps) {
         // ------------------------------------------------------------ epilogue --------
         const int ew = warp - 2;                 // staging slot
         const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter+32)
@@ -439,26 +489,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                  : __half2float(static_cast<const __half*>(g.bias)[row0 + lane]);
             }
             EpilogueTile e;
-            e.dbase = static_cast<uint8_t*>(g.d) + static_cast<size_t>(batch) * g.d_batch * (g.d_is_f32 ? 4 : 2);
+            e.dbase = static_cast<uint8_t*>(g.d) + static_cast<size_t>(batch) * g.d_batch * (OUT == OUT_F32 ? 4 : 2);
             e.ldd = g.ldd;
             e.row0 = row0;
             e.rows = static_cast<int>(min(static_cast<int64_t>(32), g.M - row0));
             e.col_base = col_base;
             e.col_end = col_end;
             e.taddr0 = taddr0;
+            e.chunk0 = ew >> 2;
+            e.chunk_step = g.epi_warps >> 2;
             e.bias = bias;
             e.scale = g.scale;
             e.vec_store = g.vec_store;
-            if (g.d_is_f32) {
-                if (g.has_scale) drain_tile<float, true>(e, stage, lane);
-                else drain_tile<float, false>(e, stage, lane);
-            } else if (g.is_bf16) {
-                if (g.has_scale) drain_tile<__nv_bfloat16, true>(e, stage, lane);
-                else drain_tile<__nv_bfloat16, false>(e, stage, lane);
-            } else {
-                if (g.has_scale) drain_tile<__half, true>(e, stage, lane);
-                else drain_tile<__half, false>(e, stage, lane);
-            }
+            drain_tile<typename out_type<OUT>::type, SCALE>(e, stage, lane);
             // this warp has finished reading the accumulator
             tc_fence_before();
             __syncwarp();
@@ -523,20 +566,35 @@ tn_status make_map(CUtensorMap* map, const void* ptr, bool bf16, int64_t inner, 
 bool mult8(int64_t v) { return (v & 7) == 0; }
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-template <int MODE>
-tn_status launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const KernelArgs& g, cudaStream_t stream) {
+template <int MODE, int OUT, bool SCALE>
+tn_status launch_one(const CUtensorMap& map_a, const CUtensorMap& map_b, const KernelArgs& g, cudaStream_t stream) {
     // the opt-in shared-memory size is a per-device attribute of the kernel
     static thread_local int attr_device = -1;
     int dev = 0;
     TN_CUDA(cudaGetDevice(&dev));
     if (attr_device != dev) {
-        TN_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        TN_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<MODE, OUT, SCALE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
         attr_device = dev;
     }
     const int64_t sms = sm_count();
     const int grid = (int)(g.total_tiles < sms ? g.total_tiles : sms);
-    tc_gemm_kernel<MODE><<<grid, kThreads, SMEM_BYTES, stream>>>(map_a, map_b, g);
+    KernelArgs args = g;
+    // A long main loop hides a 4-warp epilogue completely; short ones (HBM-bound shapes) are paced
+    // by the epilogue and get all eight warps.
+    args.epi_warps = g.k_blocks >= 16 ? 4 : 8;
+    if (const char* v = getenv("TN_TC_EPILOGUE_WARPS")) {
+        const int n = atoi(v);
+        if (n == 4 || n == 8) args.epi_warps = n;
+    }
+    tc_gemm_kernel<MODE, OUT, SCALE><<<grid, kThreads, SMEM_BYTES, stream>>>(map_a, map_b, args);
     return after_launch("tc_gemm_kernel");
+}
+
+template <int MODE>
+tn_status launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const KernelArgs& g, cudaStream_t stream) {
+    if (g.d_is_f32) return g.has_scale ? launch_one<MODE, OUT_F32, true>(map_a, map_b, g, stream) : launch_one<MODE, OUT_F32, false>(map_a, map_b, g, stream);
+    if (g.is_bf16) return g.has_scale ? launch_one<MODE, OUT_BF16, true>(map_a, map_b, g, stream) : launch_one<MODE, OUT_BF16, false>(map_a, map_b, g, stream);
+    return g.has_scale ? launch_one<MODE, OUT_F16, true>(map_a, map_b, g, stream) : launch_one<MODE, OUT_F16, false>(map_a, map_b, g, stream);
 }
 
 }  // namespace

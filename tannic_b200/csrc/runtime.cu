@@ -121,6 +121,15 @@ static tn_status ensure_pool(int id) {
 }
 
 tn_status scratch_alloc(void** ptr, size_t nbytes, cudaStream_t stream) {
+    int dev = 0;
+    TN_CUDA(cudaGetDevice(&dev));
+    {
+        Runtime& rt = runtime();
+        std::lock_guard<std::mutex> lock(rt.mutex);
+        rt.ensure_counted();
+        if (dev < 0 || dev >= (int)rt.devices.size()) return fail(TN_ERROR, "no CUDA device is current");
+    }
+    TN_TRY(ensure_pool(dev));  // keep freed scratch in the pool instead of returning it to the driver
     TN_CUDA(cudaMallocAsync(ptr, nbytes, stream));
     return TN_SUCCESS;
 }
