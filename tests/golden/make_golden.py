@@ -1,0 +1,84 @@
+"""Generates golden_reference.npz: inputs and outputs of the reference's own CPU kernels
+(oracle/_ref, compiled from the reference sources) for the dtypes its test-suite never exercises
+(fp16, bf16, int32). Run where oracle/_ref exists:
+
+    python tests/golden/make_golden.py
+
+Half-precision arrays are stored as their uint16 bit patterns. Cases named *_wide hold the result
+of the reference's float-accumulating instantiation on exactly up-converted operands, rounded once to
+the storage type — the behaviour the device path implements; the others are the literal result.
+"""
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+import oracle  # noqa: E402
+
+
+def raw(t):
+    t = t.contiguous()
+    if t.dtype in (torch.float16, torch.bfloat16):
+        return t.view(torch.int16).numpy().view(np.uint16)
+    return t.numpy()
+
+
+def main():
+    assert oracle.ref() is not None, "build oracle/_ref first (make -C oracle ref)"
+    out = {}
+
+    def put(name, **arrays):
+        for k, v in arrays.items():
+            out[f"{name}/{k}"] = raw(v)
+            out[f"{name}/{k}.dtype"] = np.array(str(v.dtype).replace("torch.", ""))
+
+    R = "ref"
+    # config 2 in miniature: Z = log(X) + Y*Y - exp(X), fp16, row-broadcast Y
+    x = oracle.fill((24, 64), torch.float16, 1, "uniform", 0.1, 4.0)
+    y = oracle.fill((1, 64), torch.float16, 2, "uniform", -2.0, 2.0)
+    z = oracle.binary("sub", oracle.binary("add", oracle.unary("log", x, impl=R), oracle.binary("mul", y, y, impl=R), impl=R),
+                      oracle.unary("exp", x, impl=R), impl=R)
+    put("expr_fp16", x=x, y=y, z=z)
+    xb, yb = x.to(torch.bfloat16), y.to(torch.bfloat16)
+    zb = oracle.binary("sub", oracle.binary("add", oracle.unary("log", xb, impl=R), oracle.binary("mul", yb, yb, impl=R), impl=R),
+                       oracle.unary("exp", xb, impl=R), impl=R)
+    put("expr_bf16", x=xb, y=yb, z=zb)
+    # int32 column-broadcast add
+    a = oracle.fill((40, 48), torch.int32, 3, "uniform", -1000, 1000)
+    b = oracle.fill((40, 1), torch.int32, 4, "uniform", -1000, 1000)
+    put("add_int32", a=a, b=b, z=oracle.binary("add", a, b, impl=R))
+    # bf16 X . W^T: literal (bf16 accumulation) and float-accumulating instantiation
+    xm = oracle.fill((3, 20, 136), torch.bfloat16, 5, "normal", 0.0, 1.0)
+    w = oracle.fill((24, 136), torch.bfloat16, 6, "normal", 0.0, 0.02)
+    put("gemm_bf16", x=xm, w=w, z=oracle.matmul(xm, w.t(), impl=R),
+        z_wide=oracle.matmul(xm, w.t().float(), impl=R).to(torch.bfloat16))
+    q = oracle.fill((2, 3, 19, 64), torch.float16, 7, "normal", 0.0, 1.0)
+    k = oracle.fill((2, 3, 19, 64), torch.float16, 8, "normal", 0.0, 1.0)
+    s = oracle.matmul(q, k.transpose(-1, -2).float(), impl=R).to(torch.float16)
+    put("scores_fp16", q=q, k=k, s_wide=s, s_scaled=oracle.scale(s, 0.125, impl=R))
+    # fp16 conv 3x3 pad 1 and 1x1, literal and float instantiation
+    xc = oracle.fill((2, 16, 9, 8), torch.float16, 9, "normal", 0.0, 1.0)
+    w3 = oracle.fill((8, 16, 3, 3), torch.float16, 10, "normal", 0.0, 0.1)
+    w1 = oracle.fill((24, 16, 1, 1), torch.float16, 11, "normal", 0.0, 0.3)
+    bias = oracle.fill((8,), torch.float16, 12, "uniform", -1.0, 1.0)
+    put("conv_fp16", x=xc, w3=w3, w1=w1, bias=bias,
+        y3=oracle.conv2d(xc, w3, 1, 1, impl=R), y3_wide=oracle.conv2d(xc.float(), w3.float(), 1, 1, impl=R).to(torch.float16),
+        y3b_wide=oracle.conv2d(xc.float(), w3.float(), 1, 1, bias=bias.float(), impl=R).to(torch.float16),
+        y1_wide=oracle.conv2d(xc.float(), w1.float(), 1, 0, impl=R).to(torch.float16),
+        y3s2_wide=oracle.conv2d(xc.float(), w3.float(), 2, 1, impl=R).to(torch.float16))
+    # bf16 row reductions over 197 columns
+    sr = oracle.fill((6, 197), torch.bfloat16, 13, "normal", 0.0, 1.0)
+    put("reduce_bf16", s=sr, argmax=oracle.reduce("argmax", sr, -1, impl=R), argmin=oracle.reduce("argmin", sr, -1, impl=R),
+        sum=oracle.reduce("sum", sr, -1, impl=R), mean=oracle.reduce("mean", sr, -1, impl=R),
+        sum_wide=oracle.reduce("sum", sr.float(), -1, impl=R).to(torch.bfloat16),
+        argmax_axis0=oracle.reduce("argmax", sr, 0, impl=R))
+    path = Path(__file__).resolve().parent / "golden_reference.npz"
+    np.savez_compressed(path, **out)
+    print(f"{len(out) // 2} arrays -> {path} ({path.stat().st_size} bytes)")
+
+
+if __name__ == "__main__":
+    main()

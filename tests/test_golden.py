@@ -1,0 +1,98 @@
+"""Golden vectors produced by the reference's own CPU kernels (tests/golden/golden_reference.npz,
+made by tests/golden/make_golden.py) for fp16 / bf16 / int32, which the reference's test-suite never
+covers. CPU: the C restatement reproduces them bit for bit. GPU (marked): the CUDA path matches the
+float-accumulating results within rtol 1e-2 / atol 1e-2, integers and indices exactly."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+NPZ = np.load(Path(__file__).parent / "golden" / "golden_reference.npz")
+DT = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32, "int32": torch.int32, "int64": torch.int64}
+
+
+def get(case, name):
+    arr = NPZ[f"{case}/{name}"]
+    dt = DT[str(NPZ[f"{case}/{name}.dtype"])]
+    t = torch.from_numpy(arr.view(np.int16) if arr.dtype == np.uint16 else arr.copy())
+    return t.view(dt) if dt in (torch.float16, torch.bfloat16) else t
+
+
+def same(a, b):
+    return a.shape == b.shape and a.dtype == b.dtype and torch.equal(a.contiguous().view(torch.uint8), b.contiguous().view(torch.uint8))
+
+
+def close(got, want, rtol=1e-2, atol=1e-2):
+    g, w = got.double(), want.double()
+    return got.shape == want.shape and bool(((g - w).abs() <= atol + rtol * w.abs()).all())
+
+
+def expr(be_unary, be_binary, x, y):
+    return be_binary("sub", be_binary("add", be_unary("log", x), be_binary("mul", y, y)), be_unary("exp", x))
+
+
+def test_port_matches_golden_expression_and_add():
+    for case in ("expr_fp16", "expr_bf16"):
+        x, y = get(case, "x"), get(case, "y")
+        got = expr(oracle.unary, oracle.binary, x, y)
+        w = get(case, "z")
+        # libm may differ from the build that made the fixture by an ulp of the storage type
+        assert close(got, w, rtol=2 ** -7, atol=1e-3)
+    assert same(oracle.binary("add", get("add_int32", "a"), get("add_int32", "b")), get("add_int32", "z"))
+
+
+def test_port_matches_golden_gemm_conv_reductions():
+    x, w = get("gemm_bf16", "x"), get("gemm_bf16", "w")
+    assert same(oracle.matmul(x, w.t(), acc=oracle.ACC_STORAGE), get("gemm_bf16", "z"))
+    assert same(oracle.matmul(x, w.t(), acc=oracle.ACC_WIDE), get("gemm_bf16", "z_wide"))
+    q, k = get("scores_fp16", "q"), get("scores_fp16", "k")
+    s = oracle.matmul(q, k.transpose(-1, -2), acc=oracle.ACC_WIDE)
+    assert same(s, get("scores_fp16", "s_wide"))
+    assert same(oracle.scale(s, 0.125), get("scores_fp16", "s_scaled"))
+    xc, w3, w1, bias = (get("conv_fp16", n) for n in ("x", "w3", "w1", "bias"))
+    assert same(oracle.conv2d(xc, w3, 1, 1, acc=oracle.ACC_STORAGE), get("conv_fp16", "y3"))
+    assert same(oracle.conv2d(xc, w3, 1, 1, acc=oracle.ACC_WIDE), get("conv_fp16", "y3_wide"))
+    assert same(oracle.conv2d(xc, w3, 1, 1, bias=bias, acc=oracle.ACC_WIDE), get("conv_fp16", "y3b_wide"))
+    assert same(oracle.conv2d(xc, w1, 1, 0, acc=oracle.ACC_WIDE), get("conv_fp16", "y1_wide"))
+    assert same(oracle.conv2d(xc, w3, 2, 1, acc=oracle.ACC_WIDE), get("conv_fp16", "y3s2_wide"))
+    s = get("reduce_bf16", "s")
+    assert same(oracle.reduce("argmax", s, -1), get("reduce_bf16", "argmax"))
+    assert same(oracle.reduce("argmin", s, -1), get("reduce_bf16", "argmin"))
+    assert same(oracle.reduce("argmax", s, 0), get("reduce_bf16", "argmax_axis0"))
+    assert same(oracle.reduce("sum", s, -1, acc=oracle.ACC_STORAGE), get("reduce_bf16", "sum"))
+    assert same(oracle.reduce("mean", s, -1, acc=oracle.ACC_STORAGE), get("reduce_bf16", "mean"))
+    assert same(oracle.reduce("sum", s, -1, acc=oracle.ACC_WIDE), get("reduce_bf16", "sum_wide"))
+
+
+@pytest.mark.gpu
+def test_cuda_matches_golden():
+    from tannic_b200 import _abi as A
+    from tannic_b200 import ops as tb
+    d = lambda t: t.cuda()  # noqa: E731
+    for case in ("expr_fp16", "expr_bf16"):
+        x, y = d(get(case, "x")), d(get(case, "y"))
+        nodes = [(A.OP_LOG, 0, 0), (A.OP_MUL, 1, 1), (A.OP_ADD, 4, 5), (A.OP_EXP, 0, 0), (A.OP_SUB, 6, 7)]
+        assert close(tb.program([x, y], nodes).cpu(), get(case, "z"))
+        assert close(tb.sub(tb.add(tb.log(x), tb.mul(y, y)), tb.exp(x)).cpu(), get(case, "z"))
+    assert same(tb.add(d(get("add_int32", "a")), d(get("add_int32", "b"))).cpu(), get("add_int32", "z"))
+    x, w = d(get("gemm_bf16", "x")), d(get("gemm_bf16", "w"))
+    assert close(tb.matmul(x, w.t()).cpu(), get("gemm_bf16", "z_wide"))
+    q, k = d(get("scores_fp16", "q")), d(get("scores_fp16", "k"))
+    assert close(tb.matmul(q, k.transpose(-1, -2)).cpu(), get("scores_fp16", "s_wide"))
+    assert close(tb.matmul(q, k.transpose(-1, -2), scale_by=0.125).cpu(), get("scores_fp16", "s_scaled"))
+    xc, w3, w1, bias = (d(get("conv_fp16", n)) for n in ("x", "w3", "w1", "bias"))
+    assert close(tb.convolve2D(xc, w3, 1, 1).cpu(), get("conv_fp16", "y3_wide"))
+    assert close(tb.convolve2D(xc, w3, 1, 1, bias=bias).cpu(), get("conv_fp16", "y3b_wide"))
+    assert close(tb.convolve2D(xc, w1, 1, 0).cpu(), get("conv_fp16", "y1_wide"))
+    assert close(tb.convolve2D(xc, w3, 2, 1).cpu(), get("conv_fp16", "y3s2_wide"))
+    s = d(get("reduce_bf16", "s"))
+    assert same(tb.argmax(s, -1).cpu(), get("reduce_bf16", "argmax"))
+    assert same(tb.argmin(s, -1).cpu(), get("reduce_bf16", "argmin"))
+    assert same(tb.argmax(s, 0).cpu(), get("reduce_bf16", "argmax_axis0"))
+    assert close(tb.sum(s, -1).cpu(), get("reduce_bf16", "sum_wide"))
+    mx, sm, am = tb.reduce_stats(s, -1)
+    assert same(am.cpu(), get("reduce_bf16", "argmax")) and close(sm.cpu(), get("reduce_bf16", "sum_wide"))
+    assert tb.device_errors() == 0
