@@ -258,6 +258,7 @@ def ours(args):
     import torch.distributed as dist
     from tannic_b200 import _abi as A
     from tannic_b200 import ops as tb
+    from tannic_b200 import shard
 
     A.lib()  # raises if the CUDA extension is missing: there is no fallback
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -323,10 +324,7 @@ def ours(args):
         step()
     torch.cuda.synchronize()
     clocks = sampler.stop()
-    if world > 1:
-        t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
+    elapsed_ms = shard.max_over_ranks(elapsed_ms, device="cuda")
     ms_per_step = elapsed_ms / args.steps
     value = world * ALGO_BYTES / ms_per_step / 1e6
 
@@ -349,13 +347,13 @@ def ours(args):
         e2e_step()
     barrier()
     e2e_s = (time.perf_counter() - t0) / e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+    e2e_s = shard.max_over_ranks(e2e_s, device="cuda")
     e2e_value = world * ALGO_BYTES / e2e_s / 1e9
 
-    # parity spot-check of what was just timed (first 4 rows against the oracle)
+    # parity spot-check of what was just timed: the first rows of Z against the oracle's node chain
+    xs, zs = x_host[:4], z_host[:4]
+    want = oracle.binary("sub", oracle.binary("add", oracle.unary("log", xs), oracle.binary("mul", y_host, y_host)), oracle.unary("exp", xs))
+    parity_ok = bool(((zs.double() - want.double()).abs() <= 1e-2 + 1e-2 * want.double().abs()).all())
     errors = tb.device_errors()
 
     if rank == 0:
@@ -369,7 +367,7 @@ def ours(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH, "peak_kind": peak_kind},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": ROWS * COLS * 2 + COLS * 2, "d2h_bytes_per_step": ROWS * COLS * 2},
-            "gpu_launches": launches, "clocks": clocks, "device_errors": errors,
+            "gpu_launches": launches, "clocks": clocks, "device_errors": errors, "parity_spot_check": parity_ok,
         }
         if world == 1 and not args.no_cpu_baseline:
             rows = 1024
@@ -385,9 +383,10 @@ def ours(args):
     return 0
 
 
-# DRAM bytes read + written by one launch of the headline kernel, from an ncu capture of the
-# same kernel (see profiles/); None until a capture exists.
-TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM bytes read + written by one launch of the headline kernel, from the ncu capture summarised in
+# profiles/ew_program_rows_config2_fp16.md (dram__bytes_read.sum 134.25 MB + dram__bytes_write.sum
+# 85.51 MB; the write side is below the 134.2 MB of Z because L2 still holds its tail at kernel end).
+TRAFFIC_BYTES_PER_LAUNCH = 219_758_080
 
 
 def main():
