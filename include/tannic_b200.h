@@ -274,7 +274,7 @@ tn_status tn_cpy(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream);
 tn_status tn_allclose(const tn_tensor_t* a, const tn_tensor_t* b, tn_stream_t stream, double rtol,
                       double atol, int* close);
 
-/* Number of CTAs of the tensor-core kernels that gave up on a bounded wait since load (0 in a
+/* Number of CTAs (tensor-core and staged-reduction kernels) that gave up on a bounded wait since load (0 in a
  * healthy run); synchronises the device. The reference has no device-side waits to bound. */
 tn_status tn_device_errors(unsigned int* count);
 

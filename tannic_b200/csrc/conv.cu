@@ -92,6 +92,43 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc(const uint16_t* __restrict__
     }
 }
 
+// Same re-layout for a dense 16-bit NCHW tensor whose image size H*W is a multiple of 8: both
+// global sides move 16 bytes per thread. A 64-channel x 64-pixel tile is held as 64 rows of 32
+// words (a word = two neighbouring pixels of one channel). Row r sits at row index
+// (r % 8) * 8 + r / 8 and its words are XOR-swizzled by 4 * (r / 8), which makes the 16-byte row
+// stores and the per-channel word gathers of the second phase both free of bank conflicts.
+__global__ void __launch_bounds__(256) nchw_to_nhwc_vec(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, int64_t C,
+                                                        int64_t HW) {
+    __shared__ __align__(16) uint32_t tile[64 * 32];
+    const int64_t p0 = (int64_t)blockIdx.x * 64, c0 = (int64_t)blockIdx.y * 64, n = blockIdx.z;
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+        const int v = threadIdx.x + it * 256;
+        const int r = v >> 3, seg = v & 7;
+        const int64_t c = c0 + r, p = p0 + seg * 8;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (c < C && p < HW) val = __ldg(reinterpret_cast<const uint4*>(x + (n * C + c) * HW + p));
+        const int rp = (r & 7) * 8 + (r >> 3);
+        *reinterpret_cast<uint4*>(&tile[rp * 32 + ((4 * seg) ^ (4 * (r >> 3)))]) = val;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int cseg = lane & 7, pp = 4 * warp + (lane >> 3);  // pixel pair 0..31 of the tile
+    uint32_t w[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) w[k] = tile[(k * 8 + cseg) * 32 + (pp ^ (4 * cseg))];
+    uint4 even, odd;  // pixel 2*pp takes the low halves, pixel 2*pp+1 the high halves
+    even.x = __byte_perm(w[0], w[1], 0x5410); odd.x = __byte_perm(w[0], w[1], 0x7632);
+    even.y = __byte_perm(w[2], w[3], 0x5410); odd.y = __byte_perm(w[2], w[3], 0x7632);
+    even.z = __byte_perm(w[4], w[5], 0x5410); odd.z = __byte_perm(w[4], w[5], 0x7632);
+    even.w = __byte_perm(w[6], w[7], 0x5410); odd.w = __byte_perm(w[6], w[7], 0x7632);
+    const int64_t p = p0 + 2 * pp, c = c0 + cseg * 8;
+    if (c < C && p < HW) {
+        *reinterpret_cast<uint4*>(out + (n * HW + p) * C + c) = even;
+        *reinterpret_cast<uint4*>(out + (n * HW + p + 1) * C + c) = odd;  // HW is even
+    }
+}
+
 // w[co, ci, kh, kw] (any strides) -> out[kh*Kw + kw][co][ci]
 __global__ void __launch_bounds__(256) pack_weights(const uint16_t* __restrict__ w, uint16_t* __restrict__ out, int64_t Cout,
                                                     int64_t Cin, int64_t Kh, int64_t Kw, int64_t ws0, int64_t ws1, int64_t ws2,
@@ -206,7 +243,10 @@ tn_status conv_impl(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_
             uint16_t* xh = reinterpret_cast<uint16_t*>(scratch);
             uint16_t* wp = reinterpret_cast<uint16_t*>(scratch + x_padded);
             const dim3 tgrid((unsigned)ceil_div(g.H * g.W, 64), (unsigned)ceil_div(g.Cin, 64), (unsigned)g.N);
-            nchw_to_nhwc<<<tgrid, 256, 0, s>>>(static_cast<const uint16_t*>(g.x), xh, g.Cin, g.H, g.W, g.xs[0], g.xs[1], g.xs[2], g.xs[3]);
+            if (dense_nchw(x) && (g.H * g.W) % 8 == 0 && (reinterpret_cast<uintptr_t>(g.x) & 15) == 0)
+                nchw_to_nhwc_vec<<<tgrid, 256, 0, s>>>(static_cast<const uint16_t*>(g.x), xh, g.Cin, g.H * g.W);
+            else
+                nchw_to_nhwc<<<tgrid, 256, 0, s>>>(static_cast<const uint16_t*>(g.x), xh, g.Cin, g.H, g.W, g.xs[0], g.xs[1], g.xs[2], g.xs[3]);
             tn_status st = after_launch("nchw_to_nhwc");
             if (st == TN_SUCCESS) {
                 int64_t wblocks = ceil_div(g.Kh * g.Kw * g.Cout * g.Cin, 256);

@@ -7,6 +7,7 @@ namespace tnb {
 
 bool read_host_scalar(const tn_scalar_t* sc, double* f, int64_t* i);
 tn_status tc_abort_count(unsigned int* count);
+tn_status reduce_abort_count(unsigned int* count);
 
 namespace {
 
@@ -278,7 +279,11 @@ tn_status tn_gemm_scaled(const tn_tensor_t* a, const tn_tensor_t* b, const tn_sc
 
 tn_status tn_device_errors(unsigned int* count) {
     if (!count) return fail(TN_ERROR, "null count");
-    return tc_abort_count(count);
+    unsigned int tc = 0, red = 0;
+    TN_TRY(tc_abort_count(&tc));
+    TN_TRY(reduce_abort_count(&red));
+    *count = tc + red;
+    return TN_SUCCESS;
 }
 
 }  // extern "C"

@@ -6,6 +6,10 @@
 //   reduce_rows_warp   dense source, last axis: one warp per row, 16-byte loads where the row
 //                      is aligned, shuffle combine; rows may start at any element offset
 //                      (197-wide bf16 rows have a 394-byte pitch);
+//   reduce_rows_staged same geometry for SHORT rows (<= 1 KiB, e.g. the 197-wide score rows): a CTA
+//                      brings a contiguous chunk of whole rows into shared memory with one TMA
+//                      bulk copy (double-buffered), then one thread reduces one row serially,
+//                      in ascending order, without any shuffle;
 //   reduce_rows_block  same geometry for long rows: one CTA per row;
 //   reduce_split       few, very long rows: every row is cut into segments whose partial
 //                      results go to scratch memory, a second kernel combines them;
@@ -161,6 +165,107 @@ __global__ void __launch_bounds__(kThreads) reduce_rows_warp(const T* __restrict
         warp_combine(st);
         if (lane == 0) write_out(st, out, r, len, len > 0 ? row[0] : T());
     }
+}
+
+// ---- staged short rows -------------------------------------------------------------------
+constexpr int kStagedThreads = 128;
+constexpr uint32_t kStagedSpinLimit = 1u << 22;  // polls of an mbarrier before a CTA gives up
+
+__device__ unsigned int g_reduce_aborts = 0;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+// Bounded wait for the bulk copy that fills a staging buffer.
+__device__ __forceinline__ bool wait_bulk(uint32_t bar, uint32_t parity) {
+    for (uint32_t it = 0; it < kStagedSpinLimit; ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        if (it > 4096) __nanosleep(32);
+    }
+    return false;
+}
+
+// rows_per_chunk rows of `len` elements are contiguous in memory; chunk k starts at row
+// k * rows_per_chunk. Whole chunks whose byte size is a multiple of 16 arrive by TMA bulk copy,
+// the ragged last chunk by ordinary loads.
+template <typename T, bool SUM, bool ARG, bool MIN>
+__global__ void __launch_bounds__(kStagedThreads) reduce_rows_staged(const T* __restrict__ src, int64_t rows, int len,
+                                                                    int rows_per_chunk, Outputs out) {
+    extern __shared__ __align__(128) unsigned char staged_smem[];
+    using A = typename acc_of<T>::type;
+    using C = typename cmp_of<T>::type;
+    const uint32_t chunk_bytes = static_cast<uint32_t>(rows_per_chunk) * len * sizeof(T);
+    const uint32_t buf_stride = (chunk_bytes + 127u) & ~127u;
+    T* buf[2] = {reinterpret_cast<T*>(staged_smem), reinterpret_cast<T*>(staged_smem + buf_stride)};
+    uint64_t* bars = reinterpret_cast<uint64_t*>(staged_smem + 2 * buf_stride);
+    const uint32_t bar0 = smem_addr(bars);
+    const int64_t chunks = (rows + rows_per_chunk - 1) / rows_per_chunk;
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0 + 8) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    auto issue = [&](int64_t chunk, int b) {
+        // one elected thread starts the copy of a full chunk; the barrier completes on the bytes
+        const int64_t first = chunk * rows_per_chunk;
+        if (first + rows_per_chunk <= rows && threadIdx.x == 0) {
+            const uint32_t bar = bar0 + 8 * b;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(chunk_bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(smem_addr(buf[b])), "l"(src + first * len), "r"(chunk_bytes), "r"(bar) : "memory");
+        }
+    };
+    uint32_t phase[2] = {0, 0};
+    int b = 0;
+    bool ok = true;
+    int64_t chunk = blockIdx.x;
+    if (chunk < chunks) issue(chunk, 0);
+    for (; chunk < chunks; chunk += gridDim.x, b ^= 1) {
+        const int64_t next = chunk + gridDim.x;
+        if (next < chunks) issue(next, b ^ 1);  // the other buffer was released by the barrier below
+        const int64_t first = chunk * rows_per_chunk;
+        const bool full = first + rows_per_chunk <= rows;
+        const int here = static_cast<int>(full ? rows_per_chunk : rows - first);
+        if (full) {
+            if (ok && !wait_bulk(bar0 + 8 * b, phase[b])) ok = false;
+            phase[b] ^= 1;
+        } else {
+            const int64_t n = static_cast<int64_t>(here) * len;
+            for (int64_t i = threadIdx.x; i < n; i += kStagedThreads) buf[b][i] = src[first * len + i];
+            __syncthreads();
+        }
+        if (ok && static_cast<int>(threadIdx.x) < here) {
+            const T* row = buf[b] + static_cast<int64_t>(threadIdx.x) * len;
+            A sum = A(0);
+            C best = cmp_init<C, MIN>();
+            int idx = -1;
+#pragma unroll 4
+            for (int j = 0; j < len; ++j) {
+                const T raw = row[j];
+                if constexpr (SUM) sum += to_compute<A>(raw);
+                if constexpr (ARG) {
+                    const C v = to_compute<C>(raw);
+                    if (MIN ? (v < best) : (v > best)) { best = v; idx = j; }
+                }
+            }
+            const int64_t o = first + threadIdx.x;
+            if constexpr (SUM) {
+                if (out.sum) static_cast<T*>(out.sum)[o] = from_compute<T, A>(out.mean ? sum / static_cast<A>(len) : sum);
+            }
+            if constexpr (ARG) {
+                if (out.index) out.index[o] = idx < 0 ? 0 : idx;
+                if (out.value) static_cast<T*>(out.value)[o] = idx < 0 ? row[0] : from_compute<T, C>(best);
+            }
+        }
+        __syncthreads();  // everyone is done with buf[b] before it is refilled two iterations on
+    }
+    if (!ok && threadIdx.x == 0) atomicAdd(&g_reduce_aborts, 1u);
 }
 
 template <typename T, bool SUM, bool ARG, bool MIN>
@@ -337,6 +442,28 @@ tn_status launch(const tn_tensor_t* src, int axis, Outputs out, cudaStream_t s) 
             tn_status fr = scratch_free(scratch, s);
             return st != TN_SUCCESS ? st : fr;
         }
+        if (row_bytes <= 1024 && len >= 8 && total >= 2048 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+            // whole rows staged in shared memory: rows per chunk is a multiple of 16 so that a
+            // chunk is a multiple of 16 bytes for any row length
+            int rpc = (int)((int64_t(44) << 10) / row_bytes) & ~15;
+            if (rpc > kStagedThreads) rpc = kStagedThreads;
+            if (rpc >= 16) {
+                const size_t buf = ((size_t)rpc * row_bytes + 127) & ~size_t(127);
+                const size_t smem = 2 * buf + 16;
+                static thread_local int attr_device = -1;
+                int dev = 0;
+                TN_CUDA(cudaGetDevice(&dev));
+                if (attr_device != dev) {
+                    TN_CUDA(cudaFuncSetAttribute(reduce_rows_staged<T, SUM, ARG, MIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 << 10));
+                    attr_device = dev;
+                }
+                const int64_t chunks = ceil_div(total, rpc);
+                int64_t grid = (int64_t)sm_count() * 2;
+                if (grid > chunks) grid = chunks;
+                reduce_rows_staged<T, SUM, ARG, MIN><<<(unsigned)grid, kStagedThreads, smem, s>>>(p, total, (int)len, rpc, out);
+                return after_launch("reduce_rows_staged");
+            }
+        }
         if (row_bytes >= 16384) {
             const int grid = (int)(total < cap ? total : cap);
             reduce_rows_block<T, SUM, ARG, MIN><<<grid, kThreads, 0, s>>>(p, total, len, out);
@@ -457,6 +584,12 @@ tn_status launch_sum_fixed(const T* p, int64_t rows, int64_t len, Outputs out, v
 }
 
 }  // namespace
+
+tn_status reduce_abort_count(unsigned int* count) {
+    TN_CUDA(cudaMemcpyFromSymbol(count, g_reduce_aborts, sizeof(unsigned int)));
+    return TN_SUCCESS;
+}
+
 }  // namespace tnb
 
 using namespace tnb;

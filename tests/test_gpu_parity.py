@@ -250,6 +250,27 @@ def test_reduce_keepdim_and_stats():
     assert_close(sm, oracle.reduce("sum", x, -1, acc=oracle.ACC_WIDE))
 
 
+@pytest.mark.parametrize("dtype,shape", [(torch.bfloat16, (12, 197, 197)), (torch.float16, (4099, 64)), (torch.float32, (3001, 100)),
+                                         (torch.int32, (2500, 33)), (torch.float64, (2100, 8)), (torch.int8, (2048, 1000))])
+def test_reductions_many_short_rows_staged_in_shared_memory(dtype, shape):
+    """Enough short rows to take the staged kernel (whole rows brought in by bulk copies, one
+    thread per row); row counts that are not a multiple of the chunk exercise the ragged tail."""
+    x = gen(shape, dtype, 60, -2.0, 2.0)
+    dx = dev(x)
+    for kind in ("argmax", "argmin", "max"):
+        assert_same(getattr(tb, kind)(dx, -1), oracle.reduce(kind, x, -1))
+    want_sum = oracle.reduce("sum", x, -1, acc=oracle.ACC_WIDE)
+    if dtype in INTS:
+        assert_same(tb.sum(dx, -1), want_sum)
+    else:
+        assert_close(tb.sum(dx, -1), want_sum)
+        assert_close(tb.mean(dx, -1), oracle.reduce("mean", x, -1, acc=oracle.ACC_WIDE))
+    mx, sm, am = tb.reduce_stats(dx, -1)
+    assert_same(am, oracle.reduce("argmax", x, -1))
+    assert_same(mx, oracle.reduce("max", x, -1))
+    assert tb.device_errors() == 0
+
+
 def test_reduce_split_path_for_few_long_rows():
     x = gen((2, 1 << 20), torch.float32, 25, -1.0, 1.0)
     assert_close(tb.sum(dev(x), -1), oracle.reduce("sum", x, -1, acc=oracle.ACC_WIDE))
