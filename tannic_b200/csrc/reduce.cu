@@ -7,9 +7,8 @@
 //                      is aligned, shuffle combine; rows may start at any element offset
 //                      (197-wide bf16 rows have a 394-byte pitch);
 //   reduce_rows_staged same geometry for SHORT rows (<= 1 KiB, e.g. the 197-wide score rows): a CTA
-//                      brings a contiguous chunk of whole rows into shared memory with one TMA
-//                      bulk copy (double-buffered), then one thread reduces one row serially,
-//                      in ascending order, without any shuffle;
+//                      brings a contiguous chunk of whole rows into shared memory with 16-byte
+//                      asynchronous copies (double-buffered), then a few lanes reduce each row;
 //   reduce_rows_block  same geometry for long rows: one CTA per row;
 //   reduce_split       few, very long rows: every row is cut into segments whose partial
 //                      results go to scratch memory, a second kernel combines them;
@@ -20,6 +19,7 @@
 
 #include <cfloat>
 #include <climits>
+#include <cstdlib>
 #include <mutex>
 
 namespace tnb {
@@ -168,104 +168,118 @@ __global__ void __launch_bounds__(kThreads) reduce_rows_warp(const T* __restrict
 }
 
 // ---- staged short rows -------------------------------------------------------------------
-constexpr int kStagedThreads = 128;
-constexpr uint32_t kStagedSpinLimit = 1u << 22;  // polls of an mbarrier before a CTA gives up
+constexpr int kStagedThreads = 512;
 
-__device__ unsigned int g_reduce_aborts = 0;
+__device__ unsigned int g_reduce_aborts = 0;  // no bounded waits remain in this file; kept for the error counter
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
-// Bounded wait for the bulk copy that fills a staging buffer.
-__device__ __forceinline__ bool wait_bulk(uint32_t bar, uint32_t parity) {
-    for (uint32_t it = 0; it < kStagedSpinLimit; ++it) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-        if (done) return true;
-        if (it > 4096) __nanosleep(32);
-    }
-    return false;
-}
-
 // rows_per_chunk rows of `len` elements are contiguous in memory; chunk k starts at row
-// k * rows_per_chunk. Whole chunks whose byte size is a multiple of 16 arrive by TMA bulk copy,
-// the ragged last chunk by ordinary loads.
+// k * rows_per_chunk. A chunk (a multiple of 16 bytes, 16-byte aligned because rows_per_chunk is a
+// multiple of 16) is brought into shared memory with per-thread 16-byte asynchronous copies
+// (cp.async), double-buffered: the copy of the next chunk is in flight while the current one is
+// reduced. (A single TMA bulk copy per chunk was measured at 3.9 TB/s at best; the per-thread
+// copies keep many more requests in flight.) The ragged last chunk uses ordinary loads.
+// `lanes` (a power of two <= 32) threads share a row: lane q visits elements q, q + lanes, ...
+// in ascending order and the partial results are merged with shuffles (lowest index wins ties).
 template <typename T, bool SUM, bool ARG, bool MIN>
 __global__ void __launch_bounds__(kStagedThreads) reduce_rows_staged(const T* __restrict__ src, int64_t rows, int len,
-                                                                    int rows_per_chunk, Outputs out) {
+                                                                    int rows_per_chunk, int lanes, Outputs out) {
     extern __shared__ __align__(128) unsigned char staged_smem[];
     using A = typename acc_of<T>::type;
     using C = typename cmp_of<T>::type;
     const uint32_t chunk_bytes = static_cast<uint32_t>(rows_per_chunk) * len * sizeof(T);
     const uint32_t buf_stride = (chunk_bytes + 127u) & ~127u;
-    T* buf[2] = {reinterpret_cast<T*>(staged_smem), reinterpret_cast<T*>(staged_smem + buf_stride)};
-    uint64_t* bars = reinterpret_cast<uint64_t*>(staged_smem + 2 * buf_stride);
-    const uint32_t bar0 = smem_addr(bars);
+    auto buffer = [&](int b) { return reinterpret_cast<T*>(staged_smem + static_cast<size_t>(b) * buf_stride); };
     const int64_t chunks = (rows + rows_per_chunk - 1) / rows_per_chunk;
-    if (threadIdx.x == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0 + 8) : "memory");
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
+    const uint32_t vectors = chunk_bytes >> 4;
     auto issue = [&](int64_t chunk, int b) {
-        // one elected thread starts the copy of a full chunk; the barrier completes on the bytes
+        // every thread starts its share of the 16-byte copies of a full chunk, then closes the group
         const int64_t first = chunk * rows_per_chunk;
-        if (first + rows_per_chunk <= rows && threadIdx.x == 0) {
-            const uint32_t bar = bar0 + 8 * b;
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(chunk_bytes) : "memory");
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                         ::"r"(smem_addr(buf[b])), "l"(src + first * len), "r"(chunk_bytes), "r"(bar) : "memory");
+        if (chunk < chunks && first + rows_per_chunk <= rows) {
+            const unsigned char* g = reinterpret_cast<const unsigned char*>(src + first * len);
+            const uint32_t sbase = smem_addr(buffer(b));
+            for (uint32_t v = threadIdx.x; v < vectors; v += kStagedThreads)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sbase + v * 16), "l"(g + static_cast<size_t>(v) * 16) : "memory");
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    uint32_t phase[2] = {0, 0};
     int b = 0;
-    bool ok = true;
     int64_t chunk = blockIdx.x;
-    if (chunk < chunks) issue(chunk, 0);
+    issue(chunk, 0);
     for (; chunk < chunks; chunk += gridDim.x, b ^= 1) {
-        const int64_t next = chunk + gridDim.x;
-        if (next < chunks) issue(next, b ^ 1);  // the other buffer was released by the barrier below
+        issue(chunk + gridDim.x, b ^ 1);  // the other buffer was released by the barrier that ended the last pass
         const int64_t first = chunk * rows_per_chunk;
         const bool full = first + rows_per_chunk <= rows;
         const int here = static_cast<int>(full ? rows_per_chunk : rows - first);
         if (full) {
-            if (ok && !wait_bulk(bar0 + 8 * b, phase[b])) ok = false;
-            phase[b] ^= 1;
+            asm volatile("cp.async.wait_group 1;" ::: "memory");  // all but the newest group have landed
         } else {
             const int64_t n = static_cast<int64_t>(here) * len;
-            for (int64_t i = threadIdx.x; i < n; i += kStagedThreads) buf[b][i] = src[first * len + i];
-            __syncthreads();
+            for (int64_t i = threadIdx.x; i < n; i += kStagedThreads) buffer(b)[i] = src[first * len + i];
         }
-        if (ok && static_cast<int>(threadIdx.x) < here) {
-            const T* row = buf[b] + static_cast<int64_t>(threadIdx.x) * len;
+        __syncthreads();
+        {
+            const int r = static_cast<int>(threadIdx.x) / lanes, q = static_cast<int>(threadIdx.x) % lanes;
+            const bool active = r < here;
+            const T* row = buffer(b) + static_cast<int64_t>(active ? r : 0) * len;
             A sum = A(0);
             C best = cmp_init<C, MIN>();
-            int idx = -1;
-#pragma unroll 4
-            for (int j = 0; j < len; ++j) {
-                const T raw = row[j];
-                if constexpr (SUM) sum += to_compute<A>(raw);
+            int idx = INT_MAX;
+            auto feed = [&](T raw, int j, A& acc) {
+                if constexpr (SUM) acc += to_compute<A>(raw);
                 if constexpr (ARG) {
                     const C v = to_compute<C>(raw);
                     if (MIN ? (v < best) : (v > best)) { best = v; idx = j; }
                 }
+            };
+            if (active) {
+                if constexpr (sizeof(T) == 2) {
+                    // 16-bit elements are read two at a time as 32-bit words. A row that starts on an
+                    // odd element is peeled by one; lane 0 takes the peeled head and a leftover tail,
+                    // so every lane still meets its indices in ascending order.
+                    const int off = static_cast<int>((reinterpret_cast<uintptr_t>(row) >> 1) & 1);
+                    const int npairs = (len - off) >> 1;
+                    const uint32_t* words = reinterpret_cast<const uint32_t*>(row + off);
+                    A sum_hi = A(0);
+                    if (off && q == 0) feed(row[0], 0, sum);
+#pragma unroll 4
+                    for (int pr = q; pr < npairs; pr += lanes) {
+                        const uint32_t w = words[pr];
+                        const uint16_t lo = static_cast<uint16_t>(w & 0xffffu), hi = static_cast<uint16_t>(w >> 16);
+                        feed(*reinterpret_cast<const T*>(&lo), off + 2 * pr, sum);
+                        feed(*reinterpret_cast<const T*>(&hi), off + 2 * pr + 1, sum_hi);
+                    }
+                    if (((len - off) & 1) && q == 0) feed(row[len - 1], len - 1, sum);
+                    if constexpr (SUM) sum += sum_hi;
+                } else {
+#pragma unroll 4
+                    for (int j = q; j < len; j += lanes) feed(row[j], j, sum);
+                }
             }
-            const int64_t o = first + threadIdx.x;
-            if constexpr (SUM) {
-                if (out.sum) static_cast<T*>(out.sum)[o] = from_compute<T, A>(out.mean ? sum / static_cast<A>(len) : sum);
+            // rows never straddle a warp (lanes divides 32): merge the lanes of a row
+            for (int m = lanes >> 1; m > 0; m >>= 1) {
+                if constexpr (SUM) sum += shfl_xor(sum, m);
+                if constexpr (ARG) {
+                    const C ob = shfl_xor(best, m);
+                    const int oi = __shfl_xor_sync(0xffffffffu, idx, m);
+                    if ((MIN ? (ob < best) : (ob > best)) || (ob == best && oi < idx)) { best = ob; idx = oi; }
+                }
             }
-            if constexpr (ARG) {
-                if (out.index) out.index[o] = idx < 0 ? 0 : idx;
-                if (out.value) static_cast<T*>(out.value)[o] = idx < 0 ? row[0] : from_compute<T, C>(best);
+            if (active && q == 0) {
+                const int64_t o = first + r;
+                if constexpr (SUM) {
+                    if (out.sum) static_cast<T*>(out.sum)[o] = from_compute<T, A>(out.mean ? sum / static_cast<A>(len) : sum);
+                }
+                if constexpr (ARG) {
+                    if (out.index) out.index[o] = idx == INT_MAX ? 0 : idx;
+                    if (out.value) static_cast<T*>(out.value)[o] = idx == INT_MAX ? row[0] : from_compute<T, C>(best);
+                }
             }
         }
-        __syncthreads();  // everyone is done with buf[b] before it is refilled two iterations on
+        __syncthreads();  // everyone is done with buffer b before it is refilled two passes on
     }
-    if (!ok && threadIdx.x == 0) atomicAdd(&g_reduce_aborts, 1u);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 template <typename T, bool SUM, bool ARG, bool MIN>
@@ -445,22 +459,29 @@ tn_status launch(const tn_tensor_t* src, int axis, Outputs out, cudaStream_t s) 
         if (row_bytes <= 1024 && len >= 8 && total >= 2048 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
             // whole rows staged in shared memory: rows per chunk is a multiple of 16 so that a
             // chunk is a multiple of 16 bytes for any row length
-            int rpc = (int)((int64_t(44) << 10) / row_bytes) & ~15;
-            if (rpc > kStagedThreads) rpc = kStagedThreads;
+            int chunk_kb = 50;
+            if (const char* v = getenv("TN_REDUCE_CHUNK_KB")) { const int n = atoi(v); if (n >= 4 && n <= 52) chunk_kb = n; }
+            int rpc = (int)((int64_t(chunk_kb) << 10) / row_bytes) & ~15;
+            if (rpc > 128) rpc = 128;
             if (rpc >= 16) {
+                int lanes = 4;  // threads per row: as many as the CTA can spare, at most a warp
+                while (lanes < 32 && rpc * lanes * 2 <= kStagedThreads) lanes *= 2;
                 const size_t buf = ((size_t)rpc * row_bytes + 127) & ~size_t(127);
-                const size_t smem = 2 * buf + 16;
+                const size_t smem = 2 * buf;
                 static thread_local int attr_device = -1;
                 int dev = 0;
                 TN_CUDA(cudaGetDevice(&dev));
                 if (attr_device != dev) {
-                    TN_CUDA(cudaFuncSetAttribute(reduce_rows_staged<T, SUM, ARG, MIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 << 10));
+                    TN_CUDA(cudaFuncSetAttribute(reduce_rows_staged<T, SUM, ARG, MIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 << 10));
                     attr_device = dev;
                 }
                 const int64_t chunks = ceil_div(total, rpc);
-                int64_t grid = (int64_t)sm_count() * 2;
+                int64_t per_sm = (int64_t(220) << 10) / (int64_t)smem;  // CTAs that fit the shared memory of an SM
+                if (per_sm > 2048 / kStagedThreads) per_sm = 2048 / kStagedThreads;
+                if (per_sm < 1) per_sm = 1;
+                int64_t grid = (int64_t)sm_count() * per_sm;
                 if (grid > chunks) grid = chunks;
-                reduce_rows_staged<T, SUM, ARG, MIN><<<(unsigned)grid, kStagedThreads, smem, s>>>(p, total, (int)len, rpc, out);
+                reduce_rows_staged<T, SUM, ARG, MIN><<<(unsigned)grid, kStagedThreads, smem, s>>>(p, total, (int)len, rpc, lanes, out);
                 return after_launch("reduce_rows_staged");
             }
         }
