@@ -12,8 +12,9 @@
 //   reduce_rows_block  same geometry for long rows: one CTA per row;
 //   reduce_split       few, very long rows: every row is cut into segments whose partial
 //                      results go to scratch memory, a second kernel combines them;
-//   reduce_cols        dense source, inner axis: one thread per output column, coalesced
-//                      across the inner extent;
+//   reduce_cols_tiled  dense source, inner axis: 32 x 8 thread tiles, 16-byte loads along the inner
+//                      extent, the reduced axis split inside and across CTAs (partials in scratch);
+//   reduce_cols        the same for a narrow inner extent: one thread per output column;
 //   reduce_strided     any view: one thread per output.
 #include "common.cuh"
 
@@ -136,20 +137,36 @@ __device__ __forceinline__ void scan_dense(State<T, SUM, ARG, MIN>& st, const T*
     // element offset (relative to lo) of the first 16-byte boundary at or before row+lo
     const int64_t head = -static_cast<int64_t>((base & 15) / sizeof(T));
     const int64_t n = hi - lo;
-    for (int64_t g = head + (int64_t)lane * V; g < n; g += (int64_t)lanes * V) {
-        if (g >= 0 && g + V <= n) {
-            alignas(16) T e[V];
-            *reinterpret_cast<uint4*>(e) = __ldg(reinterpret_cast<const uint4*>(row + lo + g));
+    const int64_t stride = static_cast<int64_t>(lanes) * V;
+    auto ragged = [&](int64_t g) {
 #pragma unroll
-            for (int k = 0; k < V; ++k) st.feed(e[k], lo + g + k);
-        } else {
-#pragma unroll
-            for (int k = 0; k < V; ++k) {
-                const int64_t j = g + k;
-                if (j >= 0 && j < n) st.feed(row[lo + j], lo + j);
-            }
+        for (int k = 0; k < V; ++k) {
+            const int64_t j = g + k;
+            if (j >= 0 && j < n) st.feed(row[lo + j], lo + j);
         }
+    };
+    int64_t g = head + static_cast<int64_t>(lane) * V;
+    if (g < 0) {  // only the lane that owns the group straddling the start of the range
+        ragged(g);
+        g += stride;
     }
+    // four independent 16-byte loads in flight per lane
+    for (; g + 3 * stride + V <= n; g += 4 * stride) {
+        alignas(16) T e[4][V];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) *reinterpret_cast<uint4*>(e[u]) = __ldg(reinterpret_cast<const uint4*>(row + lo + g + u * stride));
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int k = 0; k < V; ++k) st.feed(e[u][k], lo + g + u * stride + k);
+    }
+    for (; g + V <= n; g += stride) {
+        alignas(16) T e[V];
+        *reinterpret_cast<uint4*>(e) = __ldg(reinterpret_cast<const uint4*>(row + lo + g));
+#pragma unroll
+        for (int k = 0; k < V; ++k) st.feed(e[k], lo + g + k);
+    }
+    if (g < n) ragged(g);
 }
 
 template <typename T, bool SUM, bool ARG, bool MIN>
@@ -391,6 +408,93 @@ __global__ void __launch_bounds__(kThreads) reduce_cols(const T* __restrict__ sr
     }
 }
 
+// ---- inner-axis reduction of a dense [outer, len, inner] tensor ---------------------------
+// A CTA is 32 x 8 threads: x runs along `inner` (VEC consecutive outputs per thread, one 16-byte
+// load when VEC > 1), y splits the reduced axis inside the CTA, blockIdx.z splits it across CTAs.
+// The eight y-partials are merged through shared memory; with more than one z-split the CTA result
+// goes to scratch memory as a Partial and reduce_cols_final merges the splits in ascending order.
+template <typename T, bool SUM, bool ARG, bool MIN, int VEC>
+__global__ void __launch_bounds__(256) reduce_cols_tiled(const T* __restrict__ src, int64_t len, int64_t inner, int64_t chunk,
+                                                        Partial<T>* __restrict__ scratch, Outputs out) {
+    using S = State<T, SUM, ARG, MIN>;
+    __shared__ typename S::A s_sum[8][33];
+    __shared__ typename S::C s_best[8][33];
+    __shared__ int64_t s_idx[8][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t col0 = (static_cast<int64_t>(blockIdx.x) * 32 + tx) * VEC;
+    const int64_t ou = blockIdx.y;
+    const int64_t l0 = static_cast<int64_t>(blockIdx.z) * chunk;
+    const int64_t l1 = l0 + chunk < len ? l0 + chunk : len;
+    const bool in_range = col0 < inner;
+    S st[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) st[k].init();
+    if (in_range) {
+        const T* base = src + ou * len * inner + col0;
+        int64_t l = l0 + ty;
+        // two rows in flight per thread
+        for (; l + 8 < l1; l += 16) {
+            alignas(16) T e0[VEC], e1[VEC];
+            if constexpr (VEC > 1) {
+                *reinterpret_cast<uint4*>(e0) = __ldg(reinterpret_cast<const uint4*>(base + l * inner));
+                *reinterpret_cast<uint4*>(e1) = __ldg(reinterpret_cast<const uint4*>(base + (l + 8) * inner));
+            } else {
+                e0[0] = __ldg(base + l * inner);
+                e1[0] = __ldg(base + (l + 8) * inner);
+            }
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) st[k].feed(e0[k], l);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) st[k].feed(e1[k], l + 8);
+        }
+        for (; l < l1; l += 8) {
+            alignas(16) T e0[VEC];
+            if constexpr (VEC > 1) *reinterpret_cast<uint4*>(e0) = __ldg(reinterpret_cast<const uint4*>(base + l * inner));
+            else e0[0] = __ldg(base + l * inner);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) st[k].feed(e0[k], l);
+        }
+    }
+    const int64_t total = static_cast<int64_t>(gridDim.y) * inner;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+        __syncthreads();
+        s_sum[ty][tx] = st[k].sum;
+        s_best[ty][tx] = st[k].best;
+        s_idx[ty][tx] = st[k].idx;
+        __syncthreads();
+        if (ty == 0 && in_range && col0 + k < inner) {
+            S acc = st[k];
+            for (int y = 1; y < 8; ++y) acc.merge(s_sum[y][tx], s_best[y][tx], s_idx[y][tx]);
+            const int64_t o = ou * inner + col0 + k;
+            if (scratch != nullptr) {
+                Partial<T> p;
+                p.sum = acc.sum;
+                p.best = acc.best;
+                p.idx = acc.idx;
+                scratch[static_cast<int64_t>(blockIdx.z) * total + o] = p;
+            } else {
+                write_out(acc, out, o, len, len > 0 ? src[ou * len * inner + col0 + k] : T());
+            }
+        }
+    }
+}
+
+template <typename T, bool SUM, bool ARG, bool MIN>
+__global__ void __launch_bounds__(kThreads) reduce_cols_final(const T* __restrict__ src, int64_t total, int64_t len, int64_t inner,
+                                                              int splits, const Partial<T>* __restrict__ scratch, Outputs out) {
+    const int64_t o = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    if (o >= total) return;
+    State<T, SUM, ARG, MIN> st;
+    st.init();
+    for (int z = 0; z < splits; ++z) {
+        const Partial<T> p = scratch[static_cast<int64_t>(z) * total + o];
+        st.merge(p.sum, p.best, p.idx);
+    }
+    const int64_t ou = o / inner, in = o - ou * inner;
+    write_out(st, out, o, len, len > 0 ? src[ou * len * inner + in] : T());
+}
+
 struct StridedGeom {
     int rank;                     // dims other than the axis
     int64_t sizes[TN_MAX_RANK];   // their extents, outermost first
@@ -494,6 +598,34 @@ tn_status launch(const tn_tensor_t* src, int axis, Outputs out, cudaStream_t s) 
         if (blocks > cap) blocks = cap;
         reduce_rows_warp<T, SUM, ARG, MIN><<<(int)blocks, kThreads, 0, s>>>(p, total, len, out);
         return after_launch("reduce_rows_warp");
+    }
+    if (dense && inner >= 32 && outer <= 65535) {
+        constexpr int V = 16 / (int)sizeof(T);
+        const bool vec = V > 1 && inner % V == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+        const int64_t per_thread = vec ? V : 1;
+        const int64_t gx = ceil_div(inner, 32 * per_thread);
+        // split the reduced axis across CTAs until about two waves of CTAs exist
+        int64_t splits = ceil_div((int64_t)sm_count() * 2, gx * outer);
+        if (splits > len / 64) splits = len / 64;
+        if (splits < 1) splits = 1;
+        if (splits > 1024) splits = 1024;
+        const int64_t chunk = ceil_div(len, splits);
+        splits = ceil_div(len, chunk);
+        Partial<T>* scratch = nullptr;
+        if (splits > 1) TN_TRY(scratch_alloc(reinterpret_cast<void**>(&scratch), sizeof(Partial<T>) * total * splits, s));
+        const dim3 grid((unsigned)gx, (unsigned)outer, (unsigned)splits);
+        if (vec) reduce_cols_tiled<T, SUM, ARG, MIN, V><<<grid, 256, 0, s>>>(p, len, inner, chunk, scratch, out);
+        else reduce_cols_tiled<T, SUM, ARG, MIN, 1><<<grid, 256, 0, s>>>(p, len, inner, chunk, scratch, out);
+        tn_status st = after_launch("reduce_cols_tiled");
+        if (splits > 1) {
+            if (st == TN_SUCCESS) {
+                reduce_cols_final<T, SUM, ARG, MIN><<<(unsigned)ceil_div(total, kThreads), kThreads, 0, s>>>(p, total, len, inner, (int)splits, scratch, out);
+                st = after_launch("reduce_cols_final");
+            }
+            const tn_status fr = scratch_free(scratch, s);
+            if (st == TN_SUCCESS) st = fr;
+        }
+        return st;
     }
     if (dense) {
         int64_t blocks = ceil_div(total, kThreads);
