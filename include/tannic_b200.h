@@ -152,7 +152,8 @@ tn_status tn_host_free_pinned(void* address);
  * src/cpu/ops-binary.cpp:434-448). NumPy broadcast, operands may be strided views; the result
  * is written in dst->dtype (never wider than the buffer, unlike the reference's half x int
  * and pow(half,half) entries). Arithmetic class: any float64 or (int64 with a float) ->
- * float64; any other float -> float32; integers wrap modulo 2^n. */
+ * float64; any other float -> float32; integers wrap modulo 2^n. complex64 / complex128 operands
+ * of one type support add, sub and mul (and neg / repack below), as in the reference's tables. */
 tn_status tn_add(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream);
 tn_status tn_sub(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream);
 tn_status tn_mul(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream);
@@ -234,6 +235,10 @@ tn_status tn_conv2d(const tn_tensor_t* x, const tn_tensor_t* w, tn_tensor_t* y, 
 tn_status tn_conv2d_bias(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_t* bias,
                          tn_tensor_t* y, tn_stream_t stream, const size_t pad[2],
                          const size_t stride[2]);
+/* reference: cuda::conv1d, src/cuda/conv1d.cu (CPU twin src/cpu/conv1d.cpp): [N, C, L] signal,
+ * [Cout, Cin, K] kernel; evaluated as the H = 1 case of conv2d. */
+tn_status tn_conv1d(const tn_tensor_t* x, const tn_tensor_t* w, tn_tensor_t* y, tn_stream_t stream,
+                    size_t pad, size_t stride);
 
 /* ------------------------------------------------------------------ reductions ------- */
 

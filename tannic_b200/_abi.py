@@ -113,6 +113,7 @@ PROTOTYPES = {
     "tn_gemm_scaled": [_TP, _TP, C.POINTER(ScalarT), _TP, StreamT],
     "tn_conv2d": [_TP, _TP, _TP, StreamT, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)],
     "tn_conv2d_bias": [_TP, _TP, _TP, _TP, StreamT, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)],
+    "tn_conv1d": [_TP, _TP, _TP, StreamT, C.c_size_t, C.c_size_t],
     "tn_reduce_stats": [_TP, _TP, _TP, _TP, StreamT, C.c_uint8],
     "tn_argsum_fixed_scratch": [_TP, _TP, StreamT, C.c_uint8],
     "tn_cpy": [_TP, _TP, StreamT],

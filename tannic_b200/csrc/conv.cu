@@ -285,6 +285,25 @@ tn_status tn_conv2d(const tn_tensor_t* x, const tn_tensor_t* w, tn_tensor_t* y, 
     return conv_impl(x, w, nullptr, y, stream, pad, stride);
 }
 
+// 1-D convolution as the H = 1 case of conv2d: [N, C, L] * [Cout, Cin, K] -> [N, Cout, Lout].
+tn_status tn_conv1d(const tn_tensor_t* x, const tn_tensor_t* w, tn_tensor_t* y, tn_stream_t stream, size_t pad, size_t stride) {
+    if (!x || !w || !y) return fail(TN_ERROR, "null argument");
+    if (x->rank != 3 || w->rank != 3 || y->rank != 3) return fail(TN_ERROR, "conv1d: expected ranks 3, 3 -> 3");
+    auto lift = [](const tn_tensor_t* t) {
+        tn_tensor_t r = *t;
+        r.rank = 4;
+        r.shape.sizes[3] = t->shape.sizes[2];
+        r.strides.sizes[3] = t->strides.sizes[2];
+        r.shape.sizes[2] = 1;
+        r.strides.sizes[2] = (int64_t)t->shape.sizes[2] * t->strides.sizes[2];
+        return r;
+    };
+    const tn_tensor_t x4 = lift(x), w4 = lift(w);
+    tn_tensor_t y4 = lift(y);
+    const size_t pad2[2] = {0, pad}, stride2[2] = {1, stride};
+    return conv_impl(&x4, &w4, nullptr, &y4, stream, pad2, stride2);
+}
+
 tn_status tn_conv2d_bias(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_t* bias, tn_tensor_t* y,
                          tn_stream_t stream, const size_t pad[2], const size_t stride[2]) {
     if (!bias) return fail(TN_ERROR, "null bias");

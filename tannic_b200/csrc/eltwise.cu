@@ -429,6 +429,71 @@ tn_status launch_generic(const Plan& plan, const tn_tensor_t* a, const tn_tensor
     return after_launch("ew_generic");
 }
 
+// ---- complex64 / complex128 (same-type add, sub, mul; neg and repack) -------------------------
+// The reference's tables hold complex entries for exactly these (src/cpu/ops-binary.cpp:222-223 and
+// the Sub / Mul twins; src/cpu/ops-unary.cpp:214-215,232-233). An element is a (re, im) pair of
+// F; the kernel decodes the logical index like ew_generic.
+template <typename F, int OP, typename I>
+__global__ void __launch_bounds__(kThreads) ew_complex(GenericArgs g) {
+    const I n = static_cast<I>(g.n);
+    const I step = static_cast<I>(gridDim.x) * kThreads;
+    for (I lin = static_cast<I>(blockIdx.x) * kThreads + threadIdx.x; lin < n; lin += step) {
+        I rem = lin;
+        int64_t oa = 0, ob = 0;
+        for (int dim = g.rank - 1; dim >= 0; --dim) {
+            const I size = static_cast<I>(g.sizes[dim]);
+            const I coord = rem % size;
+            rem /= size;
+            oa += static_cast<int64_t>(coord) * g.sa[dim];
+            ob += static_cast<int64_t>(coord) * g.sb[dim];
+        }
+        const F xr = static_cast<const F*>(g.a)[2 * oa], xi = static_cast<const F*>(g.a)[2 * oa + 1];
+        const F yr = static_cast<const F*>(g.b)[2 * ob], yi = static_cast<const F*>(g.b)[2 * ob + 1];
+        F rr, ri;
+        if constexpr (OP == TN_OP_ADD) { rr = xr + yr; ri = xi + yi; }
+        else if constexpr (OP == TN_OP_SUB) { rr = xr - yr; ri = xi - yi; }
+        else if constexpr (OP == TN_OP_MUL) { rr = xr * yr - xi * yi; ri = xr * yi + xi * yr; }
+        else if constexpr (OP == TN_OP_NEG) { rr = -xr; ri = -xi; }
+        else { rr = xr; ri = xi; }
+        static_cast<F*>(g.d)[2 * static_cast<int64_t>(lin)] = rr;
+        static_cast<F*>(g.d)[2 * static_cast<int64_t>(lin) + 1] = ri;
+    }
+}
+
+inline bool is_complex(int dt) { return dt == TN_COMPLEX64 || dt == TN_COMPLEX128; }
+
+template <int OP>
+tn_status launch_complex(const Plan& plan, const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, cudaStream_t s) {
+    if constexpr (OP == TN_OP_ADD || OP == TN_OP_SUB || OP == TN_OP_MUL || OP == TN_OP_NEG || OP == TN_OP_COUNT) {
+        if (plan.n == 0) return TN_SUCCESS;
+        GenericArgs g;
+        g.a = a->address;
+        g.b = b ? b->address : a->address;
+        g.d = dst->address;
+        g.adt = g.bdt = g.ddt = a->dtype;
+        g.rank = plan.rank;
+        g.n = plan.n;
+        for (int d = 0; d < plan.rank; ++d) {
+            g.sizes[d] = plan.sizes[d];
+            g.sa[d] = plan.st[0][d];
+            g.sb[d] = b ? plan.st[1][d] : plan.st[0][d];
+        }
+        g.imm = Imm{0.0, 0};
+        const int grid = flat_grid(plan.n);
+        const bool small = plan.n < (int64_t(1) << 31);
+        if (a->dtype == TN_COMPLEX64) {
+            if (small) ew_complex<float, OP, uint32_t><<<grid, kThreads, 0, s>>>(g);
+            else ew_complex<float, OP, uint64_t><<<grid, kThreads, 0, s>>>(g);
+        } else {
+            if (small) ew_complex<double, OP, uint32_t><<<grid, kThreads, 0, s>>>(g);
+            else ew_complex<double, OP, uint64_t><<<grid, kThreads, 0, s>>>(g);
+        }
+        return after_launch("ew_complex");
+    } else {
+        return fail(TN_UNSUPPORTED_DTYPE, "operation %d has no complex form", OP);
+    }
+}
+
 // Arithmetic class of a dtype pair (mirrors the result types of the reference's tables,
 // src/cpu/ops-binary.cpp:168-430): 0 = int64 wrap, 1 = float32, 2 = float64.
 int compute_class(int a, int b) {
@@ -486,7 +551,8 @@ tn_status generic_dispatch(int cls, const Plan& plan, const tn_tensor_t* a, cons
 template <int OP>
 tn_status binary(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream) {
     if (!a || !b || !dst) return fail(TN_ERROR, "null tensor");
-    if (!pair_supported(OP, a->dtype, b->dtype) || !is_numeric(dst->dtype))
+    const bool cplx = is_complex(a->dtype) && a->dtype == b->dtype && dst->dtype == a->dtype && OP != TN_OP_POW;
+    if (!cplx && (!pair_supported(OP, a->dtype, b->dtype) || !is_numeric(dst->dtype)))
         return fail(TN_UNSUPPORTED_DTYPE, "binary op %d: dtype pair (%d, %d) -> %d unsupported", OP, (int)a->dtype,
                     (int)b->dtype, (int)dst->dtype);
     if (a->environment.kind != TN_DEVICE || b->environment.kind != TN_DEVICE ||
@@ -498,6 +564,7 @@ tn_status binary(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, t
     const tn_tensor_t* ops[2] = {a, b};
     TN_TRY(build_plan(ops, 2, dst, plan));
     cudaStream_t s = as_cuda(stream);
+    if (cplx) return launch_complex<OP>(plan, a, b, dst, s);
     Imm imm{0.0, 0};
     if (a->dtype == b->dtype && a->dtype == dst->dtype) {
         bool done = false;
@@ -516,7 +583,8 @@ bool unary_supported(int op, int dt) {
 template <int OP>
 tn_status unary(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, Imm imm) {
     if (!src || !dst) return fail(TN_ERROR, "null tensor");
-    if (!unary_supported(OP, src->dtype) || !is_numeric(dst->dtype))
+    const bool cplx = is_complex(src->dtype) && dst->dtype == src->dtype && (OP == TN_OP_NEG || OP == TN_OP_COUNT);
+    if (!cplx && (!unary_supported(OP, src->dtype) || !is_numeric(dst->dtype)))
         return fail(TN_UNSUPPORTED_DTYPE, "unary op %d: dtype %d unsupported", OP, (int)src->dtype);
     if (src->environment.kind != TN_DEVICE ||
         src->environment.resource.device.id != dst->environment.resource.device.id)
@@ -526,6 +594,7 @@ tn_status unary(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, Im
     const tn_tensor_t* ops[1] = {src};
     TN_TRY(build_plan(ops, 1, dst, plan));
     cudaStream_t s = as_cuda(stream);
+    if (cplx) return launch_complex<OP>(plan, src, nullptr, dst, s);
     if (src->dtype == dst->dtype) {
         bool done = false;
         TN_TRY((typed_dispatch<OP>(src->dtype, plan, src->address, nullptr, dst->address, imm, s, &done)));

@@ -4,7 +4,7 @@
 // complex.cpp) by forwarding to the C ABI of libtannic_b200.so. It is compiled against the
 // reference's own headers (their declarations are the contract), replaces all of src/cuda/*.cu and
 // needs no other change to the reference. Device functions outside the operator hot path
-// (outer, repeat, concat, conv1d, triangular masks, complex views) report UNSUPPORTED_DTYPE.
+// (outer, repeat, concat, triangular masks, complex views) report UNSUPPORTED_DTYPE.
 #include <cstdint>
 #include <new>
 #include <stdexcept>
@@ -67,6 +67,10 @@ status conv2d(const tensor_t* x, const tensor_t* w, const tensor_t* b, tensor_t*
     return st(tn_conv2d_bias(in(x), in(w), in(b), out(y), on(s), pad, stride));
 }
 
+status conv1d(const tensor_t* x, const tensor_t* w, tensor_t* y, stream_t s, const size_t pad, const size_t stride) {
+    return st(tn_conv1d(in(x), in(w), out(y), on(s), pad, stride));
+}
+
 status argmax(const tensor_t* x, tensor_t* d, stream_t s, uint8_t ax) { return st(tn_argmax(in(x), out(d), on(s), ax)); }
 status argmin(const tensor_t* x, tensor_t* d, stream_t s, uint8_t ax) { return st(tn_argmin(in(x), out(d), on(s), ax)); }
 status argsum(const tensor_t* x, tensor_t* d, stream_t s, uint8_t ax) { return st(tn_argsum(in(x), out(d), on(s), ax)); }
@@ -80,7 +84,6 @@ bool allclose(const tensor_t* a, const tensor_t* b, stream_t s, double rtol, dou
 }
 
 // ---- outside the operator hot path: not provided by this backend --------------------------------
-status conv1d(const tensor_t*, const tensor_t*, tensor_t*, stream_t, const size_t, const size_t) { return UNSUPPORTED_DTYPE; }
 status outer(tensor_t const*, tensor_t const*, tensor_t*, stream_t) { return UNSUPPORTED_DTYPE; }
 status repeat(const tensor_t*, tensor_t*, int, int, stream_t) { return UNSUPPORTED_DTYPE; }
 status concat(const tensor_t*, const tensor_t*, tensor_t*, stream_t, int) { return UNSUPPORTED_DTYPE; }
