@@ -213,9 +213,35 @@ __device__ __forceinline__ OutT finish(float acc, float scale, float bias) {
     }
 }
 
-template <typename OutT> __device__ __forceinline__ uint32_t bits16(OutT v);
-template <> __device__ __forceinline__ uint32_t bits16<__half>(__half v) { return __half_as_ushort(v); }
-template <> __device__ __forceinline__ uint32_t bits16<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat16_as_ushort(v); }
+// Two accumulators -> a packed pair of result elements: one conversion instruction for both,
+// and the optional scalar factor as one packed multiply. The product of two 16-bit floats is
+// exact in fp32, so the packed multiply rounds exactly like `float(a) * float(s)` rounded once.
+template <typename OutT> __device__ __forceinline__ uint32_t pair_of(float s);
+template <> __device__ __forceinline__ uint32_t pair_of<__half>(float s) {
+    const __half2 h = __float2half2_rn(s);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pair_of<__nv_bfloat16>(float s) {
+    const __nv_bfloat162 h = __float2bfloat162_rn(s);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <typename OutT, bool SCALE> __device__ __forceinline__ uint32_t finish_pair(float lo, float hi, uint32_t scale2);
+template <> __device__ __forceinline__ uint32_t finish_pair<__half, false>(float lo, float hi, uint32_t) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t finish_pair<__half, true>(float lo, float hi, uint32_t scale2) {
+    const __half2 h = __hmul2(__floats2half2_rn(lo, hi), *reinterpret_cast<const __half2*>(&scale2));
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t finish_pair<__nv_bfloat16, false>(float lo, float hi, uint32_t) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t finish_pair<__nv_bfloat16, true>(float lo, float hi, uint32_t scale2) {
+    const __nv_bfloat162 h = __hmul2(__floats2bfloat162_rn(lo, hi), *reinterpret_cast<const __nv_bfloat162*>(&scale2));
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
 
 struct EpilogueTile {
     uint8_t* dbase;      // result of this batch
@@ -239,20 +265,21 @@ __device__ __forceinline__ void store_block(const EpilogueTile& e, const uint32_
     uint32_t* stage_words = reinterpret_cast<uint32_t*>(stage);
     __syncwarp();  // the previous block's readers are done with the staging area
     if constexpr (!std::is_same<OutT, float>::value) {
+        // rows of 64 bytes at an 80-byte pitch: conflict-free both for the 16-byte writes of a
+        // lane's own row and for reads along a row
+        const uint32_t scale2 = pair_of<OutT>(e.scale);
+        uint4* mine = reinterpret_cast<uint4*>(stage + lane * 80);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                w[j] = finish_pair<OutT, SCALE>(__uint_as_float(v[8 * q + 2 * j]) + e.bias, __uint_as_float(v[8 * q + 2 * j + 1]) + e.bias, scale2);
+            mine[q] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        __syncwarp();
         if (e.vec_store) {
-            // rows of 64 bytes at an 80-byte pitch (conflict-free for 16-byte accesses), written
-            // out as 8 rows x 4 lanes x 16 bytes per instruction
-            uint4* mine = reinterpret_cast<uint4*>(stage + lane * 80);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                uint32_t w[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    w[j] = bits16(finish<OutT, SCALE>(__uint_as_float(v[8 * q + 2 * j]), e.scale, e.bias)) |
-                           (bits16(finish<OutT, SCALE>(__uint_as_float(v[8 * q + 2 * j + 1]), e.scale, e.bias)) << 16);
-                mine[q] = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-            __syncwarp();
+            // 8 rows x 4 lanes x 16 bytes per store instruction
             const int seg = lane & 3;
             const int64_t col = col0 + seg * 8;
 #pragma unroll
@@ -263,19 +290,17 @@ __device__ __forceinline__ void store_block(const EpilogueTile& e, const uint32_
                         *reinterpret_cast<const uint4*>(stage + r * 80 + seg * 16);
             }
         } else {
-            // any alignment: column pairs packed into words at a 17-word pitch, one element per
-            // lane per row on the way out
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                stage_words[lane * STAGING_PITCH + j] = bits16(finish<OutT, SCALE>(__uint_as_float(v[2 * j]), e.scale, e.bias)) |
-                                                        (bits16(finish<OutT, SCALE>(__uint_as_float(v[2 * j + 1]), e.scale, e.bias)) << 16);
-            __syncwarp();
+            // any alignment: one row of 32 elements per store instruction
             const int64_t col = col0 + lane;
             if (col < e.col_end) {
                 uint16_t* out = reinterpret_cast<uint16_t*>(e.dbase) + e.row0 * e.ldd + col;
-                const int word = lane >> 1, shift = (lane & 1) * 16;
-#pragma unroll 4
-                for (int r = 0; r < e.rows; ++r) out[r * e.ldd] = static_cast<uint16_t>(stage_words[r * STAGING_PITCH + word] >> shift);
+                const uint16_t* src = reinterpret_cast<const uint16_t*>(stage) + lane;
+                if (e.rows == 32) {
+#pragma unroll
+                    for (int r = 0; r < 32; ++r) out[r * e.ldd] = src[r * 40];
+                } else {
+                    for (int r = 0; r < e.rows; ++r) out[r * e.ldd] = src[r * 40];
+                }
             }
         }
     } else {
