@@ -4,9 +4,11 @@
 //
 //   warp 0      TMA producer   (one elected lane issues cp.async.bulk.tensor loads)
 //   warp 1      MMA issuer     (one elected lane issues tcgen05.mma / tcgen05.commit)
-//   warps 2..5  epilogue       (tcgen05.ld -> convert -> transposed through smem -> coalesced
-//                               stores, 16 bytes per lane where the result is aligned; each warp
-//                               owns the TMEM lane quarter (warp % 4))
+//   warps 2..9  epilogue       (tcgen05.ld -> convert -> shared memory -> global: 32-row x 64-byte
+//                               boxes handed to TMA where the result's base and pitches are
+//                               multiples of 16 bytes, else coalesced element stores; each warp
+//                               owns the TMEM lane quarter (warp % 4) and every second 32-column
+//                               chunk, or every chunk when only four epilogue warps run)
 //
 // Three operand modes share the main loop:
 //   MODE_K  B is K-major ([N, K]: `matmul(X, W.transpose(-1,-2))`), one 64x256 TMA box per stage;
@@ -48,7 +50,7 @@ constexpr uint32_t B_BYTES = BN * BK * 2;        // 32 KiB
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr uint32_t TMEM_COLS = 512;              // two accumulators of BN fp32 columns
 constexpr int STAGING_PITCH = 17;                // words per staged row of the element-wise path (conflict-free transpose)
-constexpr uint32_t STAGING_WARP_BYTES = 32 * 80; // per epilogue warp: 32 rows x (64 B of data + 16 B pad)
+constexpr uint32_t STAGING_WARP_BYTES = 4096;    // per epilogue warp: two 2 KiB boxes for TMA stores (or one 32 x 80 B block)
 constexpr uint32_t STAGING_BYTES = kEpilogueWarps * STAGING_WARP_BYTES;
 constexpr uint32_t SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + STAGING_BYTES + 256 /*barriers*/;
 
@@ -106,6 +108,20 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+
+// Result tiles leave through TMA as well: a warp writes a 32-row x 64-byte box into shared memory
+// (64-byte swizzle) and one lane hands it to the copy engine, which clips it at the tensor's edges.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// until at most one of this thread's store groups still reads its shared-memory source
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -168,7 +184,7 @@ struct KernelArgs {
     int64_t M, N;              // result rows / columns per batch (conv: Cout, Hout*Wout)
     int64_t ldd, d_batch;
     int m_tiles, n_tiles;
-    int64_t total_tiles;
+    uint32_t total_tiles;
     int k_blocks;              // 64-wide K blocks per tile (conv: taps * channel blocks)
     int tile_n;                // result columns per tile (256; conv: Hbox * Wout)
     int umma_n;                // N of the MMA instruction (multiple of 16, >= tile_n)
@@ -177,6 +193,7 @@ struct KernelArgs {
     int is_bf16;               // operand format: 1 = bf16, 0 = fp16
     int d_is_f32;
     int vec_store;             // result rows can be written with 16-byte stores
+    int tma_store;             // result leaves through TMA boxes (map_d is valid)
     int has_scale;
     float scale;
     // convolution geometry
@@ -187,10 +204,11 @@ struct KernelArgs {
 // Tiles are walked in groups of 16 row-tiles so that the CTAs running at the same time share
 // rows of A and columns of B in L2.
 constexpr int kGroupM = 16;
-__device__ __forceinline__ void tile_coords(int64_t t, int m_tiles, int n_tiles, int& batch, int& mt, int& nt) {
-    const int64_t per_batch = static_cast<int64_t>(m_tiles) * n_tiles;
+__device__ __forceinline__ void tile_coords(uint32_t t, int m_tiles, int n_tiles, int& batch, int& mt, int& nt) {
+    // tile counts are below 2^31 (checked on the host): 32-bit divisions only
+    const uint32_t per_batch = static_cast<uint32_t>(m_tiles) * static_cast<uint32_t>(n_tiles);
     batch = static_cast<int>(t / per_batch);
-    int r = static_cast<int>(t - static_cast<int64_t>(batch) * per_batch);
+    int r = static_cast<int>(t - static_cast<uint32_t>(batch) * per_batch);
     const int group_span = kGroupM * n_tiles;
     const int g = r / group_span;
     r -= g * group_span;
@@ -255,14 +273,60 @@ struct EpilogueTile {
     int chunk_step;      // 1: this warp takes every chunk, 2: every second one
     float bias, scale;
     int vec_store;
+    int has_bias;
+    int tma_store;
+    int batch;
+    int64_t n_total;     // columns of the whole result
+    const CUtensorMap* map_d;
 };
 
 // Writes one 32 x 32 block (lane = row, v = 32 consecutive columns starting at col0) through a
 // per-warp staging area so that the global stores run along rows. OutT and SCALE are
 // compile-time so that the per-element conversion code has no branches.
 template <typename OutT, bool SCALE>
-__device__ __forceinline__ void store_block(const EpilogueTile& e, const uint32_t (&v)[32], int64_t col0, uint8_t* stage, int lane) {
+__device__ __forceinline__ void store_block(const EpilogueTile& e, uint32_t (&v)[32], int64_t col0, uint8_t* stage, int lane, int& flip) {
     uint32_t* stage_words = reinterpret_cast<uint32_t*>(stage);
+    if (e.has_bias) {  // warp-uniform
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + e.bias);
+    }
+    // A box may run past the edge of the result (TMA clips it) but not into columns that belong
+    // to the next tile, which happens only where a convolution tile is not a multiple of 32 wide.
+    if (e.tma_store && (col0 + 32 <= e.col_end || e.col_end == e.n_total)) {  // warp-uniform
+        constexpr bool kF32 = std::is_same<OutT, float>::value;
+        const int x = (lane >> 1) & 3;  // 64-byte swizzle: 16-byte unit q of row r sits in unit q ^ ((r >> 1) & 3)
+#pragma unroll
+        for (int h = 0; h < (kF32 ? 2 : 1); ++h) {
+            uint8_t* buf = stage + (flip & 1) * 2048;
+            flip ^= 1;
+            if (lane == 0) bulk_wait_read_1();  // the store that used this buffer two boxes ago has read it
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t w[4];
+                if constexpr (kF32) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) w[j] = __float_as_uint(finish<float, SCALE>(__uint_as_float(v[h * 16 + 4 * q + j]), e.scale, 0.0f));
+                } else {
+                    const uint32_t scale2 = pair_of<OutT>(e.scale);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        w[j] = finish_pair<OutT, SCALE>(__uint_as_float(v[8 * q + 2 * j]), __uint_as_float(v[8 * q + 2 * j + 1]), scale2);
+                }
+                *reinterpret_cast<uint4*>(buf + lane * 64 + ((q ^ x) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            fence_async_smem();  // generic-proxy writes become visible to the copy engine
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_3d(e.map_d, smem_u32(buf), static_cast<int>(col0) + h * 16, static_cast<int>(e.row0), e.batch);
+                bulk_commit();
+            }
+        }
+        return;
+    }
+    if (e.tma_store) {
+        if (lane == 0) bulk_wait_read_0();  // the element-wise path below reuses the boxes' memory
+    }
     __syncwarp();  // the previous block's readers are done with the staging area
     if constexpr (!std::is_same<OutT, float>::value) {
         // rows of 64 bytes at an 80-byte pitch: conflict-free both for the 16-byte writes of a
@@ -274,7 +338,7 @@ __device__ __forceinline__ void store_block(const EpilogueTile& e, const uint32_
             uint32_t w[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-                w[j] = finish_pair<OutT, SCALE>(__uint_as_float(v[8 * q + 2 * j]) + e.bias, __uint_as_float(v[8 * q + 2 * j + 1]) + e.bias, scale2);
+                w[j] = finish_pair<OutT, SCALE>(__uint_as_float(v[8 * q + 2 * j]), __uint_as_float(v[8 * q + 2 * j + 1]), scale2);
             mine[q] = make_uint4(w[0], w[1], w[2], w[3]);
         }
         __syncwarp();
@@ -315,7 +379,7 @@ __device__ __forceinline__ void store_block(const EpilogueTile& e, const uint32_
                 for (int q = 0; q < 4; ++q) {
                     uint32_t w[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) w[j] = __float_as_uint(finish<float, SCALE>(__uint_as_float(v[h * 16 + 4 * q + j]), e.scale, e.bias));
+                    for (int j = 0; j < 4; ++j) w[j] = __float_as_uint(finish<float, SCALE>(__uint_as_float(v[h * 16 + 4 * q + j]), e.scale, 0.0f));
                     mine[q] = make_uint4(w[0], w[1], w[2], w[3]);
                 }
                 __syncwarp();
@@ -331,7 +395,7 @@ __device__ __forceinline__ void store_block(const EpilogueTile& e, const uint32_
             } else {
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
-                    stage_words[lane * STAGING_PITCH + j] = __float_as_uint(finish<float, SCALE>(__uint_as_float(v[h * 16 + j]), e.scale, e.bias));
+                    stage_words[lane * STAGING_PITCH + j] = __float_as_uint(finish<float, SCALE>(__uint_as_float(v[h * 16 + j]), e.scale, 0.0f));
                 __syncwarp();
                 const int64_t col = colh + (lane & 15);
                 if (col < e.col_end) {
@@ -346,7 +410,7 @@ __device__ __forceinline__ void store_block(const EpilogueTile& e, const uint32_
 // Drains this warp's share of the accumulator: 32 rows, every second 32-column chunk. The
 // TMEM load of the next chunk is in flight while the current one is converted and stored.
 template <typename OutT, bool SCALE>
-__device__ __forceinline__ void drain_tile(const EpilogueTile& e, uint8_t* stage, int lane) {
+__device__ __forceinline__ void drain_tile(const EpilogueTile& e, uint8_t* stage, int lane, int& flip) {
     if (e.rows <= 0) return;  // warp-uniform
     auto valid = [&](int c) { return c < BN / 32 && e.col_base + c * 32 < e.col_end; };
     uint32_t va[32], vb[32];
@@ -358,13 +422,13 @@ __device__ __forceinline__ void drain_tile(const EpilogueTile& e, uint8_t* stage
         const int c2 = c + e.chunk_step;
         const bool more2 = valid(c2);
         if (more2) tmem_load_issue(e.taddr0 + c2 * 32, vb);
-        store_block<OutT, SCALE>(e, va, e.col_base + c * 32, stage, lane);
+        store_block<OutT, SCALE>(e, va, e.col_base + c * 32, stage, lane, flip);
         if (!more2) break;
         tmem_load_wait(vb);
         c = c2 + e.chunk_step;
         const bool more = valid(c);
         if (more) tmem_load_issue(e.taddr0 + c * 32, va);
-        store_block<OutT, SCALE>(e, vb, e.col_base + c2 * 32, stage, lane);
+        store_block<OutT, SCALE>(e, vb, e.col_base + c2 * 32, stage, lane, flip);
         if (!more) break;
     }
 }
@@ -378,7 +442,8 @@ template <> struct out_type<OUT_F32> { using type = float; };
 // rounded result by a scalar. All three are compile-time so that the epilogue is branch-free.
 template <int MODE, int OUT, bool SCALE>
 __global__ void __launch_bounds__(kThreads, 1)
-tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KernelArgs g) {
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_d, const KernelArgs g) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
@@ -420,7 +485,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
+            for (uint32_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x) {
                 int batch, mt, nt;
                 tile_coords(t, g.m_tiles, g.n_tiles, batch, mt, nt);
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
@@ -464,7 +529,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                    (static_cast<uint32_t>(g.umma_n >> 3) << 17) | (static_cast<uint32_t>(BM >> 4) << 24);
             uint32_t it = 0, local_tile = 0;
             bool ok = true;
-            for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x, ++local_tile) {
+            for (uint32_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x, ++local_tile) {
                 const int buf = local_tile & 1;
                 const uint32_t acc_parity = ((local_tile >> 1) & 1) ^ 1;
                 if (!mbar_wait(acce0 + 8 * buf, acc_parity, abort_flag)) { ok = false; break; }
@@ -496,8 +561,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter+32)
         uint8_t* stage = staging_ptr + ew * STAGING_WARP_BYTES;
         uint32_t local_tile = 0;
+        int flip = 0;  // which of the warp's two store boxes is next
         bool ok = true;
-        for (int64_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x, ++local_tile) {
+        for (uint32_t t = blockIdx.x; ok && t < g.total_tiles; t += gridDim.x, ++local_tile) {
             int batch, mt, nt;
             tile_coords(t, g.m_tiles, g.n_tiles, batch, mt, nt);
             const int buf = local_tile & 1;
@@ -526,12 +592,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             e.bias = bias;
             e.scale = g.scale;
             e.vec_store = g.vec_store;
-            drain_tile<typename out_type<OUT>::type, SCALE>(e, stage, lane);
+            e.has_bias = g.bias != nullptr;
+            e.tma_store = g.tma_store;
+            e.batch = batch;
+            e.n_total = g.N;
+            e.map_d = &map_d;
+            drain_tile<typename out_type<OUT>::type, SCALE>(e, stage, lane, flip);
             // this warp has finished reading the accumulator
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(acce0 + 8 * buf);
         }
+        if (g.tma_store && lane == 0) bulk_wait_all();  // shared memory stays valid until the last box has left
     }
 
     tc_fence_before();
@@ -561,17 +633,44 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// Tiled map of rank `rank` over 16-bit elements, 128-byte swizzle, zero fill outside the tensor.
-tn_status encode(CUtensorMap* map, const void* ptr, bool bf16, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
-                 const cuuint32_t* box) {
+bool mult8(int64_t v) { return (v & 7) == 0; }
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Tiled map of rank `rank`, zero fill outside the tensor.
+tn_status encode_as(CUtensorMap* map, const void* ptr, CUtensorMapDataType type, CUtensorMapSwizzle swizzle, int rank,
+                    const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(TN_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-    CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank,
-                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = fn(map, type, (cuuint32_t)rank, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(TN_ERROR, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return TN_SUCCESS;
+}
+
+// Operand maps: 16-bit elements, 128-byte swizzle.
+tn_status encode(CUtensorMap* map, const void* ptr, bool bf16, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
+                 const cuuint32_t* box) {
+    return encode_as(map, ptr, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, CU_TENSOR_MAP_SWIZZLE_128B,
+                     rank, dims, strides, box);
+}
+
+// Result map (columns, rows, batch) for the epilogue's stores: boxes of 32 rows x 64 bytes, 64-byte
+// swizzle. Usable when the base and both pitches are multiples of 16 bytes and every tile starts
+// on a 16-byte column boundary.
+bool can_tma_store(const void* d, int64_t ldd, int64_t d_batch, int64_t tile_n, bool f32) {
+    const int64_t per16 = f32 ? 4 : 8;
+    if (getenv("TN_TC_NO_TMA_STORE")) return false;
+    return aligned16(d) && ldd % per16 == 0 && d_batch % per16 == 0 && tile_n % per16 == 0;
+}
+tn_status make_result_map(CUtensorMap* map, void* d, bool f32, bool bf16, int64_t n, int64_t m, int64_t batches, int64_t ldd, int64_t d_batch) {
+    const cuuint64_t es = f32 ? 4 : 2;
+    cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)(batches > 0 ? batches : 1)};
+    cuuint64_t pitch_batch = (cuuint64_t)(d_batch > 0 ? d_batch : ldd * m) * es;
+    cuuint64_t strides[2] = {(cuuint64_t)ldd * es, pitch_batch};
+    cuuint32_t box[3] = {(cuuint32_t)(64 / es), 32, 1};
+    const CUtensorMapDataType type = f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    return encode_as(map, d, type, CU_TENSOR_MAP_SWIZZLE_64B, 3, dims, strides, box);
 }
 
 // 3-D map (inner, rows, batch) over a 16-bit matrix; box = box_inner x box_rows x 1.
@@ -588,11 +687,9 @@ tn_status make_map(CUtensorMap* map, const void* ptr, bool bf16, int64_t inner, 
     return encode(map, ptr, bf16, 3, dims, strides, box);
 }
 
-bool mult8(int64_t v) { return (v & 7) == 0; }
-bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 template <int MODE, int OUT, bool SCALE>
-tn_status launch_one(const CUtensorMap& map_a, const CUtensorMap& map_b, const KernelArgs& g, cudaStream_t stream) {
+tn_status launch_one(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const KernelArgs& g, cudaStream_t stream) {
     // the opt-in shared-memory size is a per-device attribute of the kernel
     static thread_local int attr_device = -1;
     int dev = 0;
@@ -611,15 +708,15 @@ tn_status launch_one(const CUtensorMap& map_a, const CUtensorMap& map_b, const K
         const int n = atoi(v);
         if (n == 4 || n == 8) args.epi_warps = n;
     }
-    tc_gemm_kernel<MODE, OUT, SCALE><<<grid, kThreads, SMEM_BYTES, stream>>>(map_a, map_b, args);
+    tc_gemm_kernel<MODE, OUT, SCALE><<<grid, kThreads, SMEM_BYTES, stream>>>(map_a, map_b, map_d, args);
     return after_launch("tc_gemm_kernel");
 }
 
 template <int MODE>
-tn_status launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const KernelArgs& g, cudaStream_t stream) {
-    if (g.d_is_f32) return g.has_scale ? launch_one<MODE, OUT_F32, true>(map_a, map_b, g, stream) : launch_one<MODE, OUT_F32, false>(map_a, map_b, g, stream);
-    if (g.is_bf16) return g.has_scale ? launch_one<MODE, OUT_BF16, true>(map_a, map_b, g, stream) : launch_one<MODE, OUT_BF16, false>(map_a, map_b, g, stream);
-    return g.has_scale ? launch_one<MODE, OUT_F16, true>(map_a, map_b, g, stream) : launch_one<MODE, OUT_F16, false>(map_a, map_b, g, stream);
+tn_status launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const KernelArgs& g, cudaStream_t stream) {
+    if (g.d_is_f32) return g.has_scale ? launch_one<MODE, OUT_F32, true>(map_a, map_b, map_d, g, stream) : launch_one<MODE, OUT_F32, false>(map_a, map_b, map_d, g, stream);
+    if (g.is_bf16) return g.has_scale ? launch_one<MODE, OUT_BF16, true>(map_a, map_b, map_d, g, stream) : launch_one<MODE, OUT_BF16, false>(map_a, map_b, map_d, g, stream);
+    return g.has_scale ? launch_one<MODE, OUT_F16, true>(map_a, map_b, map_d, g, stream) : launch_one<MODE, OUT_F16, false>(map_a, map_b, map_d, g, stream);
 }
 
 }  // namespace
@@ -635,7 +732,7 @@ bool tc_gemm_eligible(const TcGemm& p) {
     // extents must fit the 32-bit coordinates of a tensor map with headroom
     if (p.M >= (int64_t(1) << 31) || p.N >= (int64_t(1) << 31) || p.K >= (int64_t(1) << 31) || p.batches >= (int64_t(1) << 31)) return false;
     const int64_t tiles = ceil_div(p.M, BM) * ceil_div(p.N, BN) * p.batches;
-    return tiles < (int64_t(1) << 40);
+    return tiles < (int64_t(1) << 31);
 }
 
 static bool can_vector_store(const void* d, int64_t ldd, int64_t d_batch, int64_t n, int64_t tile_n, bool f32) {
@@ -659,7 +756,7 @@ tn_status tc_gemm(const TcGemm& p, cudaStream_t stream) {
     g.d_batch = p.d_batch;
     g.m_tiles = (int)ceil_div(p.M, BM);
     g.n_tiles = (int)ceil_div(p.N, BN);
-    g.total_tiles = (int64_t)g.m_tiles * g.n_tiles * p.batches;
+    g.total_tiles = (uint32_t)((int64_t)g.m_tiles * g.n_tiles * p.batches);
     g.k_blocks = (int)ceil_div(p.K, BK);
     g.tile_n = BN;
     g.umma_n = BN;
@@ -671,7 +768,10 @@ tn_status tc_gemm(const TcGemm& p, cudaStream_t stream) {
     g.vec_store = can_vector_store(p.d, p.ldd, p.d_batch, p.N, BN, g.d_is_f32 != 0);
     g.has_scale = p.has_scale;
     g.scale = p.scale;
-    return p.b_n_major ? launch<MODE_N>(map_a, map_b, g, stream) : launch<MODE_K>(map_a, map_b, g, stream);
+    CUtensorMap map_d = map_a;  // placeholder when the result does not leave through TMA
+    g.tma_store = can_tma_store(p.d, p.ldd, p.d_batch, BN, g.d_is_f32 != 0);
+    if (g.tma_store) TN_TRY(make_result_map(&map_d, p.d, g.d_is_f32 != 0, bf16, p.N, p.M, p.batches, p.ldd, p.d_batch));
+    return p.b_n_major ? launch<MODE_N>(map_a, map_b, map_d, g, stream) : launch<MODE_K>(map_a, map_b, map_d, g, stream);
 }
 
 bool tc_conv_eligible(const TcConv& p) {
@@ -680,6 +780,7 @@ bool tc_conv_eligible(const TcConv& p) {
     if (!mult8(p.C)) return false;                       // NHWC pixel pitch must be a multiple of 16 bytes
     if (p.Wo > 256 || p.W > 65535 || p.H > 65535) return false;
     if (p.Kh * p.Kw > 1024 || p.N >= (int64_t(1) << 31)) return false;
+    if (ceil_div(p.Cout, BM) * p.Ho * p.N >= (int64_t(1) << 31)) return false;  // tile index is 32-bit
     return aligned16(p.x_nhwc) && aligned16(p.w_packed);
 }
 
@@ -708,7 +809,7 @@ tn_status tc_conv(const TcConv& p, cudaStream_t stream) {
     g.d_batch = p.Cout * g.N;
     g.m_tiles = (int)ceil_div(p.Cout, BM);
     g.n_tiles = (int)ceil_div(p.Ho, hbox);
-    g.total_tiles = (int64_t)g.m_tiles * g.n_tiles * p.N;
+    g.total_tiles = (uint32_t)((int64_t)g.m_tiles * g.n_tiles * p.N);
     g.cblocks = (int)ceil_div(p.C, BK);
     g.k_blocks = taps * g.cblocks;
     g.tile_n = hbox * (int)p.Wo;
@@ -724,7 +825,10 @@ tn_status tc_conv(const TcConv& p, cudaStream_t stream) {
     g.pad_h = (int)p.pad_h;
     g.pad_w = (int)p.pad_w;
     g.hbox = hbox;
-    return launch<MODE_CONV>(map_a, map_b, g, stream);
+    CUtensorMap map_d = map_a;
+    g.tma_store = can_tma_store(p.y, g.ldd, g.d_batch, g.tile_n, false);
+    if (g.tma_store) TN_TRY(make_result_map(&map_d, p.y, false, bf16, g.N, p.Cout, p.N, g.ldd, g.d_batch));
+    return launch<MODE_CONV>(map_a, map_b, map_d, g, stream);
 }
 
 tn_status tc_abort_count(unsigned int* count) {

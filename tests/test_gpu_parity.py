@@ -341,6 +341,30 @@ def test_matmul_batched_broadcast_and_more_than_256_batches():
     assert tb.device_errors() == 0
 
 
+@pytest.mark.parametrize("n_major", [False, True])
+@pytest.mark.parametrize("batches,m,n,k", [(1, 1024, 3136, 256), (3, 300, 520, 192), (400, 197, 197, 64), (2, 2000, 264, 128), (170, 256, 256, 256)])
+def test_matmul_short_k_many_row_tiles(batches, m, n, k, n_major):
+    """K of at most 256 with several row tiles and many tiles per CTA: short main loops, so the
+    epilogue and the accumulator hand-over set the pace; ragged edges in both directions."""
+    dtype = torch.bfloat16 if n_major else torch.float16
+    a = gen((batches, m, k), dtype, 60, -1, 1)
+    if n_major:
+        b = gen((batches, k, n), dtype, 61, -1, 1)
+        got = tb.matmul(dev(a), dev(b))
+        pick = lambda i, r: oracle.matmul(a[i][r], b[i], acc=oracle.ACC_WIDE)
+    else:
+        w = gen((batches, n, k), dtype, 61, -1, 1)
+        got = tb.matmul(dev(a), dev(w).transpose(-1, -2))
+        pick = lambda i, r: oracle.matmul(a[i][r], w[i].t(), acc=oracle.ACC_WIDE)
+    rows = slice(0, m) if m * n * k <= 300 * 520 * 192 else slice(m - 160, m)
+    for i in sorted({0, batches // 2, batches - 1}):
+        assert_close(got[i][rows], pick(i, rows))
+    # every batch against a float32 product on the device (loose: catches a misplaced tile)
+    ref = torch.matmul(dev(a).float(), dev(b).float() if n_major else dev(w).float().transpose(-1, -2))
+    assert torch.allclose(got.float(), ref, rtol=2e-2, atol=2e-2)
+    assert tb.device_errors() == 0
+
+
 def test_matmul_half_to_float32_result():
     a, w = gen((130, 136), torch.bfloat16, 38, -1, 1), gen((72, 136), torch.bfloat16, 39, -1, 1)
     got = tb.matmul(dev(a), dev(w).t(), out_dtype=A.FLOAT32)
