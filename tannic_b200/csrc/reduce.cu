@@ -199,14 +199,20 @@ __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cas
 // copies keep many more requests in flight.) The ragged last chunk uses ordinary loads.
 // `lanes` (a power of two <= 32) threads share a row: lane q visits elements q, q + lanes, ...
 // in ascending order and the partial results are merged with shuffles (lowest index wins ties).
-template <typename T, bool SUM, bool ARG, bool MIN>
+template <typename T, bool SUM, bool ARG, bool MIN, bool PAD>
 __global__ void __launch_bounds__(kStagedThreads) reduce_rows_staged(const T* __restrict__ src, int64_t rows, int len,
                                                                     int rows_per_chunk, int lanes, Outputs out) {
+    constexpr bool padded = PAD;
+    // PAD (rows that are a multiple of 16 bytes): every staged row gets 16 bytes of padding
+    // and is read with 16-byte loads, which keeps rows of 64, 128, ... bytes off the same banks
     extern __shared__ __align__(128) unsigned char staged_smem[];
     using A = typename acc_of<T>::type;
     using C = typename cmp_of<T>::type;
-    const uint32_t chunk_bytes = static_cast<uint32_t>(rows_per_chunk) * len * sizeof(T);
-    const uint32_t buf_stride = (chunk_bytes + 127u) & ~127u;
+    const uint32_t row_bytes = static_cast<uint32_t>(len) * sizeof(T);
+    const uint32_t pitch = padded ? row_bytes + 16u : row_bytes;
+    const uint32_t vectors_per_row = row_bytes >> 4;
+    const uint32_t chunk_bytes = static_cast<uint32_t>(rows_per_chunk) * row_bytes;
+    const uint32_t buf_stride = (static_cast<uint32_t>(rows_per_chunk) * pitch + 127u) & ~127u;
     auto buffer = [&](int b) { return reinterpret_cast<T*>(staged_smem + static_cast<size_t>(b) * buf_stride); };
     const int64_t chunks = (rows + rows_per_chunk - 1) / rows_per_chunk;
     const uint32_t vectors = chunk_bytes >> 4;
@@ -216,8 +222,11 @@ __global__ void __launch_bounds__(kStagedThreads) reduce_rows_staged(const T* __
         if (chunk < chunks && first + rows_per_chunk <= rows) {
             const unsigned char* g = reinterpret_cast<const unsigned char*>(src + first * len);
             const uint32_t sbase = smem_addr(buffer(b));
-            for (uint32_t v = threadIdx.x; v < vectors; v += kStagedThreads)
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sbase + v * 16), "l"(g + static_cast<size_t>(v) * 16) : "memory");
+            for (uint32_t v = threadIdx.x; v < vectors; v += blockDim.x) {
+                uint32_t dst = v * 16;
+                if constexpr (PAD) dst += (v / vectors_per_row) * 16;  // one pad per completed row
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sbase + dst), "l"(g + static_cast<size_t>(v) * 16) : "memory");
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -233,13 +242,14 @@ __global__ void __launch_bounds__(kStagedThreads) reduce_rows_staged(const T* __
             asm volatile("cp.async.wait_group 1;" ::: "memory");  // all but the newest group have landed
         } else {
             const int64_t n = static_cast<int64_t>(here) * len;
-            for (int64_t i = threadIdx.x; i < n; i += kStagedThreads) buffer(b)[i] = src[first * len + i];
+            const int pad_elems = padded ? static_cast<int>(16 / sizeof(T)) : 0;
+            for (int64_t i = threadIdx.x; i < n; i += blockDim.x) buffer(b)[i + (i / len) * pad_elems] = src[first * len + i];
         }
         __syncthreads();
         {
             const int r = static_cast<int>(threadIdx.x) / lanes, q = static_cast<int>(threadIdx.x) % lanes;
             const bool active = r < here;
-            const T* row = buffer(b) + static_cast<int64_t>(active ? r : 0) * len;
+            const T* row = reinterpret_cast<const T*>(reinterpret_cast<const unsigned char*>(buffer(b)) + static_cast<size_t>(active ? r : 0) * pitch);
             A sum = A(0);
             C best = cmp_init<C, MIN>();
             int idx = INT_MAX;
@@ -250,7 +260,20 @@ __global__ void __launch_bounds__(kStagedThreads) reduce_rows_staged(const T* __
                     if (MIN ? (v < best) : (v > best)) { best = v; idx = j; }
                 }
             };
-            if (active) {
+            if constexpr (PAD) {
+              if (active) {
+                // 16-byte vectors, dealt to the row's lanes in turn: ascending indices per lane
+                constexpr int PER = 16 / static_cast<int>(sizeof(T));
+                const uint4* vecs = reinterpret_cast<const uint4*>(row);
+#pragma unroll 2
+                for (int c = q; c < static_cast<int>(vectors_per_row); c += lanes) {
+                    const uint4 v = vecs[c];
+                    const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+                    for (int k = 0; k < PER; ++k) feed(e[k], c * PER + k, sum);
+                }
+              }
+            } else if (active) {
                 if constexpr (sizeof(T) == 2) {
                     // 16-bit elements are read two at a time as 32-bit words. A row that starts on an
                     // odd element is peeled by one; lane 0 takes the peeled head and a leftover tail,
@@ -290,7 +313,7 @@ __global__ void __launch_bounds__(kStagedThreads) reduce_rows_staged(const T* __
                 }
                 if constexpr (ARG) {
                     if (out.index) out.index[o] = idx == INT_MAX ? 0 : idx;
-                    if (out.value) static_cast<T*>(out.value)[o] = idx == INT_MAX ? row[0] : from_compute<T, C>(best);
+                    if (out.value) static_cast<T*>(out.value)[o] = row[idx == INT_MAX ? 0 : idx];  // the element itself (keeps the sign of a zero)
                 }
             }
         }
@@ -522,6 +545,42 @@ __global__ void __launch_bounds__(kThreads) reduce_strided(const T* __restrict__
 // ------------------------------------------------------------------ host --------------
 int grid_cap() { return sm_count() * 8; }
 
+// Launch of the staged kernel. TN_UNSUPPORTED_DTYPE means "rows too long for a chunk" and sends
+// the caller on to the next kernel; it is never returned to the user from here.
+template <typename T, bool SUM, bool ARG, bool MIN, bool PAD>
+tn_status launch_staged(const T* p, int64_t total, int64_t len, int chunk_kb, Outputs out, cudaStream_t s) {
+    const int64_t row_bytes = len * (int64_t)sizeof(T);
+    const int64_t pitch = row_bytes + (PAD ? 16 : 0);
+    // threads per row: about 64 elements and up per thread. Fewer, longer scans measured
+    // faster than wide ones (197-wide bf16 rows: 2 threads per row 3.97 TB/s, 4 or 8: 3.48)
+    int lanes = 1;
+    while (lanes < 8 && len >= 128 * lanes) lanes *= 2;
+    if (const char* v = getenv("TN_REDUCE_LANES")) { const int n = atoi(v); if (n == 1 || n == 2 || n == 4 || n == 8) lanes = n; }
+    int rpc = (int)((int64_t(chunk_kb) << 10) / pitch);
+    if (rpc > kStagedThreads / lanes) rpc = kStagedThreads / lanes;
+    rpc &= ~15;  // a chunk of 16 rows is a multiple of 16 bytes for any row length
+    if (rpc < 16) return TN_UNSUPPORTED_DTYPE;
+    const int threads = (rpc * lanes + 31) & ~31;  // one group of `lanes` threads per row of a chunk
+    const size_t buf = ((size_t)rpc * pitch + 127) & ~size_t(127);
+    const size_t smem = 2 * buf;
+    static thread_local int attr_device = -1;
+    int dev = 0;
+    TN_CUDA(cudaGetDevice(&dev));
+    if (attr_device != dev) {
+        TN_CUDA(cudaFuncSetAttribute(reduce_rows_staged<T, SUM, ARG, MIN, PAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 << 10));
+        attr_device = dev;
+    }
+    const int64_t chunks = ceil_div(total, rpc);
+    int64_t per_sm = (int64_t(220) << 10) / (int64_t)smem;  // CTAs that fit the shared memory of an SM
+    if (per_sm > 2048 / threads) per_sm = 2048 / threads;
+    if (per_sm > 16) per_sm = 16;
+    if (per_sm < 1) per_sm = 1;
+    int64_t grid = (int64_t)sm_count() * per_sm;
+    if (grid > chunks) grid = chunks;
+    reduce_rows_staged<T, SUM, ARG, MIN, PAD><<<(unsigned)grid, threads, smem, s>>>(p, total, (int)len, rpc, lanes, out);
+    return after_launch("reduce_rows_staged");
+}
+
 template <typename T, bool SUM, bool ARG, bool MIN>
 tn_status launch(const tn_tensor_t* src, int axis, Outputs out, cudaStream_t s) {
     const int R = src->rank;
@@ -565,29 +624,10 @@ tn_status launch(const tn_tensor_t* src, int axis, Outputs out, cudaStream_t s) 
             // chunk is a multiple of 16 bytes for any row length
             int chunk_kb = 50;
             if (const char* v = getenv("TN_REDUCE_CHUNK_KB")) { const int n = atoi(v); if (n >= 4 && n <= 52) chunk_kb = n; }
-            int rpc = (int)((int64_t(chunk_kb) << 10) / row_bytes) & ~15;
-            if (rpc > 128) rpc = 128;
-            if (rpc >= 16) {
-                int lanes = 4;  // threads per row: as many as the CTA can spare, at most a warp
-                while (lanes < 32 && rpc * lanes * 2 <= kStagedThreads) lanes *= 2;
-                const size_t buf = ((size_t)rpc * row_bytes + 127) & ~size_t(127);
-                const size_t smem = 2 * buf;
-                static thread_local int attr_device = -1;
-                int dev = 0;
-                TN_CUDA(cudaGetDevice(&dev));
-                if (attr_device != dev) {
-                    TN_CUDA(cudaFuncSetAttribute(reduce_rows_staged<T, SUM, ARG, MIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 << 10));
-                    attr_device = dev;
-                }
-                const int64_t chunks = ceil_div(total, rpc);
-                int64_t per_sm = (int64_t(220) << 10) / (int64_t)smem;  // CTAs that fit the shared memory of an SM
-                if (per_sm > 2048 / kStagedThreads) per_sm = 2048 / kStagedThreads;
-                if (per_sm < 1) per_sm = 1;
-                int64_t grid = (int64_t)sm_count() * per_sm;
-                if (grid > chunks) grid = chunks;
-                reduce_rows_staged<T, SUM, ARG, MIN><<<(unsigned)grid, kStagedThreads, smem, s>>>(p, total, (int)len, rpc, lanes, out);
-                return after_launch("reduce_rows_staged");
-            }
+            const bool padded = row_bytes % 16 == 0;
+            tn_status st = padded ? launch_staged<T, SUM, ARG, MIN, true>(p, total, len, chunk_kb, out, s)
+                                  : launch_staged<T, SUM, ARG, MIN, false>(p, total, len, chunk_kb, out, s);
+            if (st != TN_UNSUPPORTED_DTYPE) return st;  // else: the rows do not fit this kernel, fall through
         }
         if (row_bytes >= 16384) {
             const int grid = (int)(total < cap ? total : cap);

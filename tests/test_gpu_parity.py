@@ -271,6 +271,44 @@ def test_reductions_many_short_rows_staged_in_shared_memory(dtype, shape):
     assert tb.device_errors() == 0
 
 
+@pytest.mark.parametrize("dtype", HALVES)
+@pytest.mark.parametrize("length", [197, 64, 33, 256, 510])
+def test_staged_rows_ties_zeros_nan_and_infinities(dtype, length):
+    """Short 16-bit rows are scanned two elements per instruction; only the group of the last strict
+    improvement is remembered. Rows drawn from a handful of values put ties in every group; signed
+    zeros, NaN and infinities are sprinkled in, and some rows hold nothing but -inf / NaN."""
+    rows = 4200
+    g = torch.Generator().manual_seed(length)
+    palette = torch.tensor([-2.0, -1.0, -0.0, 0.0, 0.5, 1.0, 1.0, 3.0], dtype=torch.float32)
+    x = palette[torch.randint(0, len(palette), (rows, length), generator=g)]
+    special = torch.rand((rows, length), generator=g)
+    x[special < 0.02] = float("nan")
+    x[(special >= 0.02) & (special < 0.04)] = float("inf")
+    x[(special >= 0.04) & (special < 0.06)] = float("-inf")
+    x[7] = float("-inf")
+    x[8] = float("nan")
+    x[9] = float("-inf")
+    x[9, length - 1] = float("nan")
+    x[10, :] = -0.0
+    x[10, length // 2] = 0.0        # +0 after -0: not greater, the first zero stays
+    x[11, :] = -5.0
+    x[11, length - 1] = -4.0        # the improvement sits in the very last element
+    x[12, :] = -5.0
+    x[12, 0] = -4.0                 # ... and in the very first
+    x = x.to(dtype)
+    dx = dev(x)
+    for kind in ("argmax", "argmin"):
+        assert_same(getattr(tb, kind)(dx, -1), oracle.reduce(kind, x, -1))
+    got, want = tb.max(dx, -1).cpu(), oracle.reduce("max", x, -1)
+    both_nan = torch.isnan(got.float()) & torch.isnan(want.float())
+    assert torch.equal(got.view(torch.int16)[~both_nan], want.view(torch.int16)[~both_nan])
+    mx, sm, am = tb.reduce_stats(dx, -1)
+    assert_same(am, oracle.reduce("argmax", x, -1))
+    # views that start on an odd element: every row is peeled by one
+    v, dv = x[:, 1:], dx[:, 1:]
+    assert_same(tb.argmax(dv.contiguous(), -1), oracle.reduce("argmax", v.contiguous(), -1))
+
+
 def test_reduce_split_path_for_few_long_rows():
     x = gen((2, 1 << 20), torch.float32, 25, -1.0, 1.0)
     assert_close(tb.sum(dev(x), -1), oracle.reduce("sum", x, -1, acc=oracle.ACC_WIDE))
