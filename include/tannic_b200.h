@@ -240,6 +240,34 @@ tn_status tn_conv2d_bias(const tn_tensor_t* x, const tn_tensor_t* w, const tn_te
 tn_status tn_conv1d(const tn_tensor_t* x, const tn_tensor_t* w, tn_tensor_t* y, tn_stream_t stream,
                     size_t pad, size_t stride);
 
+/* ------------------------------------------------------------------ data movement ---- */
+
+/* reference: cuda::outer, src/cuda/outer.cu (CPU twin src/cpu/outer.cpp:25-104): dst[i][j] =
+ * a[i] * b[j] for two vectors; dtype pairs and the result type are those of the broadcast
+ * multiply (the result is written as dst->dtype, never wider). */
+tn_status tn_outer(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream);
+/* reference: cuda::repeat, src/cuda/reps.cu (CPU twin src/cpu/reps.cpp:16-97): every element along
+ * `axis` repeated `reps` times in a row (repeat_interleave); dst is dense with
+ * shape[axis] * reps; src may be any view of rank <= 7. */
+tn_status tn_repeat(const tn_tensor_t* src, tn_tensor_t* dst, int axis, int reps, tn_stream_t stream);
+/* reference: cuda::concat, src/cuda/concat.cu (CPU twin src/cpu/concat.cpp:15-127): a then b along
+ * `axis` into a dense dst; operands may be any views. (The reference's CPU loop indexes the inner
+ * block with the stride of dimension axis + 1 only, which is right for axis >= rank - 2; this entry
+ * point concatenates correctly for every axis.) */
+tn_status tn_concat(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream, int axis);
+/* reference: cuda::triu / cuda::tril, src/cuda/traing.cu (CPU twin src/cpu/triang.cpp:3-103):
+ * matrices only; triu keeps j >= i + k, tril keeps j <= i + k, the rest becomes zero. i + k is
+ * evaluated in signed arithmetic (the reference adds k to an unsigned row index, which goes wrong
+ * for negative k). */
+tn_status tn_triu(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, int k);
+tn_status tn_tril(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, int k);
+/* reference: cuda::view_as_cartesian / cuda::view_as_polar, src/cuda/complex.cu (CPU twin
+ * src/cpu/complex.cpp:14-228): complex dst (interleaved re, im; dense) from two real tensors of the
+ * result's rank with size-1 broadcasting: (re, im), or (rho cos theta, rho sin theta). float32 parts
+ * give complex64, any float64 part complex128; polar also takes integer parts (as float32). */
+tn_status tn_view_as_cartesian(const tn_tensor_t* re, const tn_tensor_t* im, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_view_as_polar(const tn_tensor_t* rho, const tn_tensor_t* theta, tn_tensor_t* dst, tn_stream_t stream);
+
 /* ------------------------------------------------------------------ reductions ------- */
 
 /* reference: cuda::argmax/argmin/argsum/argmean, src/cuda/argred.cu:167-213 (CPU twin

@@ -53,6 +53,10 @@ def port() -> C.CDLL:
         lib.orc_reduce.argtypes = [C.c_int, _TP, _TP, C.c_uint8, C.c_int]
         lib.orc_cpy.argtypes = [_TP, _TP]
         lib.orc_allclose.argtypes = [_TP, _TP, C.c_double, C.c_double, C.POINTER(C.c_int)]
+        lib.orc_repeat.argtypes = [_TP, _TP, C.c_int, C.c_int]
+        lib.orc_concat.argtypes = [_TP, _TP, _TP, C.c_int]
+        lib.orc_triangular.argtypes = [_TP, _TP, C.c_int, C.c_int]
+        lib.orc_complex_pair.argtypes = [_TP, _TP, _TP, C.c_int]
         lib.orc_fill.argtypes = [C.c_void_p, C.c_int, C.c_size_t, C.c_uint64, C.c_int, C.c_double, C.c_double]
         _port = lib
     return _port
@@ -75,6 +79,13 @@ def ref():
             getattr(lib, f"ref_{n}").argtypes = [_TP, _TP, C.c_uint8]
         lib.ref_cpy.argtypes = [_TP, _TP]
         lib.ref_allclose.argtypes = [_TP, _TP, C.c_double, C.c_double]
+        lib.ref_outer.argtypes = [_TP, _TP, _TP]
+        lib.ref_repeat.argtypes = [_TP, _TP, C.c_int, C.c_int]
+        lib.ref_concat.argtypes = [_TP, _TP, _TP, C.c_int]
+        lib.ref_triu.argtypes = [_TP, _TP, C.c_int]
+        lib.ref_tril.argtypes = [_TP, _TP, C.c_int]
+        lib.ref_view_as_cartesian.argtypes = [_TP, _TP, _TP]
+        lib.ref_view_as_polar.argtypes = [_TP, _TP, _TP]
         _ref = lib
     return _ref
 
@@ -186,4 +197,69 @@ def reduce(kind, x, axis=-1, keepdim=False, acc=ACC_WIDE, impl="port"):
     else:
         name = {"sum": "argsum", "mean": "argmean"}.get(kind, kind)
         _ok(getattr(ref(), f"ref_{name}")(C.byref(dx), C.byref(dd), ax))
+    return out
+
+
+# ---- data movement around the path -------------------------------------------------------
+
+def outer(a, b, out_dtype=None, impl="port"):
+    """a[i] * b[j]. The restatement is the broadcast multiply of two views, written in the promoted
+    dtype; the reference kernel (impl="ref") writes the type of its own table entry, which is wider
+    than the promoted one for some pairs, so `out_dtype` must name that type there."""
+    if impl == "port":
+        return binary("mul", a[:, None], b[None, :], out_dtype=out_dtype)
+    dt = out_dtype if out_dtype is not None else max(TORCH_TO_TN[a.dtype], TORCH_TO_TN[b.dtype])
+    out = _empty((a.shape[0], b.shape[0]), dt)
+    da, db, dd = desc(a), desc(b), desc(out)
+    _ok(ref().ref_outer(C.byref(da), C.byref(db), C.byref(dd)))
+    return out
+
+
+def repeat(x, repeats, axis, impl="port"):
+    axis = axis % x.dim()
+    shape = list(x.shape)
+    shape[axis] *= repeats
+    out = _empty(shape, TORCH_TO_TN[x.dtype])
+    dx, dd = desc(x), desc(out)
+    if impl == "port":
+        _ok(port().orc_repeat(C.byref(dx), C.byref(dd), axis, repeats))
+    else:
+        _ok(ref().ref_repeat(C.byref(dx), C.byref(dd), axis, repeats))
+    return out
+
+
+def concat(a, b, axis=0, impl="port"):
+    axis = axis % a.dim()
+    shape = list(a.shape)
+    shape[axis] += b.shape[axis]
+    out = _empty(shape, TORCH_TO_TN[a.dtype])
+    da, db, dd = desc(a), desc(b), desc(out)
+    if impl == "port":
+        _ok(port().orc_concat(C.byref(da), C.byref(db), C.byref(dd), axis))
+    else:
+        _ok(ref().ref_concat(C.byref(da), C.byref(db), C.byref(dd), axis))
+    return out
+
+
+def triangular(x, upper, k=0, impl="port"):
+    out = _empty(x.shape, TORCH_TO_TN[x.dtype])
+    dx, dd = desc(x), desc(out)
+    if impl == "port":
+        _ok(port().orc_triangular(C.byref(dx), C.byref(dd), 1 if upper else 0, k))
+    else:
+        _ok((ref().ref_triu if upper else ref().ref_tril)(C.byref(dx), C.byref(dd), k))
+    return out
+
+
+def complex_pair(a, b, polar, impl="port"):
+    wide = torch.float64 in (a.dtype, b.dtype)
+    out = _empty(broadcast_shape(a.shape, b.shape), A.COMPLEX128 if wide else A.COMPLEX64)
+    rank = out.dim()
+    a = a.reshape((1,) * (rank - a.dim()) + tuple(a.shape))
+    b = b.reshape((1,) * (rank - b.dim()) + tuple(b.shape))
+    da, db, dd = desc(a), desc(b), desc(out)
+    if impl == "port":
+        _ok(port().orc_complex_pair(C.byref(da), C.byref(db), C.byref(dd), 1 if polar else 0))
+    else:
+        _ok((ref().ref_view_as_polar if polar else ref().ref_view_as_cartesian)(C.byref(da), C.byref(db), C.byref(dd)))
     return out

@@ -21,6 +21,11 @@
 #include "cpu/matmul.hpp"
 #include "cpu/ops.hpp"
 #include "cpu/val.hpp"
+#include "cpu/outer.hpp"
+#include "cpu/reps.hpp"
+#include "cpu/concat.hpp"
+#include "cpu/triang.hpp"
+#include "cpu/complex.hpp"
 
 #include "tannic_b200.h"
 
@@ -83,6 +88,13 @@ int ref_argsum(const tensor_t* x, tensor_t* d, uint8_t axis) { return cpu::argsu
 int ref_argmean(const tensor_t* x, tensor_t* d, uint8_t axis) { return cpu::argmean(x, d, axis); }
 
 int ref_cpy(const tensor_t* x, tensor_t* d) { return cpu::cpy(x, d); }
+int ref_outer(const tensor_t* a, const tensor_t* b, tensor_t* d) { return cpu::outer(a, b, d); }
+int ref_repeat(const tensor_t* x, tensor_t* d, int axis, int reps) { return cpu::repeat(x, d, axis, reps); }
+int ref_concat(const tensor_t* a, const tensor_t* b, tensor_t* d, int axis) { return cpu::concat(a, b, d, axis); }
+int ref_triu(const tensor_t* x, tensor_t* d, int k) { return cpu::triu(x, d, k); }
+int ref_tril(const tensor_t* x, tensor_t* d, int k) { return cpu::tril(x, d, k); }
+int ref_view_as_cartesian(const tensor_t* a, const tensor_t* b, tensor_t* d) { return cpu::view_as_cartesian(a, b, d); }
+int ref_view_as_polar(const tensor_t* a, const tensor_t* b, tensor_t* d) { return cpu::view_as_polar(a, b, d); }
 int ref_allclose(const tensor_t* a, const tensor_t* b, double rtol, double atol) {
     try {
         return cpu::allclose(a, b, rtol, atol) ? 1 : 0;

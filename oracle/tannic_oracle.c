@@ -626,6 +626,133 @@ tn_status orc_allclose(const tn_tensor_t* a, const tn_tensor_t* b, double rtol, 
     return TN_SUCCESS;
 }
 
+/* ------------------------------------------------------------------ data movement ------ */
+
+/* src/cpu/reps.cpp:16-97: the result is dense; for every index of the dimensions before `axis`,
+ * every element j of the axis is written `reps` times in a row, each time with the whole inner
+ * block that follows the axis. Source offsets honour the source's strides. */
+tn_status orc_repeat(const tn_tensor_t* s, tn_tensor_t* d, int axis, int reps) {
+    const size_t esize = dtype_bytes((int)s->dtype);
+    if (s->dtype != d->dtype || esize == 0) return TN_UNSUPPORTED_DTYPE;
+    const int rank = s->rank;
+    if (axis < 0 || axis >= rank || reps < 1) return TN_ERROR;
+    size_t outer = 1, inner = 1;
+    for (int i = 0; i < axis; ++i) outer *= s->shape.sizes[i];
+    for (int i = axis + 1; i < rank; ++i) inner *= s->shape.sizes[i];
+    char* out = (char*)d->address;
+    for (size_t o = 0; o < outer; ++o) {
+        int64_t obase = 0;
+        size_t t = o;
+        for (int i = axis - 1; i >= 0; --i) {
+            obase += (int64_t)(t % s->shape.sizes[i]) * s->strides.sizes[i];
+            t /= s->shape.sizes[i];
+        }
+        for (size_t j = 0; j < s->shape.sizes[axis]; ++j) {
+            for (int r = 0; r < reps; ++r) {
+                for (size_t k = 0; k < inner; ++k) {
+                    int64_t off = obase + (int64_t)j * s->strides.sizes[axis];
+                    size_t tk = k;
+                    for (int i = rank - 1; i > axis; --i) {
+                        off += (int64_t)(tk % s->shape.sizes[i]) * s->strides.sizes[i];
+                        tk /= s->shape.sizes[i];
+                    }
+                    memcpy(out, (const char*)s->address + off * (int64_t)esize, esize);
+                    out += esize;
+                }
+            }
+        }
+    }
+    return TN_SUCCESS;
+}
+
+/* src/cpu/concat.cpp:15-127: dense result; per index of the dimensions before `axis`, the block
+ * of a, then the block of b. The inner block is walked through the operand's own strides for
+ * every trailing dimension (the reference multiplies a flat inner index by the stride of
+ * dimension axis + 1 alone, which is the same thing only for axis >= rank - 2). */
+tn_status orc_concat(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* d, int axis) {
+    const size_t esize = dtype_bytes((int)d->dtype);
+    if (a->dtype != d->dtype || b->dtype != d->dtype || esize == 0) return TN_UNSUPPORTED_DTYPE;
+    const int rank = d->rank;
+    if (axis < 0 || axis >= rank) return TN_ERROR;
+    size_t outer = 1, inner = 1;
+    for (int i = 0; i < axis; ++i) outer *= d->shape.sizes[i];
+    for (int i = axis + 1; i < rank; ++i) inner *= d->shape.sizes[i];
+    char* out = (char*)d->address;
+    for (size_t o = 0; o < outer; ++o) {
+        for (int which = 0; which < 2; ++which) {
+            const tn_tensor_t* s = which ? b : a;
+            int64_t obase = 0;
+            size_t t = o;
+            for (int i = axis - 1; i >= 0; --i) {
+                obase += (int64_t)(t % s->shape.sizes[i]) * s->strides.sizes[i];
+                t /= s->shape.sizes[i];
+            }
+            for (size_t j = 0; j < s->shape.sizes[axis]; ++j) {
+                for (size_t k = 0; k < inner; ++k) {
+                    int64_t off = obase + (int64_t)j * s->strides.sizes[axis];
+                    size_t tk = k;
+                    for (int i = rank - 1; i > axis; --i) {
+                        off += (int64_t)(tk % s->shape.sizes[i]) * s->strides.sizes[i];
+                        tk /= s->shape.sizes[i];
+                    }
+                    memcpy(out, (const char*)s->address + off * (int64_t)esize, esize);
+                    out += esize;
+                }
+            }
+        }
+    }
+    return TN_SUCCESS;
+}
+
+/* src/cpu/triang.cpp:3-103: matrices; upper keeps j >= i + k, lower keeps j <= i + k, every other
+ * element becomes zero. i + k in signed arithmetic (the reference's unsigned sum differs for k < 0). */
+tn_status orc_triangular(const tn_tensor_t* s, tn_tensor_t* d, int upper, int k) {
+    const size_t esize = dtype_bytes((int)s->dtype);
+    if (s->rank != 2 || d->rank != 2 || s->dtype != d->dtype || !is_numeric((int)s->dtype)) return TN_UNSUPPORTED_DTYPE;
+    for (int64_t i = 0; i < (int64_t)s->shape.sizes[0]; ++i) {
+        for (int64_t j = 0; j < (int64_t)s->shape.sizes[1]; ++j) {
+            const int keep = upper ? (j >= i + k) : (j <= i + k);
+            char* out = (char*)d->address + (i * d->strides.sizes[0] + j * d->strides.sizes[1]) * (int64_t)esize;
+            if (keep) memcpy(out, (const char*)s->address + (i * s->strides.sizes[0] + j * s->strides.sizes[1]) * (int64_t)esize, esize);
+            else memset(out, 0, esize);
+        }
+    }
+    return TN_SUCCESS;
+}
+
+/* src/cpu/complex.cpp:14-228: complex result (interleaved, dense) from two real tensors of the same
+ * rank with size-1 broadcasting; polar = (rho cos theta, rho sin theta). float32 arithmetic unless a
+ * part is float64. */
+tn_status orc_complex_pair(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* d, int polar) {
+    const int wide = a->dtype == TN_FLOAT64 || b->dtype == TN_FLOAT64;
+    if ((int)d->dtype != (wide ? TN_COMPLEX128 : TN_COMPLEX64)) return TN_UNSUPPORTED_DTYPE;
+    const int rank = d->rank;
+    size_t cnt[TN_MAX_RANK] = {0};
+    for (size_t idx = 0; idx < d->size; ++idx) {
+        int64_t oa = 0, ob = 0;
+        for (int dim = 0; dim < rank; ++dim) {
+            oa += (int64_t)(a->shape.sizes[dim] == 1 ? 0 : cnt[dim]) * a->strides.sizes[dim];
+            ob += (int64_t)(b->shape.sizes[dim] == 1 ? 0 : cnt[dim]) * b->strides.sizes[dim];
+        }
+        if (wide) {
+            const double x = load_f64(a->address, (int)a->dtype, oa), y = load_f64(b->address, (int)b->dtype, ob);
+            double* out = (double*)d->address + 2 * idx;
+            out[0] = polar ? x * cos(y) : x;
+            out[1] = polar ? x * sin(y) : y;
+        } else {
+            const float x = load_f32(a->address, (int)a->dtype, oa), y = load_f32(b->address, (int)b->dtype, ob);
+            float* out = (float*)d->address + 2 * idx;
+            out[0] = polar ? x * cosf(y) : x;
+            out[1] = polar ? x * sinf(y) : y;
+        }
+        for (int dim = rank - 1; dim >= 0; --dim) {
+            if (++cnt[dim] < d->shape.sizes[dim]) break;
+            cnt[dim] = 0;
+        }
+    }
+    return TN_SUCCESS;
+}
+
 /* ------------------------------------------------------------------ input generator ---- */
 
 /* Counter-based generator shared by the tests and the benchmark so that host and device runs

@@ -114,6 +114,13 @@ PROTOTYPES = {
     "tn_conv2d": [_TP, _TP, _TP, StreamT, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)],
     "tn_conv2d_bias": [_TP, _TP, _TP, _TP, StreamT, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)],
     "tn_conv1d": [_TP, _TP, _TP, StreamT, C.c_size_t, C.c_size_t],
+    "tn_outer": [_TP, _TP, _TP, StreamT],
+    "tn_repeat": [_TP, _TP, C.c_int, C.c_int, StreamT],
+    "tn_concat": [_TP, _TP, _TP, StreamT, C.c_int],
+    "tn_triu": [_TP, _TP, StreamT, C.c_int],
+    "tn_tril": [_TP, _TP, StreamT, C.c_int],
+    "tn_view_as_cartesian": [_TP, _TP, _TP, StreamT],
+    "tn_view_as_polar": [_TP, _TP, _TP, StreamT],
     "tn_reduce_stats": [_TP, _TP, _TP, _TP, StreamT, C.c_uint8],
     "tn_argsum_fixed_scratch": [_TP, _TP, StreamT, C.c_uint8],
     "tn_cpy": [_TP, _TP, StreamT],

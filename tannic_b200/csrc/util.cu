@@ -54,13 +54,31 @@ __global__ void __launch_bounds__(kThreads) allclose_kernel(const T* __restrict_
 // Geometry over `shape_of`'s logical shape; extent-1 dims of either side read offset 0
 // (src/cpu/cpy.cpp:19-43).
 void make_geom(const tn_tensor_t* a, const tn_tensor_t* b, const tn_tensor_t* shape_of, PairGeom& g) {
-    g.rank = shape_of->rank;
+    int64_t sizes[TN_MAX_RANK], sa[TN_MAX_RANK], sb[TN_MAX_RANK];
+    int rank = 0;
     g.n = 1;
-    for (int d = 0; d < g.rank; ++d) {
-        g.sizes[d] = (int64_t)shape_of->shape.sizes[d];
-        g.n *= g.sizes[d];
-        g.sa[d] = a->shape.sizes[d] == 1 ? 0 : a->strides.sizes[d];
-        g.sb[d] = b->shape.sizes[d] == 1 ? 0 : b->strides.sizes[d];
+    for (int d = 0; d < shape_of->rank; ++d) {
+        const int64_t sz = (int64_t)shape_of->shape.sizes[d];
+        g.n *= sz;
+        if (sz == 1) continue;  // contributes offset 0 on both sides
+        sizes[rank] = sz;
+        sa[rank] = a->shape.sizes[d] == 1 ? 0 : a->strides.sizes[d];
+        sb[rank] = b->shape.sizes[d] == 1 ? 0 : b->strides.sizes[d];
+        ++rank;
+    }
+    // merge neighbours that both sides walk as one run: fewer divisions per element
+    g.rank = 0;
+    for (int d = 0; d < rank; ++d) {
+        if (g.rank > 0 && g.sa[g.rank - 1] == sa[d] * sizes[d] && g.sb[g.rank - 1] == sb[d] * sizes[d]) {
+            g.sizes[g.rank - 1] *= sizes[d];
+            g.sa[g.rank - 1] = sa[d];
+            g.sb[g.rank - 1] = sb[d];
+        } else {
+            g.sizes[g.rank] = sizes[d];
+            g.sa[g.rank] = sa[d];
+            g.sb[g.rank] = sb[d];
+            ++g.rank;
+        }
     }
 }
 

@@ -3,8 +3,7 @@
 // reductions.cpp, resources.cpp, bindings.cpp, tensor.cpp, comparisons.cpp, IO.cpp, filter.cpp,
 // complex.cpp) by forwarding to the C ABI of libtannic_b200.so. It is compiled against the
 // reference's own headers (their declarations are the contract), replaces all of src/cuda/*.cu and
-// needs no other change to the reference. Device functions outside the operator hot path
-// (outer, repeat, concat, triangular masks, complex views) report UNSUPPORTED_DTYPE.
+// needs no other change to the reference.
 #include <cstdint>
 #include <new>
 #include <stdexcept>
@@ -84,13 +83,13 @@ bool allclose(const tensor_t* a, const tensor_t* b, stream_t s, double rtol, dou
 }
 
 // ---- outside the operator hot path: not provided by this backend --------------------------------
-status outer(tensor_t const*, tensor_t const*, tensor_t*, stream_t) { return UNSUPPORTED_DTYPE; }
-status repeat(const tensor_t*, tensor_t*, int, int, stream_t) { return UNSUPPORTED_DTYPE; }
-status concat(const tensor_t*, const tensor_t*, tensor_t*, stream_t, int) { return UNSUPPORTED_DTYPE; }
-status triu(const tensor_t*, tensor_t*, stream_t, int) { return UNSUPPORTED_DTYPE; }
-status tril(const tensor_t*, tensor_t*, stream_t, int) { return UNSUPPORTED_DTYPE; }
-status view_as_cartesian(tensor_t const*, tensor_t const*, tensor_t*, stream_t) { return UNSUPPORTED_DTYPE; }
-status view_as_polar(const tensor_t*, const tensor_t*, tensor_t*, stream_t) { return UNSUPPORTED_DTYPE; }
+status outer(tensor_t const* a, tensor_t const* b, tensor_t* d, stream_t s) { return st(tn_outer(in(a), in(b), out(d), on(s))); }
+status repeat(const tensor_t* x, tensor_t* d, int axis, int reps, stream_t s) { return st(tn_repeat(in(x), out(d), axis, reps, on(s))); }
+status concat(const tensor_t* a, const tensor_t* b, tensor_t* d, stream_t s, int axis) { return st(tn_concat(in(a), in(b), out(d), on(s), axis)); }
+status triu(const tensor_t* x, tensor_t* d, stream_t s, int k) { return st(tn_triu(in(x), out(d), on(s), k)); }
+status tril(const tensor_t* x, tensor_t* d, stream_t s, int k) { return st(tn_tril(in(x), out(d), on(s), k)); }
+status view_as_cartesian(tensor_t const* re, tensor_t const* im, tensor_t* d, stream_t s) { return st(tn_view_as_cartesian(in(re), in(im), out(d), on(s))); }
+status view_as_polar(const tensor_t* rho, const tensor_t* theta, tensor_t* d, stream_t s) { return st(tn_view_as_polar(in(rho), in(theta), out(d), on(s))); }
 
 // ---- memory and streams --------------------------------------------------------------------------
 int getDeviceCount() {

@@ -23,6 +23,7 @@ from . import _abi as A
 TORCH_TO_TN = {
     torch.int8: A.INT8, torch.int16: A.INT16, torch.int32: A.INT32, torch.int64: A.INT64,
     torch.float16: A.FLOAT16, torch.bfloat16: A.BFLOAT16, torch.float32: A.FLOAT32, torch.float64: A.FLOAT64,
+    torch.complex64: A.COMPLEX64, torch.complex128: A.COMPLEX128,
 }
 TN_TO_TORCH = {v: k for k, v in TORCH_TO_TN.items()}
 
@@ -198,6 +199,68 @@ def convolve2D(x: torch.Tensor, w: torch.Tensor, stride=1, padding=0, bias: torc
         dbias = desc(bias)
         A.check(A.lib().tn_conv2d_bias(C.byref(dx), C.byref(dw), C.byref(dbias), C.byref(dd), current_stream(x), pad, strd))
     return out
+
+
+def outer(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """include/tannic/transformations.hpp (Outer): two vectors, promoted dtype, shape [len(a), len(b)]."""
+    if a.dim() != 1 or b.dim() != 1:
+        raise ValueError("Outer product of tensors with rank more than 1 not supported.")
+    out = _empty((a.shape[0], b.shape[0]), _b.max(TORCH_TO_TN[a.dtype], TORCH_TO_TN[b.dtype]), a)
+    da, db, dd = desc(a), desc(b), desc(out)
+    A.check(A.lib().tn_outer(C.byref(da), C.byref(db), C.byref(dd), current_stream(a)))
+    return out
+
+
+def repeat(x: torch.Tensor, repeats: int, axis: int) -> torch.Tensor:
+    """include/tannic/transformations.hpp (Repetition): every element along `axis` `repeats` times in a row."""
+    axis = axis % x.dim()
+    shape = list(x.shape)
+    shape[axis] *= repeats
+    out = _empty(shape, TORCH_TO_TN[x.dtype], x)
+    dx, dd = desc(x), desc(out)
+    A.check(A.lib().tn_repeat(C.byref(dx), C.byref(dd), axis, repeats, current_stream(x)))
+    return out
+
+
+def concatenate(a: torch.Tensor, b: torch.Tensor, axis: int = 0) -> torch.Tensor:
+    """include/tannic/transformations.hpp (Concatenation): same dtype, same shape off the axis."""
+    if a.dtype != b.dtype:
+        raise ValueError("Cannot concatenate tensors of different dtypes.")
+    axis = axis % a.dim()
+    shape = list(a.shape)
+    shape[axis] += b.shape[axis]
+    out = _empty(shape, TORCH_TO_TN[a.dtype], a)
+    da, db, dd = desc(a), desc(b), desc(out)
+    A.check(A.lib().tn_concat(C.byref(da), C.byref(db), C.byref(dd), current_stream(a), axis))
+    return out
+
+
+def _triangular(name: str, x: torch.Tensor, k: int) -> torch.Tensor:
+    out = _empty(x.shape, TORCH_TO_TN[x.dtype], x)
+    dx, dd = desc(x), desc(out)
+    A.check(getattr(A.lib(), f"tn_{name}")(C.byref(dx), C.byref(dd), current_stream(x), k))
+    return out
+
+
+def triu(x, k: int = 0): return _triangular("triu", x, k)
+def tril(x, k: int = 0): return _triangular("tril", x, k)
+
+
+def _complex_from(name: str, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """include/tannic/complex.hpp (Cartesian / Polar): complex64 from float32 parts, complex128 as soon
+    as one part is float64."""
+    wide = torch.float64 in (a.dtype, b.dtype)
+    out = _empty(broadcast_shape(a.shape, b.shape), A.COMPLEX128 if wide else A.COMPLEX64, a)
+    rank = out.dim()
+    a = a.reshape((1,) * (rank - a.dim()) + tuple(a.shape))
+    b = b.reshape((1,) * (rank - b.dim()) + tuple(b.shape))
+    da, db, dd = desc(a), desc(b), desc(out)
+    A.check(getattr(A.lib(), f"tn_{name}")(C.byref(da), C.byref(db), C.byref(dd), current_stream(a)))
+    return out
+
+
+def cartesian(re, im): return _complex_from("view_as_cartesian", re, im)
+def polar(rho, theta): return _complex_from("view_as_polar", rho, theta)
 
 
 def _reduced_shape(shape, axis: int, keepdim: bool):

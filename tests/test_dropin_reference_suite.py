@@ -11,7 +11,8 @@ from pathlib import Path
 import pytest
 
 BUILD = Path(__file__).resolve().parent.parent / "tannic_b200" / "dropin" / "_build"
-SUITES = ["allocations", "convolutions", "functions", "indexing", "matmul", "operations", "reductions"]
+SUITES = ["allocations", "complex", "concat", "convolutions", "functions", "indexing", "matmul", "operations", "outer",
+          "reductions", "repeats"]
 
 
 @pytest.mark.gpu

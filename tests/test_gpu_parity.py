@@ -417,6 +417,75 @@ def test_matmul_errors():
     assert e.value.status == A.UNSUPPORTED_DTYPE
 
 
+# ---------------------------------------------------------------- data movement --------
+
+@pytest.mark.parametrize("pair", [(torch.float32, torch.float32), (torch.float16, torch.float16), (torch.bfloat16, torch.float32),
+                                  (torch.int32, torch.int32), (torch.int8, torch.int64), (torch.float64, torch.int32)])
+def test_outer(pair):
+    a, b = gen((37,), pair[0], 70, -2, 2), gen((53,), pair[1], 71, -2, 2)
+    want = oracle.outer(a, b)
+    got = tb.outer(dev(a), dev(b))
+    (assert_same if want.dtype in INTS or pair[0] == pair[1] else assert_close)(got, want)
+    assert_same(tb.outer(dev(a)[::2], dev(b)[1::3]), oracle.outer(a[::2], b[1::3])) if pair[0] == pair[1] else None
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int8, torch.int64, torch.float64])
+@pytest.mark.parametrize("axis", [0, 1, 2, -1])
+def test_repeat(dtype, axis):
+    x = gen((5, 6, 7), dtype, 72)
+    assert_same(tb.repeat(dev(x), 3, axis), oracle.repeat(x, 3, axis))
+    assert_same(tb.repeat(dev(x).transpose(0, 2), 2, axis), oracle.repeat(x.transpose(0, 2), 2, axis))  # tests/cpu/test-repeats.cpp: after permute
+    assert_same(tb.repeat(dev(x), 1, axis), x)
+    big = gen((64, 129, 33), dtype, 73)
+    assert_same(tb.repeat(dev(big), 4, 1), torch.repeat_interleave(big, 4, 1))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.int32, torch.float64])
+def test_concat(dtype):
+    a, b = gen((3, 4, 5), dtype, 74), gen((2, 4, 5), dtype, 75)
+    assert_same(tb.concatenate(dev(a), dev(b), 0), oracle.concat(a, b, 0))  # the axis the reference's CPU loop gets wrong
+    c = gen((3, 9, 5), dtype, 76)
+    assert_same(tb.concatenate(dev(a), dev(c), 1), oracle.concat(a, c, 1))
+    d = gen((3, 4, 1), dtype, 77)
+    assert_same(tb.concatenate(dev(a), dev(d), -1), oracle.concat(a, d, 2))
+    m, n = gen((40, 64), dtype, 78), gen((24, 64), dtype, 79)
+    assert_same(tb.concatenate(dev(m).t(), dev(n).t(), 1), oracle.concat(m.t(), n.t(), 1))
+    big_a, big_b = gen((300, 1000), dtype, 80), gen((300, 24), dtype, 81)
+    assert_same(tb.concatenate(dev(big_a), dev(big_b), 1), torch.cat([big_a, big_b], 1))
+    with pytest.raises(ValueError):
+        tb.concatenate(dev(a), dev(b).to(torch.int16), 0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.int32, torch.int64, torch.float64, torch.int8])
+@pytest.mark.parametrize("k", [-3, -1, 0, 1, 4])
+def test_triangular_masks(dtype, k):
+    m = gen((33, 47), dtype, 82)
+    assert_same(tb.triu(dev(m), k), oracle.triangular(m, True, k))
+    assert_same(tb.tril(dev(m), k), oracle.triangular(m, False, k))
+    assert_same(tb.triu(dev(m).t(), k), oracle.triangular(m.t(), True, k))
+    assert_same(tb.tril(dev(m), k), torch.tril(m, k))
+    with pytest.raises(A.TannicError):
+        tb.triu(dev(gen((2, 3, 4), dtype, 83)), k)
+
+
+@pytest.mark.parametrize("pair", [(torch.float32, torch.float32), (torch.float64, torch.float64), (torch.float32, torch.float64)])
+def test_complex_constructors(pair):
+    rho, theta = gen((6, 1, 33), pair[0], 84, 0, 2), gen((1, 7, 33), pair[1], 85, -3, 3)
+    got = tb.cartesian(dev(rho), dev(theta)).cpu()
+    assert torch.equal(torch.view_as_real(got), torch.view_as_real(oracle.complex_pair(rho, theta, False)))
+    got = tb.polar(dev(rho), dev(theta)).cpu()
+    want = oracle.complex_pair(rho, theta, True)
+    tol = 1e-12 if torch.float64 in pair else 1e-5
+    assert torch.allclose(torch.view_as_real(got), torch.view_as_real(want), rtol=tol, atol=tol)
+    # tests/cuda/test-cuda-complex.cpp: integer radii are accepted by polar
+    r = oracle.fill((4, 5), torch.int32, 86, "uniform", -5, 5)
+    t = gen((4, 5), torch.float32, 87, -3, 3)
+    assert torch.allclose(torch.view_as_real(tb.polar(dev(r), dev(t)).cpu()), torch.view_as_real(torch.polar(r.float(), t)), rtol=1e-5, atol=1e-5)
+    # complex arithmetic on the results (same-type complex add / mul)
+    z = tb.polar(dev(rho), dev(theta))
+    assert torch.allclose(torch.view_as_real(tb.mul(z, z).cpu()), torch.view_as_real(want * want), rtol=1e-4 if torch.float64 not in pair else 1e-10, atol=1e-5)
+
+
 # ---------------------------------------------------------------- conv2d ---------------
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.float64, torch.int32])

@@ -5,6 +5,7 @@ import pytest
 import torch
 
 import oracle
+from tannic_b200 import _abi as A
 
 INTS = [torch.int8, torch.int16, torch.int32, torch.int64]
 FLOATS = [torch.float16, torch.bfloat16, torch.float32, torch.float64]
@@ -196,3 +197,79 @@ def test_sum_wide_is_the_references_float_path(ref_lib):
     x = gen((7, 197), torch.bfloat16, 26, -2, 2)
     want = oracle.reduce("sum", x.float(), -1, impl="ref").to(torch.bfloat16)
     assert same_bits(oracle.reduce("sum", x, -1, acc=oracle.ACC_WIDE), want)
+
+
+# ---- data movement around the path -------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.float64, torch.int32, torch.int8, torch.int64])
+@pytest.mark.parametrize("axis", [0, 1, 2])
+def test_repeat_literal(ref_lib, dtype, axis):
+    x = gen((3, 4, 5), dtype, 40)
+    assert same_bits(oracle.repeat(x, 3, axis), oracle.repeat(x, 3, axis, impl="ref"))
+    assert same_bits(oracle.repeat(x, 3, axis), torch.repeat_interleave(x, 3, axis))
+    xt = x.transpose(0, 2)
+    assert same_bits(oracle.repeat(xt, 2, axis), oracle.repeat(xt, 2, axis, impl="ref"))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int32, torch.float64])
+def test_concat_literal_where_the_reference_is_right(ref_lib, dtype):
+    """The reference walks the inner block with the stride of dimension axis + 1 only: exact for the
+    last two axes, also on strided operands of rank 2."""
+    a, b = gen((3, 4, 5), dtype, 41), gen((3, 2, 5), dtype, 42)
+    assert same_bits(oracle.concat(a, b, 1), oracle.concat(a, b, 1, impl="ref"))
+    c = gen((3, 4, 7), dtype, 43)
+    assert same_bits(oracle.concat(a, c, 2), oracle.concat(a, c, 2, impl="ref"))
+    m, n = gen((6, 4), dtype, 44), gen((5, 4), dtype, 45)
+    assert same_bits(oracle.concat(m, n, 0), oracle.concat(m, n, 0, impl="ref"))
+    assert same_bits(oracle.concat(m.t(), n.t(), 1), oracle.concat(m.t(), n.t(), 1, impl="ref"))
+    assert same_bits(oracle.concat(a, b, 1), torch.cat([a, b], 1))
+
+
+def test_concat_reference_defect_for_leading_axes(ref_lib):
+    """Rank 3, axis 0: the reference multiplies the flat inner index by strides[1] and reads the wrong
+    elements; the restatement (and the device path) concatenate."""
+    a, b = gen((3, 4, 5), torch.float32, 46), gen((2, 4, 5), torch.float32, 47)
+    assert torch.equal(oracle.concat(a, b, 0), torch.cat([a, b], 0))
+    assert not torch.equal(oracle.concat(a, b, 0, impl="ref"), torch.cat([a, b], 0))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.float64, torch.int32, torch.int64])
+@pytest.mark.parametrize("k", [0, 1, 3])
+def test_triangular_literal(ref_lib, dtype, k):
+    m = gen((5, 7), dtype, 48)
+    if dtype not in (torch.float16, torch.bfloat16):  # that translation unit of the reference is built without its half types
+        for upper in (True, False):
+            assert same_bits(oracle.triangular(m, upper, k), oracle.triangular(m, upper, k, impl="ref"))
+            assert same_bits(oracle.triangular(m.t(), upper, k), oracle.triangular(m.t(), upper, k, impl="ref"))
+    assert same_bits(oracle.triangular(m, True, k), torch.triu(m, k))
+    assert same_bits(oracle.triangular(m, False, k), torch.tril(m, k))
+
+
+def test_triangular_reference_defect_for_negative_diagonals(ref_lib):
+    m = gen((5, 7), torch.float32, 49)
+    assert torch.equal(oracle.triangular(m, True, -2), torch.triu(m, -2))
+    assert torch.equal(oracle.triangular(m, False, -2), torch.tril(m, -2))
+    assert not torch.equal(oracle.triangular(m, True, -2, impl="ref"), torch.triu(m, -2))
+
+
+@pytest.mark.parametrize("pair", [(torch.float32, torch.float32), (torch.float64, torch.float64), (torch.float32, torch.float64),
+                                  (torch.int32, torch.float32), (torch.int64, torch.int64)])
+def test_outer_literal_where_the_table_type_is_the_promoted_one(ref_lib, pair):
+    a, b = gen((6,), pair[0], 50), gen((9,), pair[1], 51)
+    assert same_bits(oracle.outer(a, b), oracle.outer(a, b, impl="ref"))
+
+
+def test_outer_reference_writes_wider_than_promoted(ref_lib):
+    """(float16, float16) is a float32 kernel in the reference's table (src/cpu/outer.cpp:91) although the
+    front-end allocates float16: read as float32 it equals the product rounded once."""
+    a, b = gen((6,), torch.float16, 52, -2, 2), gen((9,), torch.float16, 53, -2, 2)
+    wide = oracle.outer(a, b, out_dtype=A.FLOAT32, impl="ref")
+    assert same_bits(oracle.outer(a, b), wide.to(torch.float16))
+
+
+@pytest.mark.parametrize("pair", [(torch.float32, torch.float32), (torch.float64, torch.float64), (torch.float32, torch.float64)])
+def test_complex_constructors(ref_lib, pair):
+    rho, theta = gen((3, 1, 4), pair[0], 54, 0, 2), gen((1, 5, 4), pair[1], 55, -3, 3)
+    assert same_bits(torch.view_as_real(oracle.complex_pair(rho, theta, False)), torch.view_as_real(oracle.complex_pair(rho, theta, False, impl="ref")))
+    got, want = oracle.complex_pair(rho, theta, True), oracle.complex_pair(rho, theta, True, impl="ref")
+    assert torch.allclose(torch.view_as_real(got), torch.view_as_real(want), rtol=1e-6, atol=1e-7)
