@@ -805,11 +805,57 @@ __device__ __forceinline__ void eval_static_packed(typename Pack2<T>::type (&val
     }
 }
 
+// One node on one 16-byte vector, opcode known at compile time. 16-bit types go through the packed
+// path (same code as the compiled programs, so results are bit-identical to them); wider types
+// compute per element and round on store.
+template <typename T, int OP>
+__device__ __forceinline__ Vec<T> node_on_vector(const Vec<T>& a, const Vec<T>& b, float immf) {
+    Vec<T> r;
+    if constexpr (sizeof(T) == 2) {
+        using P2 = typename Pack2<T>::type;
+#pragma unroll
+        for (int i = 0; i < Vec<T>::N / 2; ++i)
+            reinterpret_cast<P2*>(r.e)[i] = apply_packed<T, OP>(reinterpret_cast<const P2*>(a.e)[i], reinterpret_cast<const P2*>(b.e)[i], immf);
+    } else {
+        using C = typename compute_of<T>::type;
+        const Imm imm{(double)immf, 0};
+#pragma unroll
+        for (int i = 0; i < Vec<T>::N; ++i)
+            r.e[i] = from_compute<T, C>(round_to_storage<T, C>(apply_op<OP, false, C>(to_compute<C>(a.e[i]), to_compute<C>(b.e[i]), imm)));
+    }
+    return r;
+}
+
+// The interpreter's dispatch: one switch per node and vector, not per element.
+template <typename T>
+__device__ __forceinline__ Vec<T> node_dispatch(int op, const Vec<T>& a, const Vec<T>& b, float immf) {
+    switch (op) {
+        case TN_OP_ADD: return node_on_vector<T, TN_OP_ADD>(a, b, immf);
+        case TN_OP_SUB: return node_on_vector<T, TN_OP_SUB>(a, b, immf);
+        case TN_OP_MUL: return node_on_vector<T, TN_OP_MUL>(a, b, immf);
+        case TN_OP_POW: return node_on_vector<T, TN_OP_POW>(a, b, immf);
+        case TN_OP_NEG: return node_on_vector<T, TN_OP_NEG>(a, b, immf);
+        case TN_OP_LOG: return node_on_vector<T, TN_OP_LOG>(a, b, immf);
+        case TN_OP_EXP: return node_on_vector<T, TN_OP_EXP>(a, b, immf);
+        case TN_OP_SQRT: return node_on_vector<T, TN_OP_SQRT>(a, b, immf);
+        case TN_OP_RSQRT: return node_on_vector<T, TN_OP_RSQRT>(a, b, immf);
+        case TN_OP_ABS: return node_on_vector<T, TN_OP_ABS>(a, b, immf);
+        case TN_OP_SIN: return node_on_vector<T, TN_OP_SIN>(a, b, immf);
+        case TN_OP_COS: return node_on_vector<T, TN_OP_COS>(a, b, immf);
+        case TN_OP_TAN: return node_on_vector<T, TN_OP_TAN>(a, b, immf);
+        case TN_OP_SINH: return node_on_vector<T, TN_OP_SINH>(a, b, immf);
+        case TN_OP_COSH: return node_on_vector<T, TN_OP_COSH>(a, b, immf);
+        case TN_OP_TANH: return node_on_vector<T, TN_OP_TANH>(a, b, immf);
+        case TN_OP_SCALE: return node_on_vector<T, TN_OP_SCALE>(a, b, immf);
+        default: return a;
+    }
+}
+
 // Evaluates the program on one 16-byte vector of every input.
 template <typename T, typename P>
 __device__ __forceinline__ Vec<T> eval_vector(const Vec<T> (&vin)[kMaxIn], const ProgArgs& g) {
     using C = typename compute_of<T>::type;
-    constexpr bool FAST = sizeof(T) == 2;
+    [[maybe_unused]] constexpr bool FAST = sizeof(T) == 2;
     constexpr int V = Vec<T>::N;
     constexpr bool STATIC = P::N > 0;
     Vec<T> out;
@@ -835,19 +881,24 @@ __device__ __forceinline__ Vec<T> eval_vector(const Vec<T> (&vin)[kMaxIn], const
 #pragma unroll
         for (int i = 0; i < V; ++i) out.e[i] = from_compute<T, C>(val[kMaxIn + P::N - 1][i]);
     } else {
-        C val[kMaxIn + kMaxNodes][V];
+        // The interpreter keeps every value (inputs, then one per node, rounded to the storage type
+        // like the node-by-node chain) in shared memory: 16 bytes per thread and value, value k of
+        // thread t at word k * blockDim.x + t. Nothing is shared between threads, so no barrier
+        // is needed; shared memory only stands in for a register file that can be indexed at run time.
+        extern __shared__ uint4 program_values[];
+        uint4* mine = program_values + threadIdx.x;
 #pragma unroll
         for (int k = 0; k < kMaxIn; ++k)
-#pragma unroll
-            for (int i = 0; i < V; ++i) val[k][i] = k < g.n_inputs ? to_compute<C>(vin[k].e[i]) : C(0);
+            if (k < g.n_inputs) mine[k * kThreads] = *reinterpret_cast<const uint4*>(&vin[k]);
         for (int n = 0; n < g.n_nodes; ++n) {
             const tn_eltwise_node_t nd = g.nodes[n];
-#pragma unroll
-            for (int i = 0; i < V; ++i)
-                val[kMaxIn + n][i] = round_to_storage<T, C>(apply_dynamic<C, FAST>(nd.opcode, val[nd.lhs][i], val[nd.rhs][i], nd.imm));
+            Vec<T> a, b;
+            *reinterpret_cast<uint4*>(&a) = mine[nd.lhs * kThreads];
+            *reinterpret_cast<uint4*>(&b) = mine[nd.rhs * kThreads];
+            const Vec<T> r = node_dispatch<T>(nd.opcode, a, b, nd.imm);
+            mine[(kMaxIn + n) * kThreads] = *reinterpret_cast<const uint4*>(&r);
         }
-#pragma unroll
-        for (int i = 0; i < V; ++i) out.e[i] = from_compute<T, C>(val[kMaxIn + g.n_nodes - 1][i]);
+        *reinterpret_cast<uint4*>(&out) = mine[(kMaxIn + g.n_nodes - 1) * kThreads];
     }
     return out;
 }
@@ -960,7 +1011,7 @@ tn_status launch_program(const Plan& plan, const tn_tensor_t* const* inputs, int
         for (int k = 0; k < n_inputs; ++k) any_scalar = any_scalar || g.inner[k] == 0;
         const int unroll = env_int("TN_PROGRAM_UNROLL", 2);
         // one resident wave: CTAs per SM from the occupancy calculator (cached per instantiation)
-        auto launch = [&](auto kernel, int u) {
+        auto launch = [&](auto kernel, int u, size_t smem = 0) {
             static const int per_sm = resident_ctas(kernel, kThreads);
             const int64_t cvec = cols / V;
             // two resident waves' worth of CTAs measured a few percent faster than exactly one
@@ -972,7 +1023,7 @@ tn_status launch_program(const Plan& plan, const tn_tensor_t* const* inputs, int
             if (gy > groups) gy = groups;
             if (gy < 1) gy = 1;
             if (gy > 65535) gy = 65535;
-            kernel<<<dim3((unsigned)gx, (unsigned)gy), kThreads, 0, s>>>(g);
+            kernel<<<dim3((unsigned)gx, (unsigned)gy), kThreads, smem, s>>>(g);
         };
 #define TN_LAUNCH_PROGRAM(PROG)                                                         \
     do {                                                                                \
@@ -985,8 +1036,22 @@ tn_status launch_program(const Plan& plan, const tn_tensor_t* const* inputs, int
         else if (matches<ProgMulAdd>(nodes, n_nodes)) TN_LAUNCH_PROGRAM(ProgMulAdd);
         else if (matches<ProgSquaredDiff>(nodes, n_nodes)) TN_LAUNCH_PROGRAM(ProgSquaredDiff);
         else if (matches<ProgNormScale>(nodes, n_nodes)) TN_LAUNCH_PROGRAM(ProgNormScale);
-        else if (any_scalar) launch(ew_program_rows<T, ProgDynamic, 1, true>, 1);
-        else launch(ew_program_rows<T, ProgDynamic, 1, false>, 1);
+        else {
+            // the interpreter: 16 bytes of shared memory per thread and value
+            const size_t smem = (size_t)(kMaxIn + n_nodes) * kThreads * 16;
+            static thread_local int attr_device = -1;
+            int dev = 0;
+            TN_CUDA(cudaGetDevice(&dev));
+            if (attr_device != dev) {
+                const int most = (kMaxIn + kMaxNodes) * kThreads * 16;
+                TN_CUDA(cudaFuncSetAttribute(ew_program_rows<T, ProgDynamic, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
+                TN_CUDA(cudaFuncSetAttribute(ew_program_rows<T, ProgDynamic, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
+                TN_CUDA(cudaFuncSetAttribute(ew_program_rows<T, ProgDynamic, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
+                attr_device = dev;
+            }
+            if (any_scalar) launch(ew_program_rows<T, ProgDynamic, 1, true>, 1, smem);
+            else launch(ew_program_rows<T, ProgDynamic, 1, false>, 1, smem);
+        }
 #undef TN_LAUNCH_PROGRAM
         return after_launch("ew_program_rows");
     }

@@ -111,13 +111,16 @@ def scale(x: torch.Tensor, value) -> torch.Tensor:
     return out
 
 
-def program(inputs: Sequence[torch.Tensor], nodes: Sequence[tuple]) -> torch.Tensor:
+def program(inputs: Sequence[torch.Tensor], nodes: Sequence[tuple], out: torch.Tensor | None = None) -> torch.Tensor:
     """Fused elementwise program. `nodes` are (opcode, lhs, rhs[, imm]) with value ids 0..3 for the
-    inputs and 4+k for node k."""
+    inputs and 4+k for node k. `out` (optional) is a preallocated result of the broadcast shape."""
     shape = tuple(inputs[0].shape)
     for t in inputs[1:]:
         shape = broadcast_shape(shape, t.shape)
-    out = _empty(shape, TORCH_TO_TN[inputs[0].dtype], inputs[0])
+    if out is None:
+        out = _empty(shape, TORCH_TO_TN[inputs[0].dtype], inputs[0])
+    elif tuple(out.shape) != shape or out.dtype != inputs[0].dtype:
+        raise ValueError("out must have the broadcast shape and the inputs' dtype")
     descs = [desc(t) for t in inputs]
     ptrs = (C.POINTER(A.TensorT) * len(descs))(*[C.pointer(d) for d in descs])
     arr = (A.EltwiseNode * len(nodes))()
@@ -127,6 +130,70 @@ def program(inputs: Sequence[torch.Tensor], nodes: Sequence[tuple]) -> torch.Ten
     dd = desc(out)
     A.check(A.lib().tn_eltwise_program(ptrs, len(descs), arr, len(nodes), C.byref(dd), current_stream(out)))
     return out
+
+
+class HostPipeline:
+    """Host buffers in, host buffer out, for a fused elementwise program: the rows are cut into chunks and
+    the host-to-device copy of chunk c + 1, the kernel of chunk c and the device-to-host copy of chunk
+    c - 1 run at the same time on three streams (PCIe is full duplex), so a call costs about one
+    direction's transfer time instead of both plus the kernel. Inputs whose leading extent equals the
+    result's are chunked; smaller (broadcast) inputs are copied whole first. Host tensors should be
+    pinned, otherwise the copies are synchronous. Device staging memory is kept between calls.
+
+    The reference moves data with one synchronous cudaMemcpy per call (src/cuda/mem.cu:54-90) and has no
+    pinned host allocator (src/resources.cpp:24-38 throws)."""
+
+    def __init__(self, device: int | torch.device | None = None, chunks: int = 8):
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.chunks = chunks
+        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
+        self._staging: dict = {}
+
+    def _dev(self, key, shape, dtype):
+        buf = self._staging.get(key)
+        if buf is None or tuple(buf.shape) != tuple(shape) or buf.dtype != dtype:
+            buf = torch.empty(tuple(shape), dtype=dtype, device=self.device)
+            self._staging[key] = buf
+        return buf
+
+    def program(self, inputs: Sequence[torch.Tensor], nodes: Sequence[tuple], out_host: torch.Tensor) -> torch.Tensor:
+        shape = tuple(inputs[0].shape)
+        for t in inputs[1:]:
+            shape = broadcast_shape(shape, t.shape)
+        if tuple(out_host.shape) != shape:
+            raise ValueError("out_host must have the broadcast shape")
+        rows = shape[0] if len(shape) > 1 else 1
+        chunked = [len(shape) > 1 and t.dim() == len(shape) and t.shape[0] == rows and rows > 1 for t in inputs]
+        dev_in = [self._dev(("in", k), t.shape, t.dtype) for k, t in enumerate(inputs)]
+        dev_out = self._dev(("out",), shape, out_host.dtype)
+        caller = torch.cuda.current_stream(self.device)
+        for s in (self.s_in, self.s_run, self.s_out):
+            s.wait_stream(caller)
+        with torch.cuda.stream(self.s_in):
+            for k, t in enumerate(inputs):
+                if not chunked[k]:
+                    dev_in[k].copy_(t, non_blocking=True)
+        n = _b.max(1, _b.min(self.chunks, rows)) if any(chunked) else 1
+        bounds = [(rows * c) // n for c in range(n + 1)]
+        for c in range(n):
+            lo, hi = bounds[c], bounds[c + 1]
+            if hi == lo:
+                continue
+            with torch.cuda.stream(self.s_in):
+                for k, t in enumerate(inputs):
+                    if chunked[k]:
+                        dev_in[k][lo:hi].copy_(t[lo:hi], non_blocking=True)
+                arrived = self.s_in.record_event()
+            with torch.cuda.stream(self.s_run):
+                self.s_run.wait_event(arrived)
+                views = [dev_in[k][lo:hi] if chunked[k] else dev_in[k] for k in range(len(inputs))]
+                program(views, nodes, out=dev_out[lo:hi] if any(chunked) else dev_out)
+                done = self.s_run.record_event()
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(done)
+                (out_host[lo:hi] if any(chunked) else out_host).copy_(dev_out[lo:hi] if any(chunked) else dev_out, non_blocking=True)
+        caller.wait_stream(self.s_out)
+        return out_host
 
 
 def _matmul_dtype(a: int, b: int) -> int:

@@ -173,6 +173,22 @@ def test_fused_program_matches_node_chain(dtype, shapes):
     assert_close(chain, _program_oracle(x, y))
 
 
+@pytest.mark.parametrize("shapes", [((1000, 256), (1, 256)), ((37, 64), (37, 64)), ((5, 8), (5, 1)), ((64,), (64,))])
+def test_host_pipeline_matches_device_call(shapes):
+    """Pinned host buffers in and out through the chunked three-stream path == the device call on resident
+    tensors, bit for bit; two calls in a row reuse the staging memory."""
+    x, y = gen(shapes[0], torch.float16, 19, 0.1, 4.0).pin_memory(), gen(shapes[1], torch.float16, 20, -2.0, 2.0).pin_memory()
+    want = tb.program([dev(x), dev(y)], CFG2_NODES).cpu()
+    pipe = tb.HostPipeline(chunks=8)
+    out = torch.empty(want.shape, dtype=torch.float16).pin_memory()
+    for _ in range(2):
+        out.zero_()
+        pipe.program([x, y], CFG2_NODES, out)
+        torch.cuda.current_stream().synchronize()
+        assert_same(out, want)
+    assert_close(out, _program_oracle(x, y))
+
+
 def test_fused_program_dynamic_and_other_static_shapes():
     x, w, b = gen((64, 128), torch.float32, 19), gen((64, 128), torch.float32, 20), gen((128,), torch.float32, 21)
     want = oracle.binary("add", oracle.binary("mul", x, w), b)
