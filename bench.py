@@ -5,15 +5,15 @@
     python bench.py --impl reference --gpus N --steps K ...   # the reference's CPU kernels
 
 A "step" is one pass of the hot path over one batch of synthetic input. The headline workload
-is BASELINE config 2: Z = log(X) + Y*Y - exp(X) on float16 X[8192,8192] (uniform[0.1,4]) and
+is benchmark configuration 2: Z = log(X) + Y*Y - exp(X) on float16 X[8192,8192] (uniform[0.1,4]) and
 Y[1,8192] (uniform[-2,2], row-broadcast), seed 1, evaluated by ONE fused kernel that streams HBM
 once. With N GPUs every rank owns its own [8192,8192] row shard of a [8192*N, 8192] problem (weak
 scaling, no collective on the data path; Y is replicated). The metric is algorithmic HBM bytes
 (read X + read Y + write Z) per second, summed over ranks, timed with CUDA events and taken as the
 max over ranks.
 
-The same JSON line carries, under "workloads", device-timed figures for the other BASELINE
-configs (int32 broadcast add, the Llama-3-8B MLP GEMM, the ResNet-50 convolutions, the ViT score
+The same JSON line carries, under "workloads", device-timed figures for the other benchmark
+configurations (int32 broadcast add, the Llama-3-8B MLP GEMM, the ResNet-50 convolutions, the ViT score
 path) on rank 0's GPU.
 """
 from __future__ import annotations
@@ -177,7 +177,7 @@ def time_device(fn, steps, warmup, torch):
 
 
 def secondary_workloads(torch, tb, A, hbm_peak, tf_peak, only=None, small=False):
-    """Device-timed figures for the other BASELINE configs (rank 0 only). Inputs are seeded
+    """Device-timed figures for the other benchmark configurations (rank 0 only). Inputs are seeded
     synthetic tensors of the named shapes and distributions, created on the device. `only` runs a
     single workload (used for profiling); `small` shrinks the leading dimension so that a
     profiler capture stays short (inputs still exceed L2 where the workload is HBM-bound)."""

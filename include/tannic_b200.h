@@ -138,6 +138,12 @@ tn_status tn_copy_from_host(const tn_device_t* device, const void* host, void* d
 tn_status tn_copy_to_host(const tn_device_t* device, const void* dev, void* host, size_t nbytes);
 tn_status tn_compare_from_host(const tn_device_t* device, const void* host, const void* dev,
                                size_t nbytes, int* equal);
+/* Stream-ordered variants with no reference counterpart (the reference copies synchronously): they
+ * return once the copy is queued on `stream`; the host range should come from
+ * tn_host_allocate_pinned, a pageable one makes the copy synchronous. The caller keeps both ranges
+ * alive until the stream has passed the copy. */
+tn_status tn_copy_from_host_async(const tn_device_t* device, const void* host, void* dev, size_t nbytes, tn_stream_t stream);
+tn_status tn_copy_to_host_async(const tn_device_t* device, const void* dev, void* host, size_t nbytes, tn_stream_t stream);
 /* reference: cuda::copy (Tensor::to), src/cuda/mem.cu:67-93 — direction from the two
  * environments; pinned host memory copies asynchronously on `stream`, pageable synchronously. */
 tn_status tn_copy(const tn_tensor_t* src, tn_tensor_t* dst, size_t nbytes, tn_stream_t stream);

@@ -102,6 +102,8 @@ PROTOTYPES = {
     "tn_deallocate": [C.POINTER(DeviceT), C.c_void_p],
     "tn_copy_from_host": [C.POINTER(DeviceT), C.c_void_p, C.c_void_p, C.c_size_t],
     "tn_copy_to_host": [C.POINTER(DeviceT), C.c_void_p, C.c_void_p, C.c_size_t],
+    "tn_copy_from_host_async": [C.POINTER(DeviceT), C.c_void_p, C.c_void_p, C.c_size_t, StreamT],
+    "tn_copy_to_host_async": [C.POINTER(DeviceT), C.c_void_p, C.c_void_p, C.c_size_t, StreamT],
     "tn_compare_from_host": [C.POINTER(DeviceT), C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(C.c_int)],
     "tn_copy": [_TP, _TP, C.c_size_t, StreamT],
     "tn_host_allocate_pinned": [C.c_size_t, C.POINTER(C.c_void_p)],

@@ -4,7 +4,7 @@
 // Paths:
 //   1x1, stride 1, no padding, dense fp16/bf16 tensors -> batched tensor-core GEMM
 //        y[n] = W[Cout, Cin] . x[n][Cin, H*W]   (x[n] is an N-major B operand);
-//   other stride-1 fp16/bf16 convolutions with Cin % 8 == 0 and Wout <= 256 -> implicit GEMM on
+//   other fp16/bf16 convolutions (stride 1..8) with Cin % 8 == 0 and Wout * stride <= 256 -> implicit GEMM on
 //        the tcgen05 main loop: the activation is first re-laid as NHWC and the weights as
 //        [tap][Cout][Cin] in scratch memory (TMA needs the channel axis innermost: a tap shift
 //        of one pixel along W would otherwise break its 16-byte start alignment), then every
@@ -225,13 +225,14 @@ tn_status conv_impl(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_
         if (tc_gemm_eligible(p)) return tc_gemm(p, s);
     }
 
-    if (is_half(g.dt) && g.str_h == 1 && g.str_w == 1 && dense_nchw(y) && (!bias || g.bias_stride == 1) && g.N <= 65535) {
+    if (is_half(g.dt) && g.str_h <= 8 && g.str_w <= 8 && dense_nchw(y) && (!bias || g.bias_stride == 1) && g.N <= 65535) {
         TcConv p;
         p.bias = g.bias;
         p.y = g.y;
         p.dtype = g.dt;
         p.N = g.N; p.C = g.Cin; p.H = g.H; p.W = g.W; p.Cout = g.Cout; p.Kh = g.Kh; p.Kw = g.Kw;
         p.Ho = g.Ho; p.Wo = g.Wo; p.pad_h = g.pad_h; p.pad_w = g.pad_w;
+        p.stride_h = g.str_h; p.stride_w = g.str_w;
         // placeholders so that the eligibility test sees aligned pointers; the real ones follow
         p.x_nhwc = g.y;
         p.w_packed = g.y;

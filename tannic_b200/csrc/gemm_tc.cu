@@ -197,7 +197,7 @@ struct KernelArgs {
     int has_scale;
     float scale;
     // convolution geometry
-    int cblocks, kw, pad_h, pad_w, hbox;
+    int cblocks, kw, pad_h, pad_w, hbox, str_h;
     int epi_warps;             // 4 or 8 epilogue warps take part (the others exit at once)
 };
 
@@ -500,7 +500,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         tma_load_3d(sa, &map_a, full0 + 8 * s, cb * BK, mt * BM, tap);
                         // innermost coordinate (channels) is a multiple of 64; the W and H coordinates
                         // carry the tap shift and may be negative or past the edge (zero fill)
-                        tma_load_4d(sb, &map_b, full0 + 8 * s, cb * BK, kwi - g.pad_w, nt * g.hbox + kh - g.pad_h, batch);
+                        tma_load_4d(sb, &map_b, full0 + 8 * s, cb * BK, kwi - g.pad_w, nt * g.hbox * g.str_h + kh - g.pad_h, batch);
                     } else {
                         tma_load_3d(sa, &map_a, full0 + 8 * s, kb * BK, mt * BM, g.a_batched ? batch : 0);
                         if constexpr (MODE == MODE_N) {
@@ -638,10 +638,12 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 
 // Tiled map of rank `rank`, zero fill outside the tensor.
 tn_status encode_as(CUtensorMap* map, const void* ptr, CUtensorMapDataType type, CUtensorMapSwizzle swizzle, int rank,
-                    const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box) {
+                    const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box, const cuuint32_t* traversal = nullptr) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(TN_ERROR, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    if (traversal)
+        for (int i = 0; i < rank; ++i) estr[i] = traversal[i];
     CUresult r = fn(map, type, (cuuint32_t)rank, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(TN_ERROR, "cuTensorMapEncodeTiled failed with code %d", (int)r);
@@ -650,9 +652,9 @@ tn_status encode_as(CUtensorMap* map, const void* ptr, CUtensorMapDataType type,
 
 // Operand maps: 16-bit elements, 128-byte swizzle.
 tn_status encode(CUtensorMap* map, const void* ptr, bool bf16, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
-                 const cuuint32_t* box) {
+                 const cuuint32_t* box, const cuuint32_t* traversal = nullptr) {
     return encode_as(map, ptr, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, CU_TENSOR_MAP_SWIZZLE_128B,
-                     rank, dims, strides, box);
+                     rank, dims, strides, box, traversal);
 }
 
 // Result map (columns, rows, batch) for the epilogue's stores: boxes of 32 rows x 64 bytes, 64-byte
@@ -778,7 +780,8 @@ bool tc_conv_eligible(const TcConv& p) {
     if (p.dtype != TN_FLOAT16 && p.dtype != TN_BFLOAT16) return false;
     if (p.N <= 0 || p.C <= 0 || p.Cout <= 0 || p.Ho <= 0 || p.Wo <= 0) return false;
     if (!mult8(p.C)) return false;                       // NHWC pixel pitch must be a multiple of 16 bytes
-    if (p.Wo > 256 || p.W > 65535 || p.H > 65535) return false;
+    if (p.stride_h < 1 || p.stride_h > 8 || p.stride_w < 1 || p.stride_w > 8) return false;  // traversal strides of a tensor map
+    if (p.Wo * p.stride_w > 256 || p.W > 65535 || p.H > 65535) return false;              // a box spans at most 256 elements
     if (p.Kh * p.Kw > 1024 || p.N >= (int64_t(1) << 31)) return false;
     if (ceil_div(p.Cout, BM) * p.Ho * p.N >= (int64_t(1) << 31)) return false;  // tile index is 32-bit
     return aligned16(p.x_nhwc) && aligned16(p.w_packed);
@@ -789,6 +792,7 @@ tn_status tc_conv(const TcConv& p, cudaStream_t stream) {
     const int taps = (int)(p.Kh * p.Kw);
     int hbox = (int)(256 / p.Wo);
     if (hbox > p.Ho) hbox = (int)p.Ho;
+    if (hbox > 256 / p.stride_h) hbox = (int)(256 / p.stride_h);
     if (hbox < 1) hbox = 1;
     CUtensorMap map_a, map_b;
     // weights [tap][Cout][Cin]
@@ -797,8 +801,11 @@ tn_status tc_conv(const TcConv& p, cudaStream_t stream) {
     {
         cuuint64_t dims[4] = {(cuuint64_t)p.C, (cuuint64_t)p.W, (cuuint64_t)p.H, (cuuint64_t)p.N};
         cuuint64_t strides[3] = {(cuuint64_t)p.C * 2, (cuuint64_t)p.W * p.C * 2, (cuuint64_t)p.H * p.W * p.C * 2};
-        cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)p.Wo, (cuuint32_t)hbox, 1};
-        TN_TRY(encode(&map_b, p.x_nhwc, bf16, 4, dims, strides, box));
+        // a strided convolution reads every stride-th pixel: the map walks W and H with that
+        // traversal stride, and a box that is to deliver n elements spans n * stride
+        cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)(p.Wo * p.stride_w), (cuuint32_t)(hbox * p.stride_h), 1};
+        cuuint32_t walk[4] = {1, (cuuint32_t)p.stride_w, (cuuint32_t)p.stride_h, 1};
+        TN_TRY(encode(&map_b, p.x_nhwc, bf16, 4, dims, strides, box, walk));
     }
     KernelArgs g = {};
     g.d = p.y;
@@ -825,6 +832,7 @@ tn_status tc_conv(const TcConv& p, cudaStream_t stream) {
     g.pad_h = (int)p.pad_h;
     g.pad_w = (int)p.pad_w;
     g.hbox = hbox;
+    g.str_h = (int)p.stride_h;
     CUtensorMap map_d = map_a;
     g.tma_store = can_tma_store(p.y, g.ldd, g.d_batch, g.tile_n, false);
     if (g.tma_store) TN_TRY(make_result_map(&map_d, p.y, false, bf16, g.N, p.Cout, p.N, g.ldd, g.d_batch));

@@ -35,6 +35,7 @@ struct TcConv {
     void* y = nullptr;
     int dtype = 0;
     int64_t N = 0, C = 0, H = 0, W = 0, Cout = 0, Kh = 0, Kw = 0, Ho = 0, Wo = 0, pad_h = 0, pad_w = 0;
+    int64_t stride_h = 1, stride_w = 1;  // 1..8: the traversal strides of the activation's tensor map
 };
 bool tc_conv_eligible(const TcConv& p);
 tn_status tc_conv(const TcConv& p, cudaStream_t stream);

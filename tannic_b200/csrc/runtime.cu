@@ -259,6 +259,22 @@ tn_status tn_copy_to_host(const tn_device_t* device, const void* dev, void* host
     return TN_SUCCESS;
 }
 
+tn_status tn_copy_from_host_async(const tn_device_t* device, const void* host, void* dev, size_t nbytes, tn_stream_t stream) {
+    if (!device) return fail(TN_ERROR, "null device");
+    TN_TRY(use_device(device->id));
+    const cudaError_t err = cudaMemcpyAsync(dev, host, nbytes, cudaMemcpyHostToDevice, as_cuda(stream));
+    if (err != cudaSuccess) return fail(TN_ERROR, "H2D copy failed: %s", cudaGetErrorString(err));
+    return TN_SUCCESS;
+}
+
+tn_status tn_copy_to_host_async(const tn_device_t* device, const void* dev, void* host, size_t nbytes, tn_stream_t stream) {
+    if (!device) return fail(TN_ERROR, "null device");
+    TN_TRY(use_device(device->id));
+    const cudaError_t err = cudaMemcpyAsync(host, dev, nbytes, cudaMemcpyDeviceToHost, as_cuda(stream));
+    if (err != cudaSuccess) return fail(TN_ERROR, "D2H copy failed: %s", cudaGetErrorString(err));
+    return TN_SUCCESS;
+}
+
 tn_status tn_compare_from_host(const tn_device_t* device, const void* host, const void* dev,
                                size_t nbytes, int* equal) {
     if (!device || !equal) return fail(TN_ERROR, "null argument");

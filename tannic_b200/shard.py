@@ -1,6 +1,6 @@
 """Sharding of the operator hot path over the GPUs of one box (one process per GPU).
 
-Every BASELINE workload splits on its leading dimension — rows of an elementwise op, images of
+Every benchmark workload splits on its leading dimension — rows of an elementwise op, images of
 a convolution, batch entries of a matmul — with the small operands (a row-broadcast vector,
 weights) replicated, so ranks exchange nothing on the data path. Collectives appear in exactly two
 places, both outside the kernels:

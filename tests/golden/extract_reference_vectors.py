@@ -1,7 +1,7 @@
 """Extracts the literal tensors of the reference's own CPU tests into reference_vectors.json.
 
 Run where the reference tree is present:
-    python tests/golden/extract_reference_vectors.py /root/reference
+    python tests/golden/extract_reference_vectors.py <reference checkout>
 
 Every `TEST(Suite, Name)` body of the listed files is scanned for
 `Tensor X(dtype, {shape}); X.initialize({...});` pairs; the nested initialiser lists are stored

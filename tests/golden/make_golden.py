@@ -79,6 +79,28 @@ def main():
     np.savez_compressed(path, **out)
     print(f"{len(out) // 2} arrays -> {path} ({path.stat().st_size} bytes)")
 
+    # ---- data movement around the path (a file of its own: golden_data_movement.npz) ----
+    out.clear()
+    xr = oracle.fill((3, 4, 5), torch.bfloat16, 20, "uniform", -4, 4)
+    put("repeat_bf16", x=xr, axis1_x3=oracle.repeat(xr, 3, 1, impl=R), axis0_x2=oracle.repeat(xr, 2, 0, impl=R),
+        permuted_axis1_x2=oracle.repeat(xr.transpose(0, 2), 2, 1, impl=R))
+    ca, cb, cc = (oracle.fill(shape, torch.float16, seed, "uniform", -4, 4) for shape, seed in (((3, 4, 5), 21), ((3, 2, 5), 22), ((3, 4, 7), 23)))
+    ma, mb = oracle.fill((6, 4), torch.int32, 24, "uniform", -100, 100), oracle.fill((5, 4), torch.int32, 25, "uniform", -100, 100)
+    put("concat", a=ca, b=cb, c=cc, ab_axis1=oracle.concat(ca, cb, 1, impl=R), ac_axis2=oracle.concat(ca, cc, 2, impl=R),
+        m=ma, n=mb, mn_axis0=oracle.concat(ma, mb, 0, impl=R))
+    tf, ti = oracle.fill((5, 7), torch.float32, 26, "uniform", -4, 4), oracle.fill((6, 6), torch.int64, 27, "uniform", -100, 100)
+    put("triangular", f=tf, i=ti, f_triu0=oracle.triangular(tf, True, 0, impl=R), f_tril1=oracle.triangular(tf, False, 1, impl=R),
+        i_triu2=oracle.triangular(ti, True, 2, impl=R), i_tril0=oracle.triangular(ti, False, 0, impl=R))
+    oa, ob = oracle.fill((6,), torch.float32, 28, "uniform", -2, 2), oracle.fill((9,), torch.float32, 29, "uniform", -2, 2)
+    ia, ib = oracle.fill((5,), torch.int64, 30, "uniform", -100, 100), oracle.fill((4,), torch.int64, 31, "uniform", -100, 100)
+    put("outer", a=oa, b=ob, ab=oracle.outer(oa, ob, impl=R), ia=ia, ib=ib, iab=oracle.outer(ia, ib, impl=R))
+    rho, theta = oracle.fill((3, 1, 4), torch.float32, 32, "uniform", 0, 2), oracle.fill((1, 5, 4), torch.float32, 33, "uniform", -3, 3)
+    put("complex", rho=rho, theta=theta, cartesian=torch.view_as_real(oracle.complex_pair(rho, theta, False, impl=R)),
+        polar=torch.view_as_real(oracle.complex_pair(rho, theta, True, impl=R)))
+    path = Path(__file__).resolve().parent / "golden_data_movement.npz"
+    np.savez_compressed(path, **out)
+    print(f"{len(out) // 2} arrays -> {path} ({path.stat().st_size} bytes)")
+
 
 if __name__ == "__main__":
     main()

@@ -96,3 +96,74 @@ def test_cuda_matches_golden():
     mx, sm, am = tb.reduce_stats(s, -1)
     assert same(am.cpu(), get("reduce_bf16", "argmax")) and close(sm.cpu(), get("reduce_bf16", "sum_wide"))
     assert tb.device_errors() == 0
+
+
+# ---- data movement around the path: golden_data_movement.npz (same generator script) ----
+
+MOVE = np.load(Path(__file__).parent / "golden" / "golden_data_movement.npz")
+
+
+def mv(case, name):
+    arr = MOVE[f"{case}/{name}"]
+    dt = DT[str(MOVE[f"{case}/{name}.dtype"])]
+    t = torch.from_numpy(arr.view(np.int16) if arr.dtype == np.uint16 else arr.copy())
+    return t.view(dt) if dt in (torch.float16, torch.bfloat16) else t
+
+
+class _Port:
+    def up(self, t): return t
+    def down(self, t): return t
+    repeat = staticmethod(lambda x, r, ax: oracle.repeat(x, r, ax))
+    concat = staticmethod(lambda a, b, ax: oracle.concat(a, b, ax))
+    triu = staticmethod(lambda x, k: oracle.triangular(x, True, k))
+    tril = staticmethod(lambda x, k: oracle.triangular(x, False, k))
+    outer = staticmethod(lambda a, b: oracle.outer(a, b))
+    cartesian = staticmethod(lambda a, b: torch.view_as_real(oracle.complex_pair(a, b, False)))
+    polar = staticmethod(lambda a, b: torch.view_as_real(oracle.complex_pair(a, b, True)))
+
+
+class _Cuda:
+    def __init__(self):
+        from tannic_b200 import ops
+        self.tb = ops
+
+    def up(self, t): return t.cuda()
+    def down(self, t): return t.cpu()
+    def repeat(self, x, r, ax): return self.tb.repeat(x, r, ax)
+    def concat(self, a, b, ax): return self.tb.concatenate(a, b, ax)
+    def triu(self, x, k): return self.tb.triu(x, k)
+    def tril(self, x, k): return self.tb.tril(x, k)
+    def outer(self, a, b): return self.tb.outer(a, b)
+    def cartesian(self, a, b): return torch.view_as_real(self.tb.cartesian(a, b))
+    def polar(self, a, b): return torch.view_as_real(self.tb.polar(a, b))
+
+
+def check_data_movement(be):
+    u, dn = be.up, be.down
+    x = u(mv("repeat_bf16", "x"))
+    assert same(dn(be.repeat(x, 3, 1)), mv("repeat_bf16", "axis1_x3"))
+    assert same(dn(be.repeat(x, 2, 0)), mv("repeat_bf16", "axis0_x2"))
+    assert same(dn(be.repeat(x.transpose(0, 2), 2, 1)), mv("repeat_bf16", "permuted_axis1_x2"))
+    a, b, c = (u(mv("concat", n)) for n in "abc")
+    assert same(dn(be.concat(a, b, 1)), mv("concat", "ab_axis1"))
+    assert same(dn(be.concat(a, c, 2)), mv("concat", "ac_axis2"))
+    assert same(dn(be.concat(u(mv("concat", "m")), u(mv("concat", "n")), 0)), mv("concat", "mn_axis0"))
+    f, i = u(mv("triangular", "f")), u(mv("triangular", "i"))
+    assert same(dn(be.triu(f, 0)), mv("triangular", "f_triu0"))
+    assert same(dn(be.tril(f, 1)), mv("triangular", "f_tril1"))
+    assert same(dn(be.triu(i, 2)), mv("triangular", "i_triu2"))
+    assert same(dn(be.tril(i, 0)), mv("triangular", "i_tril0"))
+    assert same(dn(be.outer(u(mv("outer", "a")), u(mv("outer", "b")))), mv("outer", "ab"))
+    assert same(dn(be.outer(u(mv("outer", "ia")), u(mv("outer", "ib")))), mv("outer", "iab"))
+    rho, theta = u(mv("complex", "rho")), u(mv("complex", "theta"))
+    assert same(dn(be.cartesian(rho, theta)), mv("complex", "cartesian"))
+    assert close(dn(be.polar(rho, theta)), mv("complex", "polar"), rtol=1e-5, atol=1e-6)
+
+
+def test_port_matches_golden_data_movement():
+    check_data_movement(_Port())
+
+
+@pytest.mark.gpu
+def test_cuda_matches_golden_data_movement():
+    check_data_movement(_Cuda())

@@ -348,7 +348,7 @@ def test_matmul_simt_pairs(pair):
 
 
 def test_matmul_config1_float32():
-    """BASELINE config 1: float32 [512,1024] x [1024,512], uniform[-1,1], seed 0."""
+    """benchmark configuration 1: float32 [512,1024] x [1024,512], uniform[-1,1], seed 0."""
     a, b = oracle.fill((512, 1024), torch.float32, 0, "uniform", -1, 1), oracle.fill((1024, 512), torch.float32, 1000, "uniform", -1, 1)
     want = a.double() @ b.double()
     got = tb.matmul(dev(a), dev(b)).cpu()
@@ -454,6 +454,9 @@ def test_repeat(dtype, axis):
     assert_same(tb.repeat(dev(x), 1, axis), x)
     big = gen((64, 129, 33), dtype, 73)
     assert_same(tb.repeat(dev(big), 4, 1), torch.repeat_interleave(big, 4, 1))
+    wide = gen((16, 24, 64), dtype, 74)  # inner runs that move as 16-byte words
+    assert_same(tb.repeat(dev(wide), 3, 1), torch.repeat_interleave(wide, 3, 1))
+    assert_same(tb.repeat(dev(wide), 2, 0), torch.repeat_interleave(wide, 2, 0))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.int32, torch.float64])
@@ -550,6 +553,30 @@ def test_conv2d_implicit_gemm_tensor_core(dtype, shape):
     assert tb.device_errors() == 0
 
 
+@pytest.mark.parametrize("dtype", HALVES)
+@pytest.mark.parametrize("shape", [
+    # (N, Cin, H, W, Cout, Kh, Kw, stride, pad)
+    (2, 64, 56, 56, 128, 3, 3, 2, 1),        # ResNet stage entry: 3x3 stride 2
+    (2, 256, 28, 28, 136, 1, 1, 2, 0),       # ResNet downsample: 1x1 stride 2
+    (1, 16, 33, 47, 24, 3, 3, (2, 3), 1),    # different strides per axis, odd extents
+    (2, 8, 30, 30, 16, 7, 7, 2, 3),          # 49 taps, stride 2, padding 3
+    (1, 32, 40, 40, 8, 3, 3, 4, 0),          # stride 4
+])
+def test_conv2d_strided_on_tensor_cores(dtype, shape):
+    """Stride > 1 through the implicit GEMM: the activation's tensor map walks W and H with the
+    convolution's stride, every other part of the kernel is the stride-1 one."""
+    n, cin, h, w, cout, kh, kw, stride, pad = shape
+    x = gen((n, cin, h, w), dtype, 52, -1, 1)
+    wt = gen((cout, cin, kh, kw), dtype, 53, -0.2, 0.2)
+    bias = gen((cout,), dtype, 54, -1, 1)
+    launches = tb.launch_count()
+    got = tb.convolve2D(dev(x), dev(wt), stride, pad)
+    assert tb.launch_count() - launches == 3, "expected staging + weight packing + tensor-core GEMM"
+    assert_close(got, oracle.conv2d(x, wt, stride, pad, acc=oracle.ACC_WIDE))
+    assert_close(tb.convolve2D(dev(x), dev(wt), stride, pad, bias=dev(bias)), oracle.conv2d(x, wt, stride, pad, bias=bias, acc=oracle.ACC_WIDE))
+    assert tb.device_errors() == 0
+
+
 def test_conv2d_implicit_gemm_strided_input_view():
     x = gen((2, 12, 10, 64), torch.float16, 50, -1, 1)            # [N, H, W, C] storage
     xv = x.permute(0, 3, 1, 2)                                     # NCHW view with channel stride 1
@@ -613,6 +640,22 @@ def test_allocator_streams_and_copies():
     A.check(lib.tn_stream_put(C.byref(d), s1))
     A.check(lib.tn_stream_pop(C.byref(d), C.byref(s2)))
     assert s1.address == s2.address and s1.address != 0  # LIFO: the same stream comes back
+    # stream-ordered copies through pinned host memory
+    hp, hq, dp = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    nbytes = host.numel() * 4
+    A.check(lib.tn_host_allocate_pinned(nbytes, C.byref(hp)))
+    A.check(lib.tn_host_allocate_pinned(nbytes, C.byref(hq)))
+    A.check(lib.tn_allocate(C.byref(d), nbytes, C.byref(dp)))
+    C.memmove(hp, host.data_ptr(), nbytes)
+    A.check(lib.tn_copy_from_host_async(C.byref(d), hp, dp, nbytes, s2))
+    A.check(lib.tn_copy_to_host_async(C.byref(d), dp, hq, nbytes, s2))
+    A.check(lib.tn_stream_synchronize(s2))
+    got = torch.zeros_like(host)
+    C.memmove(got.data_ptr(), hq, nbytes)
+    assert torch.equal(got, host)
+    A.check(lib.tn_deallocate(C.byref(d), dp))
+    A.check(lib.tn_host_free_pinned(hp))
+    A.check(lib.tn_host_free_pinned(hq))
     A.check(lib.tn_stream_put(C.byref(d), s2))
     bad = A.DeviceT(99)
     p = C.c_void_p()
