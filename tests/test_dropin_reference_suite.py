@@ -25,3 +25,17 @@ def test_reference_cuda_suite_passes_on_this_backend(suite):
     tail = "\n".join((res.stdout + res.stderr).splitlines()[-25:])
     assert res.returncode == 0, f"{res.returncode} failing case(s):\n{tail}"
     assert "[ RUN      ]" in res.stdout
+
+
+@pytest.mark.gpu
+def test_reference_expression_templates_evaluate_as_one_kernel():
+    """tannic_b200/dropin/fused.hpp walks the reference's Binary / Unary / Function templates and emits one
+    `tn_eltwise_program` call; its own test compares that with the expression's node-by-node forward() and
+    counts the launches."""
+    exe = BUILD / "test-fused-expression"
+    if not exe.exists():
+        pytest.skip(f"{exe.name} not built (needs the reference tree at build time)")
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=600)
+    tail = "\n".join((res.stdout + res.stderr).splitlines()[-25:])
+    assert res.returncode == 0, f"{res.returncode} failing case(s):\n{tail}"
+    assert "[ RUN      ]" in res.stdout
