@@ -344,7 +344,7 @@ def ours(args):
 
     # the public host-to-host call: rows in chunks, copy-in / kernel / copy-out overlapped on three
     # streams; every step copies all of X and Y in and all of Z out
-    pipe = tb.HostPipeline(device=local, chunks=8)
+    pipe = tb.HostPipeline(device=local, chunks=int(os.environ.get("TN_E2E_CHUNKS", "8")))
 
     def e2e_step():
         pipe.program([x_host, y_host], nodes, z_host)

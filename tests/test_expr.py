@@ -60,7 +60,8 @@ def test_fused_and_node_by_node_agree_with_the_oracle(dtype):
     other = E.tanh(X * 0.5) * Y + E.sqrt(X)
     w = oracle.binary("add", oracle.binary("mul", oracle.unary("tanh", oracle.scale(x, 0.5)), y), oracle.unary("sqrt", x))
     assert torch.allclose(other.forward().cpu().double(), w.double(), rtol=tol, atol=tol)
-    z32 = oracle.fill((96, 200), torch.float32, 3, "uniform", -1, 1)
-    mixed = X + E.lazy(z32.cuda())
+    wider = torch.float64 if dtype == torch.float32 else torch.float32
+    z = oracle.fill((96, 200), wider, 3, "uniform", -1, 1)
+    mixed = X + E.lazy(z.cuda())
     assert mixed.compile() is None
-    assert torch.allclose(mixed.forward().cpu().double(), oracle.binary("add", x, z32).double(), rtol=tol, atol=tol)
+    assert torch.allclose(mixed.forward().cpu().double(), oracle.binary("add", x, z).double(), rtol=tol, atol=tol)
