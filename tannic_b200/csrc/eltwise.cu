@@ -826,29 +826,67 @@ __device__ __forceinline__ Vec<T> node_on_vector(const Vec<T>& a, const Vec<T>& 
     return r;
 }
 
-// The interpreter's dispatch: one switch per node and vector, not per element.
-template <typename T>
-__device__ __forceinline__ Vec<T> node_dispatch(int op, const Vec<T>& a, const Vec<T>& b, float immf) {
+// The interpreter's dispatch: one switch per node for all U vectors a thread holds, not per element.
+template <typename T, int U>
+__device__ __forceinline__ void node_dispatch(int op, const Vec<T> (&a)[U], const Vec<T> (&b)[U], float immf, Vec<T> (&r)[U]) {
+#define TN_NODE_CASE(OP)                                                        \
+    case OP:                                                                    \
+        _Pragma("unroll") for (int u = 0; u < U; ++u) r[u] = node_on_vector<T, OP>(a[u], b[u], immf); \
+        break;
     switch (op) {
-        case TN_OP_ADD: return node_on_vector<T, TN_OP_ADD>(a, b, immf);
-        case TN_OP_SUB: return node_on_vector<T, TN_OP_SUB>(a, b, immf);
-        case TN_OP_MUL: return node_on_vector<T, TN_OP_MUL>(a, b, immf);
-        case TN_OP_POW: return node_on_vector<T, TN_OP_POW>(a, b, immf);
-        case TN_OP_NEG: return node_on_vector<T, TN_OP_NEG>(a, b, immf);
-        case TN_OP_LOG: return node_on_vector<T, TN_OP_LOG>(a, b, immf);
-        case TN_OP_EXP: return node_on_vector<T, TN_OP_EXP>(a, b, immf);
-        case TN_OP_SQRT: return node_on_vector<T, TN_OP_SQRT>(a, b, immf);
-        case TN_OP_RSQRT: return node_on_vector<T, TN_OP_RSQRT>(a, b, immf);
-        case TN_OP_ABS: return node_on_vector<T, TN_OP_ABS>(a, b, immf);
-        case TN_OP_SIN: return node_on_vector<T, TN_OP_SIN>(a, b, immf);
-        case TN_OP_COS: return node_on_vector<T, TN_OP_COS>(a, b, immf);
-        case TN_OP_TAN: return node_on_vector<T, TN_OP_TAN>(a, b, immf);
-        case TN_OP_SINH: return node_on_vector<T, TN_OP_SINH>(a, b, immf);
-        case TN_OP_COSH: return node_on_vector<T, TN_OP_COSH>(a, b, immf);
-        case TN_OP_TANH: return node_on_vector<T, TN_OP_TANH>(a, b, immf);
-        case TN_OP_SCALE: return node_on_vector<T, TN_OP_SCALE>(a, b, immf);
-        default: return a;
+        TN_NODE_CASE(TN_OP_ADD)
+        TN_NODE_CASE(TN_OP_SUB)
+        TN_NODE_CASE(TN_OP_MUL)
+        TN_NODE_CASE(TN_OP_POW)
+        TN_NODE_CASE(TN_OP_NEG)
+        TN_NODE_CASE(TN_OP_LOG)
+        TN_NODE_CASE(TN_OP_EXP)
+        TN_NODE_CASE(TN_OP_SQRT)
+        TN_NODE_CASE(TN_OP_RSQRT)
+        TN_NODE_CASE(TN_OP_ABS)
+        TN_NODE_CASE(TN_OP_SIN)
+        TN_NODE_CASE(TN_OP_COS)
+        TN_NODE_CASE(TN_OP_TAN)
+        TN_NODE_CASE(TN_OP_SINH)
+        TN_NODE_CASE(TN_OP_COSH)
+        TN_NODE_CASE(TN_OP_TANH)
+        TN_NODE_CASE(TN_OP_SCALE)
+        default:
+#pragma unroll
+            for (int u = 0; u < U; ++u) r[u] = a[u];
+            break;
     }
+#undef TN_NODE_CASE
+}
+
+// The interpreter on U vectors at once. Every value (inputs, then one per node, rounded to the storage
+// type like the node-by-node chain) lives in shared memory: 16 bytes per thread, vector and value,
+// at word (value * U + u) * blockDim.x + thread. Nothing is shared between threads, so no barrier is
+// needed; shared memory only stands in for a register file that can be indexed at run time.
+template <typename T, int U>
+__device__ __forceinline__ void eval_interpreted(const Vec<T> (&vin)[U][kMaxIn], Vec<T> (&out)[U], const ProgArgs& g) {
+    extern __shared__ uint4 program_values[];
+    uint4* mine = program_values + threadIdx.x;
+#pragma unroll
+    for (int k = 0; k < kMaxIn; ++k)
+        if (k < g.n_inputs) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) mine[(k * U + u) * kThreads] = *reinterpret_cast<const uint4*>(&vin[u][k]);
+        }
+    for (int n = 0; n < g.n_nodes; ++n) {
+        const tn_eltwise_node_t nd = g.nodes[n];
+        Vec<T> a[U], b[U], r[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            *reinterpret_cast<uint4*>(&a[u]) = mine[(nd.lhs * U + u) * kThreads];
+            *reinterpret_cast<uint4*>(&b[u]) = mine[(nd.rhs * U + u) * kThreads];
+        }
+        node_dispatch<T, U>(nd.opcode, a, b, nd.imm, r);
+#pragma unroll
+        for (int u = 0; u < U; ++u) mine[((kMaxIn + n) * U + u) * kThreads] = *reinterpret_cast<const uint4*>(&r[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) *reinterpret_cast<uint4*>(&out[u]) = mine[((kMaxIn + g.n_nodes - 1) * U + u) * kThreads];
 }
 
 // Evaluates the program on one 16-byte vector of every input.
@@ -881,24 +919,7 @@ __device__ __forceinline__ Vec<T> eval_vector(const Vec<T> (&vin)[kMaxIn], const
 #pragma unroll
         for (int i = 0; i < V; ++i) out.e[i] = from_compute<T, C>(val[kMaxIn + P::N - 1][i]);
     } else {
-        // The interpreter keeps every value (inputs, then one per node, rounded to the storage type
-        // like the node-by-node chain) in shared memory: 16 bytes per thread and value, value k of
-        // thread t at word k * blockDim.x + t. Nothing is shared between threads, so no barrier
-        // is needed; shared memory only stands in for a register file that can be indexed at run time.
-        extern __shared__ uint4 program_values[];
-        uint4* mine = program_values + threadIdx.x;
-#pragma unroll
-        for (int k = 0; k < kMaxIn; ++k)
-            if (k < g.n_inputs) mine[k * kThreads] = *reinterpret_cast<const uint4*>(&vin[k]);
-        for (int n = 0; n < g.n_nodes; ++n) {
-            const tn_eltwise_node_t nd = g.nodes[n];
-            Vec<T> a, b;
-            *reinterpret_cast<uint4*>(&a) = mine[nd.lhs * kThreads];
-            *reinterpret_cast<uint4*>(&b) = mine[nd.rhs * kThreads];
-            const Vec<T> r = node_dispatch<T>(nd.opcode, a, b, nd.imm);
-            mine[(kMaxIn + n) * kThreads] = *reinterpret_cast<const uint4*>(&r);
-        }
-        *reinterpret_cast<uint4*>(&out) = mine[(kMaxIn + g.n_nodes - 1) * kThreads];
+        static_assert(STATIC, "interpreted programs go through eval_interpreted");
     }
     return out;
 }
@@ -933,9 +954,17 @@ __global__ void __launch_bounds__(kThreads) ew_program_rows(const __grid_constan
                     }
                 }
             }
+            if constexpr (P::N == 0) {
+                Vec<T> outs[UNROLL];
+                eval_interpreted<T, UNROLL>(vin, outs, g);
 #pragma unroll
-            for (int u = 0; u < UNROLL; ++u)
-                if (r0 + u < g.rows) store_vec(static_cast<T*>(g.d) + (r0 + u) * g.cols + c, eval_vector<T, P>(vin[u], g));
+                for (int u = 0; u < UNROLL; ++u)
+                    if (r0 + u < g.rows) store_vec(static_cast<T*>(g.d) + (r0 + u) * g.cols + c, outs[u]);
+            } else {
+#pragma unroll
+                for (int u = 0; u < UNROLL; ++u)
+                    if (r0 + u < g.rows) store_vec(static_cast<T*>(g.d) + (r0 + u) * g.cols + c, eval_vector<T, P>(vin[u], g));
+            }
         }
     }
 }
@@ -1038,18 +1067,20 @@ tn_status launch_program(const Plan& plan, const tn_tensor_t* const* inputs, int
         else if (matches<ProgNormScale>(nodes, n_nodes)) TN_LAUNCH_PROGRAM(ProgNormScale);
         else {
             // the interpreter: 16 bytes of shared memory per thread and value
-            const size_t smem = (size_t)(kMaxIn + n_nodes) * kThreads * 16;
+            const int iu = any_scalar ? 1 : (env_int("TN_INTERPRETER_UNROLL", 2) >= 2 ? 2 : 1);
+            const size_t smem = (size_t)(kMaxIn + n_nodes) * kThreads * 16 * iu;
             static thread_local int attr_device = -1;
             int dev = 0;
             TN_CUDA(cudaGetDevice(&dev));
             if (attr_device != dev) {
-                const int most = (kMaxIn + kMaxNodes) * kThreads * 16;
+                const int most = (kMaxIn + kMaxNodes) * kThreads * 16 * 2;
                 TN_CUDA(cudaFuncSetAttribute(ew_program_rows<T, ProgDynamic, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
                 TN_CUDA(cudaFuncSetAttribute(ew_program_rows<T, ProgDynamic, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
                 TN_CUDA(cudaFuncSetAttribute(ew_program_rows<T, ProgDynamic, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
                 attr_device = dev;
             }
             if (any_scalar) launch(ew_program_rows<T, ProgDynamic, 1, true>, 1, smem);
+            else if (iu == 2) launch(ew_program_rows<T, ProgDynamic, 2, false>, 2, smem);
             else launch(ew_program_rows<T, ProgDynamic, 1, false>, 1, smem);
         }
 #undef TN_LAUNCH_PROGRAM
