@@ -217,6 +217,15 @@ def secondary_workloads(torch, tb, A, hbm_peak, tf_peak, only=None, small=False)
         ms = time_device(lambda: tb.program([x, y], nodes, out=z), iters, warm, torch)
         record("config2c_interpreted_expression_fp16", ms, bytes_=2 * 8192 * 8192 * 2 + 8192 * 2, note="log(X)+Y*Y-exp(X), nodes reordered")
 
+    def config1():
+        # the reference's own CPU-runnable case, on the device for information: float32, so the
+        # SIMT kernel (the tensor-core path takes 16-bit operands)
+        g.manual_seed(0)
+        a = torch.rand((512, 1024), device="cuda", generator=g) * 2 - 1
+        b = torch.rand((1024, 512), device="cuda", generator=g) * 2 - 1
+        ms = time_device(lambda: tb.matmul(a, b), iters, warm, torch)
+        record("config1_matmul_f32_512x1024x512", ms, flops=2 * 512 * 512 * 1024, bound="fp32", note="gemm_simt, float32 accumulate")
+
     def config3():
         batch = 2 if small else 8
         g.manual_seed(2)
@@ -252,7 +261,7 @@ def secondary_workloads(torch, tb, A, hbm_peak, tf_peak, only=None, small=False)
         ms = time_device(lambda: tb.convolve2D(xin, w3, 1, 1), max(2, iters // 2), max(1, warm - 1), torch)
         record("config4a_conv3x3_fp16", ms, flops=2 * n * 256 * 3136 * 256 * 9, bound="tensor", note=f"x[{n},256,56,56]")
 
-    table = {"config2b": config2b, "config2c": config2c, "config3": config3, "config5": config5, "config4": config4}
+    table = {"config1": config1, "config2b": config2b, "config2c": config2c, "config3": config3, "config5": config5, "config4": config4}
     for name, fn in table.items():
         if only is not None and only != name:
             continue
@@ -409,7 +418,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--headline-only", action="store_true", help="skip the secondary workloads")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--only", default=None, choices=["config2b", "config2c", "config3", "config4", "config5"],
+    ap.add_argument("--only", default=None, choices=["config1", "config2b", "config2c", "config3", "config4", "config5"],
                     help="run one secondary workload alone (profiling aid)")
     ap.add_argument("--small", action="store_true", help="with --only: shrink the leading dimension for a short profiler capture")
     args = ap.parse_args()

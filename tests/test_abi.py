@@ -106,3 +106,27 @@ def test_front_end_rules_mirror_the_reference():
     d = tb.desc(t.t())
     assert (d.rank, d.size, list(d.shape.sizes[:2]), list(d.strides.sizes[:2])) == (2, 12, [4, 3], [1, 4])
     assert d.environment.kind == A.HOST
+
+
+def test_header_is_plain_c(tmp_path):
+    """include/tannic_b200.h compiles as C11 on its own (no C++ or CUDA types leak into the ABI), and a C
+    translation unit that takes the address of every declared entry point links against the library."""
+    import re
+    import shutil
+    import subprocess
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    gcc = shutil.which("gcc")
+    lib = root / "tannic_b200" / "libtannic_b200.so"
+    if gcc is None or not lib.exists():
+        pytest.skip("needs gcc and the built library")
+    header = (root / "include" / "tannic_b200.h").read_text()
+    names = sorted(set(re.findall(r"\b(tn_[a-z0-9_]+)\s*\(", header)))
+    assert len(names) > 50
+    src = tmp_path / "abi.c"
+    src.write_text('#include "tannic_b200.h"\n#include <stdio.h>\ntypedef void (*any_fn)(void);\nint main(void) {\n  any_fn table[] = {\n'
+                   + "".join(f"    (any_fn){n},\n" for n in names)
+                   + '  };\n  printf("%zu\\n", sizeof table / sizeof table[0]);\n  return sizeof(tn_tensor_t) == 176 ? 0 : 1;\n}\n')
+    exe = tmp_path / "abi"
+    subprocess.run([gcc, "-std=c11", "-Wall", "-Werror", "-pedantic", f"-I{root / 'include'}", str(src), "-o", str(exe),
+                    f"-L{lib.parent}", "-ltannic_b200", f"-Wl,-rpath,{lib.parent}"], check=True, capture_output=True, text=True)
