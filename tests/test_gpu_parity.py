@@ -267,7 +267,9 @@ def test_reduce_keepdim_and_stats():
 
 
 @pytest.mark.parametrize("dtype,shape", [(torch.bfloat16, (12, 197, 197)), (torch.float16, (4099, 64)), (torch.float32, (3001, 100)),
-                                         (torch.int32, (2500, 33)), (torch.float64, (2100, 8)), (torch.int8, (2048, 1000))])
+                                         (torch.int32, (2500, 33)), (torch.float64, (2100, 8)), (torch.int8, (2048, 1000)),
+                                         (torch.bfloat16, (2100, 1000)), (torch.float32, (2300, 300)), (torch.float16, (2200, 999)),
+                                         (torch.float64, (2050, 250)), (torch.int16, (2111, 1001))])
 def test_reductions_many_short_rows_staged_in_shared_memory(dtype, shape):
     """Enough short rows to take the staged kernel (whole rows brought in by bulk copies, one
     thread per row); row counts that are not a multiple of the chunk exercise the ragged tail."""
