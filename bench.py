@@ -288,6 +288,9 @@ def ours(args):
         raise SystemExit("bench.py needs a CUDA device")
     torch.cuda.set_device(local)
     if world > 1:
+        # stdout carries the one JSON line and nothing else: NCCL's own messages (its version banner
+        # under NCCL_DEBUG=VERSION, for one) go to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     hbm_peak, tf_peak, peak_kind = peaks()
     if args.only:
