@@ -291,6 +291,8 @@ def ours(args):
         # stdout carries the one JSON line and nothing else: NCCL's own messages (its version banner
         # under NCCL_DEBUG=VERSION, for one) go to stderr
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # the banner is written to stdout whatever the debug file is
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     hbm_peak, tf_peak, peak_kind = peaks()
     if args.only:
