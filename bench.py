@@ -218,13 +218,12 @@ def secondary_workloads(torch, tb, A, hbm_peak, tf_peak, only=None, small=False)
         record("config2c_interpreted_expression_fp16", ms, bytes_=2 * 8192 * 8192 * 2 + 8192 * 2, note="log(X)+Y*Y-exp(X), nodes reordered")
 
     def config1():
-        # the reference's own CPU-runnable case, on the device for information: float32, so the
-        # SIMT kernel (the tensor-core path takes 16-bit operands)
+        # the reference's own CPU-runnable case, on the device for information
         g.manual_seed(0)
         a = torch.rand((512, 1024), device="cuda", generator=g) * 2 - 1
         b = torch.rand((1024, 512), device="cuda", generator=g) * 2 - 1
         ms = time_device(lambda: tb.matmul(a, b), iters, warm, torch)
-        record("config1_matmul_f32_512x1024x512", ms, flops=2 * 512 * 512 * 1024, bound="fp32", note="gemm_simt, float32 accumulate")
+        record("config1_matmul_f32_512x1024x512", ms, flops=2 * 512 * 512 * 1024, bound="fp32", note="float32 as three bfloat16 parts on the tensor cores, float32 accumulate")
 
     def config3():
         batch = 2 if small else 8

@@ -27,6 +27,7 @@ struct SimtArgs {
     int has_scale;
     double scale_f;
     int64_t scale_i;
+    const int* run_if;  // when set: the kernel does nothing unless *run_if != 0 (device-side fallback)
 };
 
 constexpr int TM = 64, TN = 64, TK = 16;
@@ -38,6 +39,7 @@ template <typename C>
 __global__ void __launch_bounds__(256) gemm_simt(const __grid_constant__ SimtArgs g) {
     __shared__ C As[TK][TM + 1];
     __shared__ C Bs[TK][TN + 1];
+    if (g.run_if != nullptr && *g.run_if == 0) return;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     for (int64_t batch = blockIdx.z; batch < g.batches; batch += gridDim.z) {
         int64_t oa = 0, ob = 0, od = 0, rem = batch;
@@ -135,6 +137,62 @@ int compute_class(int a, int b) {
     return 0;
 }
 
+// ---- float32 operands on the tensor cores: three-way bfloat16 split -------------------------
+// x = x0 + x1 + x2 with every part a bfloat16 (x0 = bf16(x), x1 = bf16(x - x0), x2 = bf16(x - x0 - x1);
+// bfloat16 has float32's exponent range, so the parts carry 24 significand bits between them).
+// A.B is then the sum of the six products A_i.B_j with i + j <= 2 (the others are below 2^-24 of
+// the result), evaluated as ONE bfloat16 GEMM with float32 accumulation whose K extent is six times
+// as long: A' = [A0 A0 A1 A0 A1 A2] and B' = [B0 B1 B0 B2 B1 B0] along K.
+constexpr int kSplitTerms = 6;
+__constant__ int kSplitA[kSplitTerms] = {0, 0, 1, 0, 1, 2};
+__constant__ int kSplitB[kSplitTerms] = {0, 1, 0, 2, 1, 0};
+
+__device__ __forceinline__ void split3(float x, uint16_t (&part)[3], int* non_finite) {
+    if (!isfinite(x)) *non_finite = 1;  // benign race: every writer stores the same value
+    __nv_bfloat16 p0 = __float2bfloat16_rn(x);
+    if (isinf(__bfloat162float(p0)) && !isinf(x)) p0 = __ushort_as_bfloat16(x < 0 ? 0xFF7Fu : 0x7F7Fu);  // rounding overflowed
+    float r = x - __bfloat162float(p0);
+    if (!isfinite(x)) r = 0.0f;  // inf / NaN live in the first part alone
+    const __nv_bfloat16 p1 = __float2bfloat16_rn(r);
+    r -= __bfloat162float(p1);
+    const __nv_bfloat16 p2 = __float2bfloat16_rn(r);
+    part[0] = __bfloat16_as_ushort(p0);
+    part[1] = __bfloat16_as_ushort(p1);
+    part[2] = __bfloat16_as_ushort(p2);
+}
+
+// x[batch][r][k] (any strides) -> out[batch][r][6 * kp], k fastest on the way out; columns k >= K are zero.
+__global__ void __launch_bounds__(256) split_k_major(const float* __restrict__ x, uint16_t* __restrict__ out, int64_t rows, int64_t K,
+                                                     int64_t kp, int64_t s_r, int64_t s_k, int64_t s_batch, int second_operand, int* non_finite) {
+    const int64_t batch = blockIdx.z;
+    const float* xb = x + batch * s_batch;
+    uint16_t* ob = out + batch * rows * kSplitTerms * kp;
+    const int64_t n = rows * kp;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+        const int64_t r = i / kp, k = i - r * kp;
+        uint16_t part[3] = {0, 0, 0};
+        if (k < K) split3(xb[r * s_r + k * s_k], part, non_finite);
+#pragma unroll
+        for (int t = 0; t < kSplitTerms; ++t) ob[r * kSplitTerms * kp + t * kp + k] = part[second_operand ? kSplitB[t] : kSplitA[t]];
+    }
+}
+
+// b[batch][k][n] with n contiguous -> out[batch][6 * kp][np], n fastest; rows k >= K and columns n >= N are zero.
+__global__ void __launch_bounds__(256) split_n_major(const float* __restrict__ b, uint16_t* __restrict__ out, int64_t K, int64_t N,
+                                                     int64_t kp, int64_t np, int64_t s_k, int64_t s_batch, int* non_finite) {
+    const int64_t batch = blockIdx.z;
+    const float* bb = b + batch * s_batch;
+    uint16_t* ob = out + batch * kSplitTerms * kp * np;
+    const int64_t n_all = kp * np;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n_all; i += (int64_t)gridDim.x * 256) {
+        const int64_t k = i / np, n = i - k * np;
+        uint16_t part[3] = {0, 0, 0};
+        if (k < K && n < N) split3(bb[k * s_k + n], part, non_finite);
+#pragma unroll
+        for (int t = 0; t < kSplitTerms; ++t) ob[(t * kp + k) * np + n] = part[kSplitB[t]];
+    }
+}
+
 tn_status gemm_impl(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, const tn_scalar_t* scale,
                     tn_stream_t stream) {
     if (!a || !b || !dst) return fail(TN_ERROR, "null tensor");
@@ -190,6 +248,7 @@ tn_status gemm_impl(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst
     g.has_scale = 0;
     g.scale_f = 1.0;
     g.scale_i = 1;
+    g.run_if = nullptr;
     if (scale) {
         if (scale->dtype != dst->dtype) return fail(TN_UNSUPPORTED_DTYPE, "gemm_scaled: scalar dtype %d, result dtype %d", (int)scale->dtype, (int)dst->dtype);
         if (!read_host_scalar(scale, &g.scale_f, &g.scale_i)) return fail(TN_ERROR, "gemm_scaled: unreadable scalar");
@@ -197,6 +256,99 @@ tn_status gemm_impl(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst
     }
     if (g.M == 0 || g.N == 0 || g.batches == 0) return TN_SUCCESS;
     cudaStream_t s = as_cuda(stream);
+
+    // collapse the batch dims of an operand into one stride; possible when walking them in row-major
+    // order advances by a constant stride, or the operand is shared by every batch
+    auto collapse_batches = [&](const int64_t* bs, int64_t* stride) {
+        bool any = false, all = true;
+        int64_t expect = 0;
+        for (int dim = g.nbatch - 1; dim >= 0; --dim) {
+            if (g.bsize[dim] == 1) continue;
+            if (bs[dim] == 0) { all = false; continue; }
+            if (!any) { expect = bs[dim]; *stride = bs[dim]; any = true; }
+            if (bs[dim] != expect) return false;
+            expect = bs[dim] * g.bsize[dim];
+        }
+        if (!any) { *stride = 0; return true; }
+        return all;
+    };
+
+    // ---- float32 on the tensor cores (three-way bfloat16 split), for products big enough to pay for
+    //      the split passes: dense rows in the result, batch dims that collapse
+    static const bool f32_on_tc = !getenv("TN_GEMM_F32_SIMT");
+    if (f32_on_tc && a->dtype == TN_FLOAT32 && b->dtype == TN_FLOAT32 && dst->dtype == TN_FLOAT32 && g.d_sn == 1 && g.K > 0 &&
+        (double)g.batches * (double)g.M * (double)g.N * (double)g.K >= (double)(1 << 24) && g.batches <= 65535) {
+        int64_t sa = 0, sb = 0, sd = 0;
+        if (collapse_batches(g.a_bs, &sa) && collapse_batches(g.b_bs, &sb) && collapse_batches(g.d_bs, &sd) && (sd != 0 || g.batches == 1)) {
+            const int64_t kp = (g.K + 7) & ~int64_t(7), np = (g.N + 7) & ~int64_t(7);
+            const bool b_n_major = g.b_sn == 1 && g.b_sk != 1;
+            const int64_t a_copies = sa ? g.batches : 1, b_copies = sb ? g.batches : 1;
+            const size_t a_elems = (size_t)a_copies * g.M * kSplitTerms * kp;
+            const size_t b_elems = (size_t)b_copies * kSplitTerms * kp * (b_n_major ? np : g.N);
+            const size_t a_bytes = (a_elems * 2 + 255) & ~size_t(255), b_bytes = b_elems * 2;
+            if (a_bytes + b_bytes <= (size_t(8) << 30) && ceil_div(g.M, TM) <= 65535) {
+                uint8_t* scratch = nullptr;
+                TN_TRY(scratch_alloc(reinterpret_cast<void**>(&scratch), a_bytes + b_bytes + 256, s));
+                uint16_t* a3 = reinterpret_cast<uint16_t*>(scratch);
+                uint16_t* b3 = reinterpret_cast<uint16_t*>(scratch + a_bytes);
+                // An infinity or NaN cannot go through the split (inf times the parts of the other operand
+                // gives infinities of both signs). The split passes raise this flag when they meet one, and
+                // the element-wise kernel, launched behind the tensor-core GEMM, recomputes the product only
+                // if the flag is up: no host round trip, one near-empty launch otherwise.
+                int* non_finite = reinterpret_cast<int*>(scratch + a_bytes + ((b_bytes + 255) & ~size_t(255)));
+                if (cudaMemsetAsync(non_finite, 0, sizeof(int), s) != cudaSuccess) {
+                    scratch_free(scratch, s);
+                    return fail(TN_ERROR, "gemm: could not clear the fallback flag");
+                }
+                const int blocks = sm_count() * 8;
+                split_k_major<<<dim3((unsigned)std::min<int64_t>(blocks, ceil_div(g.M * kp, 256)), 1, (unsigned)a_copies), 256, 0, s>>>(
+                    static_cast<const float*>(g.a), a3, g.M, g.K, kp, g.a_sm, g.a_sk, sa, 0, non_finite);
+                tn_status st = after_launch("split_k_major");
+                if (st == TN_SUCCESS) {
+                    if (b_n_major)
+                        split_n_major<<<dim3((unsigned)std::min<int64_t>(blocks, ceil_div(kp * np, 256)), 1, (unsigned)b_copies), 256, 0, s>>>(
+                            static_cast<const float*>(g.b), b3, g.K, g.N, kp, np, g.b_sk, sb, non_finite);
+                    else
+                        split_k_major<<<dim3((unsigned)std::min<int64_t>(blocks, ceil_div(g.N * kp, 256)), 1, (unsigned)b_copies), 256, 0, s>>>(
+                            static_cast<const float*>(g.b), b3, g.N, g.K, kp, g.b_sn, g.b_sk, sb, 1, non_finite);
+                    st = after_launch("split operand");
+                }
+                if (st == TN_SUCCESS) {
+                    TcGemm p;
+                    p.a = a3;
+                    p.b = b3;
+                    p.d = g.d;
+                    p.ab_dtype = TN_BFLOAT16;
+                    p.d_dtype = TN_FLOAT32;
+                    p.M = g.M;
+                    p.N = g.N;
+                    p.K = kSplitTerms * kp;
+                    p.lda = kSplitTerms * kp;
+                    p.b_n_major = b_n_major;
+                    p.ldb = b_n_major ? np : kSplitTerms * kp;
+                    p.ldd = g.d_sm;
+                    p.batches = g.batches;
+                    p.a_batch = sa ? g.M * kSplitTerms * kp : 0;
+                    p.b_batch = sb ? kSplitTerms * kp * (b_n_major ? np : g.N) : 0;
+                    p.d_batch = sd;
+                    p.has_scale = g.has_scale != 0;
+                    p.scale = (float)g.scale_f;
+                    st = tc_gemm_eligible(p) ? tc_gemm(p, s) : TN_UNSUPPORTED_DTYPE;
+                    const int64_t gy = ceil_div(g.M, TM);
+                    if (st == TN_SUCCESS && gy <= 65535) {
+                        SimtArgs guarded = g;
+                        guarded.run_if = non_finite;
+                        const dim3 grid((unsigned)ceil_div(g.N, TN), (unsigned)gy, (unsigned)g.batches);
+                        gemm_simt<float><<<grid, 256, 0, s>>>(guarded);
+                        st = after_launch("gemm_simt (non-finite fallback)");
+                    }
+                }
+                const tn_status fr = scratch_free(scratch, s);
+                if (st == TN_SUCCESS) return fr;
+                if (st != TN_UNSUPPORTED_DTYPE) return st;  // else: not addressable by TMA, take the SIMT kernel
+            }
+        }
+    }
 
     // ---- tensor-core path: 16-bit operands of one type, result of that type or fp32,
     //      row-major result, batch dims that collapse to one stride per operand.

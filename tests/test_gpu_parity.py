@@ -421,6 +421,50 @@ def test_matmul_short_k_many_row_tiles(batches, m, n, k, n_major):
     assert tb.device_errors() == 0
 
 
+@pytest.mark.parametrize("case", ["plain", "b_transposed", "a_transposed", "batched", "shared_b", "odd"])
+def test_matmul_float32_on_tensor_cores(case):
+    """float32 products above 2^24 multiply-adds run on the tensor cores: each operand is split into three
+    bfloat16 parts and the six significant part products are summed in float32. Checked against the float64
+    product (summation order differs from the reference loop) and, on a block of rows, against the oracle."""
+    if case == "plain":
+        a, b = gen((384, 520), torch.float32, 90, -1, 1), gen((520, 300), torch.float32, 91, -1, 1)
+        da, db = dev(a), dev(b)
+    elif case == "b_transposed":
+        a, w = gen((256, 1024), torch.float32, 92, -1, 1), gen((136, 1024), torch.float32, 93, -1, 1)
+        b = w.t()
+        da, db = dev(a), dev(w).t()
+    elif case == "a_transposed":
+        at, b = gen((512, 200), torch.float32, 94, -1, 1), gen((512, 264), torch.float32, 95, -1, 1)
+        a = at.t()
+        da, db = dev(at).t(), dev(b)
+    elif case == "batched":
+        a, b = gen((5, 130, 333), torch.float32, 96, -1, 1), gen((5, 333, 200), torch.float32, 97, -1, 1)
+        da, db = dev(a), dev(b)
+    elif case == "shared_b":
+        a, b = gen((3, 4, 100, 256), torch.float32, 98, -1, 1), gen((256, 192), torch.float32, 99, -1, 1)
+        da, db = dev(a), dev(b)
+    else:
+        a, b = gen((257, 1001), torch.float32, 100, -50, 50), gen((1001, 67), torch.float32, 101, -1e-3, 1e-3)
+        da, db = dev(a), dev(b)
+    launches = tb.launch_count()
+    got = tb.matmul(da, db)
+    assert tb.launch_count() - launches == 4, "expected two split passes, the tensor-core GEMM and the (idle) fallback"
+    want = torch.matmul(a.double(), b.double())
+    scale = torch.matmul(a.double().abs(), b.double().abs())  # size of the terms that were summed
+    assert got.dtype == torch.float32 and got.shape == want.shape
+    assert bool(((got.cpu().double() - want).abs() <= 4e-6 * scale + 1e-30).all())
+    rows = oracle.matmul(a.reshape(-1, a.shape[-2], a.shape[-1])[0][:8], b.reshape(-1, b.shape[-2], b.shape[-1])[0], acc=oracle.ACC_STORAGE)
+    assert torch.allclose(got.reshape(-1, got.shape[-2], got.shape[-1])[0][:8].cpu(), rows, rtol=1e-4, atol=1e-4 * float(scale.max()))
+    assert tb.device_errors() == 0
+    # infinities and NaN cannot be split: the passes flag them and the element-wise kernel recomputes on the device
+    a2 = a.clone().reshape(-1, a.shape[-1])
+    a2[0, 0], a2[1, 1] = float("inf"), 3.0e38
+    a2 = a2.reshape(a.shape)
+    out = tb.matmul(dev(a2) if case != "a_transposed" else dev(a2.t().contiguous()).t(), db).cpu()
+    ref = torch.matmul(a2.double(), b.double()).float()
+    assert torch.isinf(out.reshape(-1, out.shape[-1])[0]).all() and torch.equal(torch.isinf(out), torch.isinf(ref))
+
+
 def test_matmul_half_to_float32_result():
     a, w = gen((130, 136), torch.bfloat16, 38, -1, 1), gen((72, 136), torch.bfloat16, 39, -1, 1)
     got = tb.matmul(dev(a), dev(w).t(), out_dtype=A.FLOAT32)
