@@ -237,18 +237,27 @@ tn_status conv_impl(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_
         p.x_nhwc = g.y;
         p.w_packed = g.y;
         if (tc_conv_eligible(p)) {
-            const size_t x_bytes = (size_t)(g.N * g.H * g.W * g.Cin) * 2, w_bytes = (size_t)(g.Kh * g.Kw * g.Cout * g.Cin) * 2;
+            // an activation that already lies as [N][H][W][C] in memory (an NCHW view of channels-last
+            // storage) is read in place; only the weights are repacked then
+            const bool x_is_nhwc = g.xs[1] == 1 && g.xs[3] == g.Cin && g.xs[2] == g.W * g.Cin && g.xs[0] == g.H * g.W * g.Cin &&
+                                   (reinterpret_cast<uintptr_t>(g.x) & 15) == 0;
+            const size_t x_bytes = x_is_nhwc ? 0 : (size_t)(g.N * g.H * g.W * g.Cin) * 2, w_bytes = (size_t)(g.Kh * g.Kw * g.Cout * g.Cin) * 2;
             const size_t x_padded = (x_bytes + 255) & ~size_t(255);
             uint8_t* scratch = nullptr;
             TN_TRY(scratch_alloc(reinterpret_cast<void**>(&scratch), x_padded + w_bytes, s));
             uint16_t* xh = reinterpret_cast<uint16_t*>(scratch);
             uint16_t* wp = reinterpret_cast<uint16_t*>(scratch + x_padded);
             const dim3 tgrid((unsigned)ceil_div(g.H * g.W, 64), (unsigned)ceil_div(g.Cin, 64), (unsigned)g.N);
-            if (dense_nchw(x) && (g.H * g.W) % 8 == 0 && (reinterpret_cast<uintptr_t>(g.x) & 15) == 0)
-                nchw_to_nhwc_vec<<<tgrid, 256, 0, s>>>(static_cast<const uint16_t*>(g.x), xh, g.Cin, g.H * g.W);
-            else
-                nchw_to_nhwc<<<tgrid, 256, 0, s>>>(static_cast<const uint16_t*>(g.x), xh, g.Cin, g.H, g.W, g.xs[0], g.xs[1], g.xs[2], g.xs[3]);
-            tn_status st = after_launch("nchw_to_nhwc");
+            tn_status st = TN_SUCCESS;
+            if (x_is_nhwc) {
+                xh = const_cast<uint16_t*>(static_cast<const uint16_t*>(g.x));
+            } else {
+                if (dense_nchw(x) && (g.H * g.W) % 8 == 0 && (reinterpret_cast<uintptr_t>(g.x) & 15) == 0)
+                    nchw_to_nhwc_vec<<<tgrid, 256, 0, s>>>(static_cast<const uint16_t*>(g.x), xh, g.Cin, g.H * g.W);
+                else
+                    nchw_to_nhwc<<<tgrid, 256, 0, s>>>(static_cast<const uint16_t*>(g.x), xh, g.Cin, g.H, g.W, g.xs[0], g.xs[1], g.xs[2], g.xs[3]);
+                st = after_launch("nchw_to_nhwc");
+            }
             if (st == TN_SUCCESS) {
                 int64_t wblocks = ceil_div(g.Kh * g.Kw * g.Cout * g.Cin, 256);
                 if (wblocks > 1184) wblocks = 1184;

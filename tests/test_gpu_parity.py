@@ -628,7 +628,13 @@ def test_conv2d_implicit_gemm_strided_input_view():
     xv = x.permute(0, 3, 1, 2)                                     # NCHW view with channel stride 1
     wt = gen((16, 64, 3, 3), torch.float16, 51, -0.2, 0.2)
     want = oracle.conv2d(xv, wt, 1, 1, acc=oracle.ACC_WIDE)
-    assert_close(tb.convolve2D(dev(x).permute(0, 3, 1, 2), dev(wt), 1, 1), want)
+    launches = tb.launch_count()
+    got = tb.convolve2D(dev(x).permute(0, 3, 1, 2), dev(wt), 1, 1)
+    assert tb.launch_count() - launches == 2, "channels-last storage is read in place: weight packing + GEMM only"
+    assert_close(got, want)
+    # a view that is neither NCHW-dense nor channels-last goes through the generic staging kernel
+    xs = gen((2, 64, 12, 20), torch.float16, 55, -1, 1)
+    assert_close(tb.convolve2D(dev(xs)[:, :, :, ::2], dev(wt), 1, 1), oracle.conv2d(xs[:, :, :, ::2], wt, 1, 1, acc=oracle.ACC_WIDE))
 
 
 def test_conv2d_errors():
