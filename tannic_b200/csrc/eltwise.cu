@@ -1126,7 +1126,21 @@ tn_status tn_mul(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* d, tn_
 tn_status tn_pow(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* d, tn_stream_t s) { return binary<TN_OP_POW>(a, b, d, s); }
 
 tn_status tn_neg(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_NEG>(x, d, s, Imm{0, 0}); }
-tn_status tn_repack(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_COUNT>(x, d, s, Imm{0, 0}); }
+tn_status tn_repack(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) {
+    // a strided view goes through the copy machinery (coalesced dimensions, 16-byte runs, tiled
+    // transposes); a dense source keeps the flat path
+    if (x && d && x->dtype == d->dtype && x->rank == d->rank && x->rank > 0) {
+        bool dense = true, same = true;
+        int64_t expect = 1;
+        for (int dim = x->rank - 1; dim >= 0; --dim) {
+            if (x->shape.sizes[dim] != d->shape.sizes[dim]) same = false;
+            if (x->shape.sizes[dim] != 1 && x->strides.sizes[dim] != expect) dense = false;
+            expect *= (int64_t)x->shape.sizes[dim];
+        }
+        if (same && !dense) return tn_cpy(x, d, s);
+    }
+    return unary<TN_OP_COUNT>(x, d, s, Imm{0, 0});
+}
 tn_status tn_log(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_LOG>(x, d, s, Imm{0, 0}); }
 tn_status tn_exp(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_EXP>(x, d, s, Imm{0, 0}); }
 tn_status tn_sqrt(const tn_tensor_t* x, tn_tensor_t* d, tn_stream_t s) { return unary<TN_OP_SQRT>(x, d, s, Imm{0, 0}); }

@@ -36,6 +36,87 @@ __global__ void __launch_bounds__(kThreads) cpy_strided(const W* __restrict__ sr
     }
 }
 
+// Tiled transpose for views whose unit-stride dimension is not the result's: 32 x 32 element tiles
+// through shared memory, read along the source's unit-stride dimension `jd`, written along the
+// result's last one. The other dimensions are decoded once per tile.
+template <typename W>
+__global__ void __launch_bounds__(kThreads) cpy_transposed(const W* __restrict__ src, W* __restrict__ dst, PairGeom g, int jd,
+                                                           int64_t tiles_j, int64_t tiles_l, int64_t tiles) {
+    __shared__ W tile[32][33];
+    const int last = g.rank - 1;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    const int64_t J = g.sizes[jd], L = g.sizes[last];
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int64_t tl = t % tiles_l;
+        int64_t rest = t / tiles_l;
+        const int64_t tj = rest % tiles_j;
+        rest /= tiles_j;
+        int64_t oa = 0, ob = 0;
+        for (int d = last - 1; d >= 0; --d) {
+            if (d == jd) continue;
+            const int64_t c = rest % g.sizes[d];
+            rest /= g.sizes[d];
+            oa += c * g.sa[d];
+            ob += c * g.sb[d];
+        }
+        const int64_t j0 = tj * 32, l0 = tl * 32;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int64_t l = l0 + ty + 8 * i, j = j0 + tx;
+            if (l < L && j < J) tile[ty + 8 * i][tx] = src[oa + j * g.sa[jd] + l * g.sa[last]];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int64_t j = j0 + ty + 8 * i, l = l0 + tx;
+            if (j < J && l < L) dst[ob + j * g.sb[jd] + l * g.sb[last]] = tile[tx][ty + 8 * i];
+        }
+        __syncthreads();
+    }
+}
+
+// The same for 2-byte elements, two at a time: 64 x 64 tiles, 4-byte global loads along the
+// source's unit-stride dimension and 4-byte global stores along the result's (128 bytes per warp
+// row either way). Needs even extents, even strides and 4-byte aligned bases (checked on the host).
+__global__ void __launch_bounds__(kThreads) cpy_transposed_pairs(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, PairGeom g,
+                                                                 int jd, int64_t tiles_j, int64_t tiles_l, int64_t tiles) {
+    __shared__ uint16_t tile[64][66];  // [l][j], 33-word pitch
+    const int last = g.rank - 1;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 lanes x 8 rows per pass
+    const int64_t J = g.sizes[jd], L = g.sizes[last];
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int64_t tl = t % tiles_l;
+        int64_t rest = t / tiles_l;
+        const int64_t tj = rest % tiles_j;
+        rest /= tiles_j;
+        int64_t oa = 0, ob = 0;
+        for (int d = last - 1; d >= 0; --d) {
+            if (d == jd) continue;
+            const int64_t c = rest % g.sizes[d];
+            rest /= g.sizes[d];
+            oa += c * g.sa[d];
+            ob += c * g.sb[d];
+        }
+        const int64_t j0 = tj * 64, l0 = tl * 64;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int64_t l = l0 + ty + 8 * i, j = j0 + 2 * tx;
+            if (l < L && j < J)  // J is even: the pair is inside or outside as a whole
+                *reinterpret_cast<uint32_t*>(&tile[ty + 8 * i][2 * tx]) = *reinterpret_cast<const uint32_t*>(src + oa + j + l * g.sa[last]);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int64_t j = j0 + ty + 8 * i, l = l0 + 2 * tx;
+            if (j < J && l < L) {
+                const uint32_t pair = static_cast<uint32_t>(tile[2 * tx][ty + 8 * i]) | (static_cast<uint32_t>(tile[2 * tx + 1][ty + 8 * i]) << 16);
+                *reinterpret_cast<uint32_t*>(dst + ob + j * g.sb[jd] + l) = pair;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads) allclose_kernel(const T* __restrict__ a, const T* __restrict__ b, PairGeom g,
                                                             double rtol, double atol, int* mismatch) {
@@ -128,6 +209,45 @@ tn_status tn_cpy(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream) {
             }
             cpy_strided<uint4><<<grid_for(w.n), kThreads, 0, s>>>(static_cast<const uint4*>(src->address), static_cast<uint4*>(dst->address), w);
             return after_launch("cpy_strided");
+        }
+    }
+    // A transposing view: the source is contiguous along a dimension that is not the result's last.
+    {
+        const int last = g.rank - 1;
+        int jd = -1;
+        if (last >= 1 && g.sb[last] == 1 && g.sa[last] != 1 && g.sizes[last] >= 16)
+            for (int d = 0; d < last; ++d)
+                if (g.sa[d] == 1 && g.sizes[d] >= 16) jd = d;
+        const int esize = dtype_bytes(src->dtype);
+        if (jd >= 0 && esize <= 8) {
+            int64_t outer = 1;
+            for (int d = 0; d < last; ++d)
+                if (d != jd) outer *= g.sizes[d];
+            const int64_t cap = (int64_t)sm_count() * 16;
+            if (esize == 2) {
+                bool pairs = g.sizes[jd] % 2 == 0 && g.sizes[last] % 2 == 0 && (reinterpret_cast<uintptr_t>(src->address) & 3) == 0 &&
+                             (reinterpret_cast<uintptr_t>(dst->address) & 3) == 0;
+                for (int d = 0; pairs && d <= last; ++d) {
+                    if (d != jd && g.sa[d] % 2 != 0) pairs = false;
+                    if (d != last && g.sb[d] % 2 != 0) pairs = false;
+                }
+                if (pairs) {
+                    const int64_t tj = ceil_div(g.sizes[jd], 64), tl = ceil_div(g.sizes[last], 64), n_tiles = outer * tj * tl;
+                    cpy_transposed_pairs<<<(int)(n_tiles < cap ? n_tiles : cap), kThreads, 0, s>>>(
+                        static_cast<const uint16_t*>(src->address), static_cast<uint16_t*>(dst->address), g, jd, tj, tl, n_tiles);
+                    return after_launch("cpy_transposed_pairs");
+                }
+            }
+            const int64_t tiles_j = ceil_div(g.sizes[jd], 32), tiles_l = ceil_div(g.sizes[last], 32);
+            const int64_t tiles = outer * tiles_j * tiles_l;
+            const int tgrid = (int)(tiles < cap ? tiles : cap);
+            switch (esize) {
+                case 1: cpy_transposed<uint8_t><<<tgrid, kThreads, 0, s>>>(static_cast<const uint8_t*>(src->address), static_cast<uint8_t*>(dst->address), g, jd, tiles_j, tiles_l, tiles); break;
+                case 2: cpy_transposed<uint16_t><<<tgrid, kThreads, 0, s>>>(static_cast<const uint16_t*>(src->address), static_cast<uint16_t*>(dst->address), g, jd, tiles_j, tiles_l, tiles); break;
+                case 4: cpy_transposed<uint32_t><<<tgrid, kThreads, 0, s>>>(static_cast<const uint32_t*>(src->address), static_cast<uint32_t*>(dst->address), g, jd, tiles_j, tiles_l, tiles); break;
+                default: cpy_transposed<uint64_t><<<tgrid, kThreads, 0, s>>>(static_cast<const uint64_t*>(src->address), static_cast<uint64_t*>(dst->address), g, jd, tiles_j, tiles_l, tiles); break;
+            }
+            return after_launch("cpy_transposed");
         }
     }
     const int grid = grid_for(g.n);

@@ -142,6 +142,23 @@ def test_unary_strided_source():
     assert_same(tb.repack(dev(x)[::2, 1::3]), oracle.unary("repack", x[::2, 1::3]))
 
 
+@pytest.mark.parametrize("dtype", [torch.int8, torch.float16, torch.bfloat16, torch.float32, torch.float64, torch.int64])
+@pytest.mark.parametrize("shape,perm", [((70, 45), (1, 0)), ((3, 197, 12, 64), (0, 2, 1, 3)), ((5, 33, 100), (0, 2, 1)), ((4, 50, 6, 40), (3, 1, 2, 0)),
+                                        ((2, 3, 64, 96), (0, 1, 3, 2)), ((17, 16), (1, 0)), ((2, 1, 300, 20), (3, 0, 1, 2))])
+def test_repack_of_permuted_views(dtype, shape, perm):
+    """Views that permute dimensions: runs that stay contiguous move as 16-byte words, transposing views go
+    through 32 x 32 shared-memory tiles, everything else element by element; all bit-exact."""
+    x = gen(shape, dtype, 21)
+    v = x.permute(*perm)
+    assert_same(tb.repack(dev(x).permute(*perm)), v.contiguous())
+    assert_same(tb.repack(dev(x).permute(*perm)), oracle.unary("repack", v))
+    out = torch.empty(v.shape, dtype=dtype, device="cuda")
+    tb.cpy(dev(x).permute(*perm), out)
+    assert_same(out, v.contiguous())
+    sliced = dev(x).permute(*perm)[..., 1::2]
+    assert_same(tb.repack(sliced), v[..., 1::2].contiguous())
+
+
 @pytest.mark.parametrize("dtype,value", [(torch.int32, 3), (torch.int8, -7), (torch.float16, 0.125), (torch.bfloat16, 0.125), (torch.float32, 1.7), (torch.float64, -2.5)])
 def test_scale(dtype, value):
     x = gen((31, 64), dtype, 16)
