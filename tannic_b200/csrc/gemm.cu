@@ -419,14 +419,65 @@ using namespace tnb;
 
 extern "C" {
 
+// 16-bit operands whose layout the tensor-core path cannot address (first operand not K-contiguous,
+// second neither K- nor N-contiguous, pitches that are not multiples of 16 bytes) are first copied
+// into dense scratch tensors (the strided copy transposes through shared-memory tiles), when the
+// product is big enough for the tensor cores to pay for that pass.
+static bool tc_addressable(const tn_tensor_t* t, bool second) {
+    const int r = t->rank;
+    if (r < 2) return true;
+    const int64_t s_row = t->strides.sizes[r - 2], s_col = t->strides.sizes[r - 1];
+    const bool rows_ok = s_col == 1 && s_row % 8 == 0;                 // last dimension contiguous
+    const bool cols_ok = second && s_row == 1 && s_col % 8 == 0;       // second operand as [N, K] seen transposed
+    if (!(rows_ok || cols_ok) || (reinterpret_cast<uintptr_t>(t->address) & 15) != 0) return false;
+    for (int d = 0; d < r - 2; ++d)
+        if (t->shape.sizes[d] != 1 && t->strides.sizes[d] % 8 != 0) return false;
+    return true;
+}
+
+static tn_status gemm_entry(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, const tn_scalar_t* scale, tn_stream_t stream) {
+    if (a && b && dst && a->dtype == b->dtype && is_half(a->dtype) && a->rank >= 2 && b->rank >= 2 && dst->rank >= 2 &&
+        a->environment.kind == TN_DEVICE && b->environment.kind == TN_DEVICE && dst->environment.kind == TN_DEVICE) {
+        const bool fix_a = !tc_addressable(a, false), fix_b = !tc_addressable(b, true);
+        const double work = (double)dst->size * (double)a->shape.sizes[a->rank - 1];
+        if ((fix_a || fix_b) && work >= (double)(1 << 24) && a->shape.sizes[a->rank - 1] % 8 == 0 &&
+            (!fix_b || b->shape.sizes[b->rank - 1] % 8 == 0)) {
+            TN_TRY(use_device_of(dst));
+            cudaStream_t s = as_cuda(stream);
+            auto dense_copy = [&](const tn_tensor_t* t, tn_tensor_t* out, void** mem) -> tn_status {
+                *out = *t;
+                int64_t run = 1;
+                for (int d = t->rank - 1; d >= 0; --d) {
+                    out->strides.sizes[d] = run;
+                    run *= (int64_t)t->shape.sizes[d];
+                }
+                out->layout = TN_CONTIGUOUS;
+                TN_TRY(scratch_alloc(mem, (size_t)run * 2, s));
+                out->address = *mem;
+                return tn_cpy(t, out, stream);
+            };
+            tn_tensor_t da, db;
+            void *ma = nullptr, *mb = nullptr;
+            tn_status st = TN_SUCCESS;
+            if (fix_a) st = dense_copy(a, &da, &ma);
+            if (st == TN_SUCCESS && fix_b) st = dense_copy(b, &db, &mb);
+            if (st == TN_SUCCESS) st = gemm_impl(fix_a ? &da : a, fix_b ? &db : b, dst, scale, stream);
+            if (ma) scratch_free(ma, s);
+            if (mb) scratch_free(mb, s);
+            return st;
+        }
+    }
+    return gemm_impl(a, b, dst, scale, stream);
+}
+
 tn_status tn_gemm(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream) {
-    return gemm_impl(a, b, dst, nullptr, stream);
+    return gemm_entry(a, b, dst, nullptr, stream);
 }
 
 tn_status tn_gemm_scaled(const tn_tensor_t* a, const tn_tensor_t* b, const tn_scalar_t* scale, tn_tensor_t* dst,
                          tn_stream_t stream) {
     if (!scale) return fail(TN_ERROR, "null scalar");
-    return gemm_impl(a, b, dst, scale, stream);
+    return gemm_entry(a, b, dst, scale, stream);
 }
 
 tn_status tn_device_errors(unsigned int* count) {

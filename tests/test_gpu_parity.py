@@ -482,6 +482,39 @@ def test_matmul_float32_on_tensor_cores(case):
     assert torch.isinf(out.reshape(-1, out.shape[-1])[0]).all() and torch.equal(torch.isinf(out), torch.isinf(ref))
 
 
+@pytest.mark.parametrize("dtype", HALVES)
+@pytest.mark.parametrize("case", ["a_transposed", "both_transposed", "b_strided", "odd_pitch", "batched_a_transposed"])
+def test_matmul_half_operands_in_any_layout_reach_the_tensor_cores(dtype, case):
+    """tests/cpu/test-matmul.cpp BothTransposed and friends, at sizes where it matters: operands the TMA
+    maps cannot address are copied dense first (tiled transpose), then take the tcgen05 path."""
+    if case == "a_transposed":
+        at, b = gen((512, 264), dtype, 110, -1, 1), gen((512, 320), dtype, 111, -1, 1)
+        a, da, db = at.t(), dev(at).t(), dev(b)
+    elif case == "both_transposed":
+        at, bt = gen((256, 300), dtype, 112, -1, 1), gen((264, 256), dtype, 113, -1, 1)
+        a, b, da, db = at.t(), bt.t(), dev(at).t(), dev(bt).t()
+    elif case == "b_strided":
+        a, b0 = gen((300, 512), dtype, 114, -1, 1), gen((512, 528), dtype, 115, -1, 1)
+        b, da, db = b0[:, ::2], dev(a), dev(b0)[:, ::2]
+    elif case == "odd_pitch":
+        a0, b = gen((300, 1001), dtype, 116, -1, 1), gen((512, 200), dtype, 117, -1, 1)
+        a, da, db = a0[:, :512], dev(a0)[:, :512], dev(b)
+    else:
+        at, b = gen((6, 128, 200), dtype, 118, -1, 1), gen((6, 128, 136), dtype, 119, -1, 1)
+        a, da, db = at.transpose(-1, -2), dev(at).transpose(-1, -2), dev(b)
+    launches = tb.launch_count()
+    got = tb.matmul(da, db)
+    assert tb.launch_count() - launches >= 2, "expected a staging copy in front of the tensor-core GEMM"
+    a3, b3, g3 = (t.reshape((-1,) + tuple(t.shape[-2:])) for t in (a, b, got.cpu()))
+    for i in sorted({0, a3.shape[0] - 1}):
+        # the reference loop reads an operand through max(stride) alone (src/cpu/matmul.cpp:126-176), so it is
+        # given dense copies of views whose inner stride is not 1
+        assert_close(g3[i][:24], oracle.matmul(a3[i][:24].contiguous(), b3[i].contiguous(), acc=oracle.ACC_WIDE))
+    ref = torch.matmul(da.float(), db.float())
+    assert torch.allclose(got.float(), ref, rtol=2e-2, atol=2e-2)
+    assert tb.device_errors() == 0
+
+
 def test_matmul_half_to_float32_result():
     a, w = gen((130, 136), torch.bfloat16, 38, -1, 1), gen((72, 136), torch.bfloat16, 39, -1, 1)
     got = tb.matmul(dev(a), dev(w).t(), out_dtype=A.FLOAT32)
