@@ -548,6 +548,66 @@ tn_status generic_dispatch(int cls, const Plan& plan, const tn_tensor_t* a, cons
     return fail(TN_UNSUPPORTED_DTYPE, "operation needs a floating dtype");
 }
 
+// Dense operands of two different types (float16 + float32, float32 + float64, int32 + float32, ...):
+// eight elements per thread and iteration through 16-byte loads, computed in the wider type like the
+// element-wise kernel, which takes every other mixed case.
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, T (&v)[8]) {
+    constexpr int CHUNKS = 8 * sizeof(T) / 16;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) reinterpret_cast<uint4*>(v)[c] = __ldg(reinterpret_cast<const uint4*>(p) + c);
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const T (&v)[8]) {
+    constexpr int CHUNKS = 8 * sizeof(T) / 16;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) reinterpret_cast<uint4*>(p)[c] = reinterpret_cast<const uint4*>(v)[c];
+}
+
+template <typename TA, typename TB, typename TD, typename C, int OP>
+__global__ void __launch_bounds__(kThreads) ew_flat_mixed(const TA* __restrict__ a, const TB* __restrict__ b, TD* __restrict__ d, int64_t n, Imm imm) {
+    const int64_t groups = n / 8;
+    const int64_t step = (int64_t)gridDim.x * kThreads;
+    for (int64_t g = (int64_t)blockIdx.x * kThreads + threadIdx.x; g < groups; g += step) {
+        alignas(16) TA va[8];
+        alignas(16) TB vb[8];
+        alignas(16) TD vd[8];
+        load8(a + g * 8, va);
+        load8(b + g * 8, vb);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) vd[k] = from_compute<TD, C>(apply_op<OP, false, C>(to_compute<C>(va[k]), to_compute<C>(vb[k]), imm));
+        store8(d + g * 8, vd);
+    }
+    if (blockIdx.x == 0 && threadIdx.x < n - groups * 8) {
+        const int64_t i = groups * 8 + threadIdx.x;
+        d[i] = from_compute<TD, C>(apply_op<OP, false, C>(to_compute<C>(a[i]), to_compute<C>(b[i]), imm));
+    }
+}
+
+template <typename TA, typename TB, typename TD, typename C, int OP>
+tn_status launch_flat_mixed(const void* a, const void* b, void* d, int64_t n, Imm imm, cudaStream_t s) {
+    ew_flat_mixed<TA, TB, TD, C, OP><<<flat_grid(ceil_div(n, 8)), kThreads, 0, s>>>(static_cast<const TA*>(a), static_cast<const TB*>(b),
+                                                                                static_cast<TD*>(d), n, imm);
+    return after_launch("ew_flat_mixed");
+}
+
+// Returns TN_UNSUPPORTED_DTYPE when the triple is not one of the compiled ones (the caller goes on).
+template <int OP>
+tn_status flat_mixed_dispatch(int adt, int bdt, int ddt, const void* a, const void* b, void* d, int64_t n, Imm imm, cudaStream_t s) {
+#define TN_MIXED(A_DT, B_DT, D_DT, TA, TB, TD, C) \
+    if (adt == A_DT && bdt == B_DT && ddt == D_DT) return launch_flat_mixed<TA, TB, TD, C, OP>(a, b, d, n, imm, s);
+    TN_MIXED(TN_FLOAT16, TN_FLOAT32, TN_FLOAT32, __half, float, float, float)
+    TN_MIXED(TN_FLOAT32, TN_FLOAT16, TN_FLOAT32, float, __half, float, float)
+    TN_MIXED(TN_BFLOAT16, TN_FLOAT32, TN_FLOAT32, __nv_bfloat16, float, float, float)
+    TN_MIXED(TN_FLOAT32, TN_BFLOAT16, TN_FLOAT32, float, __nv_bfloat16, float, float)
+    TN_MIXED(TN_FLOAT32, TN_FLOAT64, TN_FLOAT64, float, double, double, double)
+    TN_MIXED(TN_FLOAT64, TN_FLOAT32, TN_FLOAT64, double, float, double, double)
+    TN_MIXED(TN_INT32, TN_FLOAT32, TN_FLOAT32, int32_t, float, float, float)
+    TN_MIXED(TN_FLOAT32, TN_INT32, TN_FLOAT32, float, int32_t, float, float)
+#undef TN_MIXED
+    return TN_UNSUPPORTED_DTYPE;
+}
+
 // Large same-type operations whose operands are strided views of the full result shape (transposes,
 // permutes, strided slices) would take the element-by-element kernel at about 1 TB/s. Copying such an
 // operand dense first (tiled transposes, 16-byte runs: about 3 TB/s) and then taking the vector
@@ -620,6 +680,11 @@ tn_status binary(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, t
             if (mb) scratch_free(mb, s);
             return st;
         }
+    }
+    if (a->dtype != b->dtype && plan.n >= 4096 && is_dense(a) && is_dense(b) && is_dense(dst) && a->size == dst->size && b->size == dst->size &&
+        ((reinterpret_cast<uintptr_t>(a->address) | reinterpret_cast<uintptr_t>(b->address) | reinterpret_cast<uintptr_t>(dst->address)) & 15) == 0) {
+        const tn_status st = flat_mixed_dispatch<OP>(a->dtype, b->dtype, dst->dtype, a->address, b->address, dst->address, plan.n, imm, s);
+        if (st != TN_UNSUPPORTED_DTYPE) return st;
     }
     return generic_dispatch<OP>(compute_class(a->dtype, b->dtype), plan, a, b, dst, imm, s);
 }

@@ -83,6 +83,26 @@ def test_binary_mixed_dtypes(pair, op):
         assert_close(got, want)
 
 
+@pytest.mark.parametrize("pair", [(torch.float16, torch.float32), (torch.float32, torch.float16), (torch.bfloat16, torch.float32),
+                                  (torch.float32, torch.bfloat16), (torch.float32, torch.float64), (torch.float64, torch.float32),
+                                  (torch.int32, torch.float32), (torch.float32, torch.int32)])
+@pytest.mark.parametrize("op", ["add", "sub", "mul", "pow"])
+def test_binary_mixed_dtypes_dense_vector_path(pair, op):
+    """Dense operands of two types take the eight-elements-per-thread kernel from 4096 elements on; a length
+    that is not a multiple of eight exercises its tail. Same arithmetic as the element-wise kernel."""
+    lo, hi = (0.1, 3.0) if op == "pow" else (-4.0, 4.0)
+    a, b = gen((37, 333), pair[0], 5, lo, hi), gen((37, 333), pair[1], 6, lo, hi)
+    if op == "pow" and torch.int32 in pair:
+        a, b = a.abs() + 1, (b.abs() % 3) + 1
+    want = oracle.binary(op, a, b)
+    got = getattr(tb, op)(dev(a), dev(b))
+    assert got.dtype == want.dtype
+    if op == "pow":
+        assert_close(got, want, tol=(1e-4, 1e-4) if want.dtype == torch.float32 else None)
+    else:
+        assert_same(got, want)
+
+
 def test_binary_half_with_int_writes_result_dtype():
     """The reference's (float16, int32) entry writes float32 into a float16-sized buffer
     (src/cpu/ops-binary.cpp:199-206); the device path writes exactly dst->dtype."""
