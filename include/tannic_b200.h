@@ -120,20 +120,28 @@ tn_status tn_device_count(int* count);
 tn_status tn_set_device(int id);
 
 /* reference: cuda::Streams::pop / put behind tannic::pop_stream / put_stream,
- * src/cuda/streams.cu:23-38, src/bindings.cpp:22-42. One non-blocking stream per device is
- * handed out in LIFO order, so successive ops of one thread are ordered; the pool is
- * mutex-protected. */
+ * src/cuda/streams.cu:23-38, src/bindings.cpp:22-42. Streams are handed out in LIFO order, so
+ * successive ops of one thread land on one stream and are ordered; they are created like the
+ * reference's (cudaStreamCreate: ordered with the legacy default stream); the pool is
+ * mutex-protected. tn_stream_synchronize returns TN_ERROR (with text) when a thread block gave up
+ * on a bounded device-side wait since the last synchronising call on that device. */
 tn_status tn_stream_pop(const tn_device_t* device, tn_stream_t* stream);
 tn_status tn_stream_put(const tn_device_t* device, tn_stream_t stream);
 tn_status tn_stream_synchronize(tn_stream_t stream);
 
-/* reference: cuda::allocate / cuda::deallocate, src/cuda/mem.cu:19-36. Stream-ordered pool
- * allocation (cudaMallocAsync on the device's pooled stream, release threshold = unlimited so
- * freed blocks are reused without returning to the driver). */
+/* reference: cuda::allocate / cuda::deallocate, src/cuda/mem.cu:19-36. Stream-ordered allocation
+ * from a memory pool that belongs to this library (one per device, release threshold = unlimited so
+ * freed blocks are reused without returning to the driver; the process-wide default pool is left
+ * alone). Allocation and release are ordered on the device's pool stream, and through it with the
+ * legacy default stream; a caller that uses the memory on another non-blocking stream orders that
+ * stream itself. A failed allocation returns TN_ERROR with *address = NULL; the process goes on. */
 tn_status tn_allocate(const tn_device_t* device, size_t nbytes, void** address);
 tn_status tn_deallocate(const tn_device_t* device, void* address);
 
-/* reference: cuda::copyFromHost / copyDeviceToHost / compareFromHost, src/cuda/mem.cu:38-65 */
+/* reference: cuda::copyFromHost / copyDeviceToHost / compareFromHost, src/cuda/mem.cu:38-65.
+ * tn_copy_from_host returns once the copy is queued on the pool stream: a pageable source may be
+ * reused at once, a pinned one must stay unchanged until that stream has passed the copy.
+ * tn_copy_to_host waits for the copy and, like tn_stream_synchronize, reports device-side aborts. */
 tn_status tn_copy_from_host(const tn_device_t* device, const void* host, void* dev, size_t nbytes);
 tn_status tn_copy_to_host(const tn_device_t* device, const void* dev, void* host, size_t nbytes);
 tn_status tn_compare_from_host(const tn_device_t* device, const void* host, const void* dev,
@@ -151,6 +159,15 @@ tn_status tn_copy(const tn_tensor_t* src, tn_tensor_t* dst, size_t nbytes, tn_st
  * "not supported yet" (src/resources.cpp:24-38). */
 tn_status tn_host_allocate_pinned(size_t nbytes, void** address);
 tn_status tn_host_free_pinned(void* address);
+/* Host-memory placement for the transfer path. No reference counterpart (its `Mesh` of devices is a
+ * TODO, include/tannic/resources.hpp:194-197, and nothing there knows which host memory node a GPU
+ * hangs off). tn_device_numa_node reports the node of the device's PCIe function (-1 where the
+ * platform names none); tn_host_allocate_pinned_near pins memory preferably on that node (freed with
+ * tn_host_free_pinned); tn_bind_thread_near restricts the calling thread to that node's CPUs (within
+ * the CPUs the process may use). All three succeed without effect where no node is known. */
+tn_status tn_device_numa_node(const tn_device_t* device, int* node);
+tn_status tn_host_allocate_pinned_near(const tn_device_t* device, size_t nbytes, void** address);
+tn_status tn_bind_thread_near(const tn_device_t* device, int* node);
 
 /* ------------------------------------------------------------------ elementwise ------ */
 
@@ -217,6 +234,17 @@ tn_status tn_eltwise_program(const tn_tensor_t* const* inputs, int n_inputs,
                              const tn_eltwise_node_t* nodes, int n_nodes,
                              tn_tensor_t* dst, tn_stream_t stream);
 
+/* The same program over HOST tensors: dense inputs and a dense result in host memory (pinned memory
+ * from tn_host_allocate_pinned[_near] makes the copies asynchronous), evaluated on `device`. The rows
+ * (leading extent of dst) are cut into `chunks` pieces (0 = 8) and the copy-in of piece c + 1, the
+ * kernel of piece c and the copy-out of piece c - 1 overlap on three private streams; inputs smaller
+ * than the result (a broadcast row) are copied whole first. Returns when dst is complete. Device
+ * staging memory is kept between calls and only grows. Replaces the reference's sequence of
+ * Tensor::to(Device) -> one launch per node -> read-back, each a synchronous cudaMemcpy
+ * (src/tensor.cpp:34-136, src/cuda/mem.cu:54-90). Calls are serialised inside the library. */
+tn_status tn_eltwise_program_host(const tn_device_t* device, const tn_tensor_t* const* inputs, int n_inputs,
+                                  const tn_eltwise_node_t* nodes, int n_nodes, tn_tensor_t* dst, int chunks);
+
 /* ------------------------------------------------------------------ contractions ----- */
 
 /* reference: cuda::gemm, src/cuda/matmul.cu:189-191 (CPU twin src/cpu/matmul.cpp:254-256).
@@ -232,6 +260,19 @@ tn_status tn_gemm(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, 
  * `matmul(Q, K^T) * 0.125` (src/transformations.cpp:33-39 then src/operations.cpp:40-43). */
 tn_status tn_gemm_scaled(const tn_tensor_t* a, const tn_tensor_t* b, const tn_scalar_t* scale,
                          tn_tensor_t* dst, tn_stream_t stream);
+
+/* The scores-then-statistics path in one kernel: dst = matmul(a, b) [* scale] as above (scale may be
+ * NULL), and for every row of dst (its last axis) the maximum, the sum and the index of the first
+ * maximum, taken from the rounded result while the tensor-core epilogue still holds the row.
+ * Replaces gemm + scale + three reductions that would each re-read dst
+ * (src/transformations.cpp:33-39, src/operations.cpp:40-43, src/reductions.cpp:23-53). max_out and
+ * sum_out have dst's dtype, argmax_out is int64; each has one element per row of dst and may be
+ * NULL. Semantics are those of tn_max / tn_argsum / tn_argmax applied to dst. Results that the
+ * fused epilogue does not cover (more than 256 columns, a padded row pitch, non-16-bit types) are
+ * computed by the product followed by one tn_reduce_stats pass. */
+tn_status tn_gemm_scaled_stats(const tn_tensor_t* a, const tn_tensor_t* b, const tn_scalar_t* scale,
+                               tn_tensor_t* dst, tn_tensor_t* max_out, tn_tensor_t* sum_out,
+                               tn_tensor_t* argmax_out, tn_stream_t stream);
 
 /* reference: cuda::conv2d (two overloads), src/cuda/conv2d.cu:216-222 (CPU twin
  * src/cpu/conv2d.cpp:257-265). NCHW cross-correlation, zero padding, floor output size,
@@ -316,6 +357,13 @@ tn_status tn_allclose(const tn_tensor_t* a, const tn_tensor_t* b, tn_stream_t st
 /* Number of CTAs (tensor-core and staged-reduction kernels) that gave up on a bounded wait since load (0 in a
  * healthy run); synchronises the device. The reference has no device-side waits to bound. */
 tn_status tn_device_errors(unsigned int* count);
+
+/* Failure-detection self-test, no reference counterpart: launches one warp that waits, with the same
+ * bounded wait the tensor-core kernels use, on a barrier nothing ever completes. The wait runs out
+ * after `polls` polls (about 64 ns each, capped at the kernels' own limit), the kernel returns
+ * normally and the abort counter rises by one, so tn_device_errors() and the next synchronising
+ * call report it. Nothing faults or hangs. */
+tn_status tn_selftest_bounded_wait(const tn_device_t* device, tn_stream_t stream, unsigned int polls);
 
 /* Number of kernels this library has launched on the calling process since load (all threads).
  * Used by the benchmark to count launches inside its timed region. */

@@ -6,7 +6,8 @@
                  from its sources (None when it was never built on this machine).
 
 Only tests/, `__graft_entry__.smoke()` and the CPU-baseline leg of bench.py may import this
-package; the product (tannic_b200) never does.
+package; the product (tannic_b200) never does, and this package imports nothing from the product:
+its records and front-end rules are its own (`_records.py`).
 """
 from __future__ import annotations
 
@@ -16,7 +17,7 @@ from pathlib import Path
 
 import torch
 
-from tannic_b200 import _abi as A
+from . import _records as A
 
 HERE = Path(__file__).resolve().parent
 PORT_PATH = HERE / "liboracle.so"
@@ -58,6 +59,7 @@ def port() -> C.CDLL:
         lib.orc_triangular.argtypes = [_TP, _TP, C.c_int, C.c_int]
         lib.orc_complex_pair.argtypes = [_TP, _TP, _TP, C.c_int]
         lib.orc_fill.argtypes = [C.c_void_p, C.c_int, C.c_size_t, C.c_uint64, C.c_int, C.c_double, C.c_double]
+        lib.orc_fill_range.argtypes = [C.c_void_p, C.c_int, C.c_uint64, C.c_size_t, C.c_uint64, C.c_int, C.c_double, C.c_double]
         _port = lib
     return _port
 
@@ -93,7 +95,8 @@ def ref():
 # ---------------------------------------------------------------------------------------
 # Convenience layer over CPU torch tensors (torch is used as a typed host buffer only).
 
-from tannic_b200.ops import TN_TO_TORCH, TORCH_TO_TN, broadcast_shape, desc, _matmul_dtype  # noqa: E402
+from ._records import TN_TO_TORCH, TORCH_TO_TN, broadcast_shape, desc  # noqa: E402
+from ._records import matmul_dtype as _matmul_dtype  # noqa: E402
 
 
 class OracleError(RuntimeError):
@@ -107,10 +110,29 @@ def _ok(status):
         raise OracleError(status)
 
 
-def fill(shape, dtype: torch.dtype, seed: int, kind: str = "uniform", lo: float = 0.0, hi: float = 1.0) -> torch.Tensor:
-    """Seeded host tensor: 'uniform' in [lo, hi) (integers: inclusive range), 'normal'(mean=lo, std=hi)."""
-    t = torch.empty(tuple(shape), dtype=dtype)
-    _ok(port().orc_fill(t.data_ptr(), TORCH_TO_TN[dtype], t.numel(), seed, 0 if kind == "uniform" else 1, lo, hi))
+def fill(shape, dtype: torch.dtype, seed: int, kind: str = "uniform", lo: float = 0.0, hi: float = 1.0,
+         first: int = 0, threads: int = 1, pinned: bool = False) -> torch.Tensor:
+    """Seeded host tensor: 'uniform' in [lo, hi) (integers: inclusive range), 'normal'(mean=lo, std=hi).
+    The generator is counter based (element i depends on (seed, i) only): `first` is the counter of
+    the tensor's first element, so a shard of a larger tensor is generated without the rest, and
+    `threads` splits the work over host threads without changing a bit of the result."""
+    t = torch.empty(tuple(shape), dtype=dtype, pin_memory=pinned)
+    n, tn, k = t.numel(), TORCH_TO_TN[dtype], 0 if kind == "uniform" else 1
+    es = t.element_size()
+    if threads <= 1 or n < (1 << 16):
+        _ok(port().orc_fill_range(t.data_ptr(), tn, first, n, seed, k, lo, hi))
+        return t
+    from concurrent.futures import ThreadPoolExecutor
+    bounds = [(n * i) // threads for i in range(threads + 1)]
+    lib = port()
+
+    def part(i):
+        a, b = bounds[i], bounds[i + 1]
+        return lib.orc_fill_range(t.data_ptr() + a * es, tn, first + a, b - a, seed, k, lo, hi)
+
+    with ThreadPoolExecutor(max_workers=threads) as pool:
+        for status in pool.map(part, range(threads)):
+            _ok(status)
     return t
 
 

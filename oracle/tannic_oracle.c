@@ -767,15 +767,18 @@ static uint64_t splitmix64(uint64_t x) {
 static double unit(uint64_t seed, uint64_t i) { return (double)(splitmix64(seed * 0xD1342543DE82EF95ull + i) >> 11) * (1.0 / 9007199254740992.0); }
 
 /* kind 0: uniform [lo, hi); kind 1: normal(mean = lo, std = hi) by Box-Muller; integers:
- * uniform integers in [lo, hi]. Writes `n` elements of dtype `dt`, half types rounded RNE. */
-tn_status orc_fill(void* dst, int dt, size_t n, uint64_t seed, int kind, double lo, double hi) {
+ * uniform integers in [lo, hi]. Writes `n` elements of dtype `dt`, half types rounded RNE.
+ * Element k of the output carries the value of counter `first + k`, so a slice of a larger
+ * tensor can be generated on its own (a rank's shard; a chunk per host thread). */
+tn_status orc_fill_range(void* dst, int dt, uint64_t first, size_t n, uint64_t seed, int kind, double lo, double hi) {
     if (!is_numeric(dt)) return TN_UNSUPPORTED_DTYPE;
-    for (size_t i = 0; i < n; ++i) {
+    for (size_t k = 0; k < n; ++k) {
+        const uint64_t i = first + k;
         double v;
         if (is_int(dt)) {
             const double span = hi - lo + 1.0;
             v = lo + floor(unit(seed, i) * span);
-            store_i64(dst, dt, (int64_t)i, (int64_t)v);
+            store_i64(dst, dt, (int64_t)k, (int64_t)v);
             continue;
         }
         if (kind == 0) v = lo + (hi - lo) * unit(seed, i);
@@ -784,8 +787,12 @@ tn_status orc_fill(void* dst, int dt, size_t n, uint64_t seed, int kind, double 
             if (u1 < 1e-300) u1 = 1e-300;
             v = lo + hi * sqrt(-2.0 * log(u1)) * cos(6.283185307179586 * u2);
         }
-        if (dt == TN_FLOAT64) ((double*)dst)[i] = v;
-        else store_f32(dst, dt, (int64_t)i, (float)v);
+        if (dt == TN_FLOAT64) ((double*)dst)[k] = v;
+        else store_f32(dst, dt, (int64_t)k, (float)v);
     }
     return TN_SUCCESS;
+}
+
+tn_status orc_fill(void* dst, int dt, size_t n, uint64_t seed, int kind, double lo, double hi) {
+    return orc_fill_range(dst, dt, 0, n, seed, kind, lo, hi);
 }

@@ -108,6 +108,11 @@ PROTOTYPES = {
     "tn_copy": [_TP, _TP, C.c_size_t, StreamT],
     "tn_host_allocate_pinned": [C.c_size_t, C.POINTER(C.c_void_p)],
     "tn_host_free_pinned": [C.c_void_p],
+    "tn_device_numa_node": [C.POINTER(DeviceT), C.POINTER(C.c_int)],
+    "tn_host_allocate_pinned_near": [C.POINTER(DeviceT), C.c_size_t, C.POINTER(C.c_void_p)],
+    "tn_bind_thread_near": [C.POINTER(DeviceT), C.POINTER(C.c_int)],
+    "tn_eltwise_program_host": [C.POINTER(DeviceT), C.POINTER(_TP), C.c_int, C.POINTER(EltwiseNode), C.c_int, _TP, C.c_int],
+    "tn_gemm_scaled_stats": [_TP, _TP, C.POINTER(ScalarT), _TP, _TP, _TP, _TP, StreamT],
     "tn_rsqrt": [_TP, _TP, StreamT, C.c_float],
     "tn_scale": [_TP, C.POINTER(ScalarT), _TP, StreamT],
     "tn_eltwise_program": [C.POINTER(_TP), C.c_int, C.POINTER(EltwiseNode), C.c_int, _TP, StreamT],
@@ -128,6 +133,7 @@ PROTOTYPES = {
     "tn_cpy": [_TP, _TP, StreamT],
     "tn_allclose": [_TP, _TP, StreamT, C.c_double, C.c_double, C.POINTER(C.c_int)],
     "tn_device_errors": [C.POINTER(C.c_uint)],
+    "tn_selftest_bounded_wait": [C.POINTER(DeviceT), StreamT, C.c_uint],
     "tn_launch_count": [],
 }
 for _n in _UNARY:

@@ -140,4 +140,10 @@ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 tn_status scratch_alloc(void** ptr, size_t nbytes, cudaStream_t stream);
 tn_status scratch_free(void* ptr, cudaStream_t stream);
 
+// Called by the entry points that synchronise with the device (tn_stream_synchronize,
+// tn_copy_to_host, tn_allclose) after the device is idle: if a CTA gave up on a bounded wait since
+// the last such call on the current device, the results it owed were never written, so the call
+// reports TN_ERROR with a message instead of SUCCESS.
+tn_status surface_device_aborts();
+
 }  // namespace tnb

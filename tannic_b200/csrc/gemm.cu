@@ -8,6 +8,22 @@ namespace tnb {
 bool read_host_scalar(const tn_scalar_t* sc, double* f, int64_t* i);
 tn_status tc_abort_count(unsigned int* count);
 tn_status reduce_abort_count(unsigned int* count);
+tn_status tc_wait_probe(cudaStream_t stream, unsigned int polls);
+
+tn_status surface_device_aborts() {
+    static std::atomic<unsigned int> seen[64];
+    int dev = 0;
+    TN_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return TN_SUCCESS;
+    unsigned int tc = 0, red = 0;
+    TN_TRY(tc_abort_count(&tc));
+    TN_TRY(reduce_abort_count(&red));
+    const unsigned int total = tc + red, before = seen[dev].exchange(total);
+    if (total > before)
+        return fail(TN_ERROR, "%u thread block(s) on device %d gave up on a bounded device-side wait since the last synchronising call; "
+                              "results written by those launches are incomplete", total - before, dev);
+    return TN_SUCCESS;
+}
 
 namespace {
 
@@ -193,8 +209,16 @@ __global__ void __launch_bounds__(256) split_n_major(const float* __restrict__ b
     }
 }
 
+// Row statistics of the result requested together with the product (tn_gemm_scaled_stats).
+struct StatsRequest {
+    tn_tensor_t* max = nullptr;
+    tn_tensor_t* sum = nullptr;
+    tn_tensor_t* argmax = nullptr;
+    bool any() const { return max || sum || argmax; }
+};
+
 tn_status gemm_impl(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, const tn_scalar_t* scale,
-                    tn_stream_t stream) {
+                    tn_stream_t stream, const StatsRequest* stats = nullptr, bool* stats_done = nullptr) {
     if (!a || !b || !dst) return fail(TN_ERROR, "null tensor");
     if (!pair_supported(a->dtype, b->dtype) || !is_numeric(dst->dtype))
         return fail(TN_UNSUPPORTED_DTYPE, "gemm: dtype pair (%d, %d) -> %d unsupported", (int)a->dtype, (int)b->dtype,
@@ -354,21 +378,7 @@ tn_status gemm_impl(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst
     //      row-major result, batch dims that collapse to one stride per operand.
     if (a->dtype == b->dtype && is_half(a->dtype) && (dst->dtype == a->dtype || dst->dtype == TN_FLOAT32) &&
         g.a_sk == 1 && g.d_sn == 1 && (g.b_sk == 1 || g.b_sn == 1) && g.K > 0) {
-        // collapse the batch dims of each operand into (count, stride); possible when walking
-        // them in row-major order advances by a constant stride, or the operand is shared
-        auto collapse = [&](const int64_t* bs, int64_t* stride) {
-            bool any = false, all = true;
-            int64_t expect = 0;
-            for (int dim = g.nbatch - 1; dim >= 0; --dim) {
-                if (g.bsize[dim] == 1) continue;
-                if (bs[dim] == 0) { all = false; continue; }
-                if (!any) { expect = bs[dim]; *stride = bs[dim]; any = true; }
-                if (bs[dim] != expect) return false;
-                expect = bs[dim] * g.bsize[dim];
-            }
-            if (!any) { *stride = 0; return true; }  // shared by every batch
-            return all;                                // partial broadcast does not collapse
-        };
+        auto& collapse = collapse_batches;
         int64_t sa = 0, sb = 0, sd = 0;
         if (collapse(g.a_bs, &sa) && collapse(g.b_bs, &sb) && collapse(g.d_bs, &sd) && (sd != 0 || g.batches == 1)) {
             TcGemm p;
@@ -396,7 +406,15 @@ tn_status gemm_impl(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst
             }
             p.has_scale = g.has_scale != 0;
             p.scale = (float)g.scale_f;
+            if (stats && stats->any() && tc_gemm_can_fuse_stats(p)) {
+                // the epilogue keeps each row's maximum, sum and argmax while it drains the row
+                p.stat_max = stats->max ? stats->max->address : nullptr;
+                p.stat_sum = stats->sum ? stats->sum->address : nullptr;
+                p.stat_argmax = stats->argmax ? static_cast<int64_t*>(stats->argmax->address) : nullptr;
+                if (stats_done) *stats_done = true;
+            }
             if (tc_gemm_eligible(p)) return tc_gemm(p, s);
+            if (stats_done) *stats_done = false;
         }
     }
 
@@ -435,7 +453,8 @@ static bool tc_addressable(const tn_tensor_t* t, bool second) {
     return true;
 }
 
-static tn_status gemm_entry(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, const tn_scalar_t* scale, tn_stream_t stream) {
+static tn_status gemm_entry(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, const tn_scalar_t* scale, tn_stream_t stream,
+                            const StatsRequest* stats = nullptr, bool* stats_done = nullptr) {
     if (a && b && dst && a->dtype == b->dtype && is_half(a->dtype) && a->rank >= 2 && b->rank >= 2 && dst->rank >= 2 &&
         a->environment.kind == TN_DEVICE && b->environment.kind == TN_DEVICE && dst->environment.kind == TN_DEVICE) {
         const bool fix_a = !tc_addressable(a, false), fix_b = !tc_addressable(b, true);
@@ -461,13 +480,13 @@ static tn_status gemm_entry(const tn_tensor_t* a, const tn_tensor_t* b, tn_tenso
             tn_status st = TN_SUCCESS;
             if (fix_a) st = dense_copy(a, &da, &ma);
             if (st == TN_SUCCESS && fix_b) st = dense_copy(b, &db, &mb);
-            if (st == TN_SUCCESS) st = gemm_impl(fix_a ? &da : a, fix_b ? &db : b, dst, scale, stream);
+            if (st == TN_SUCCESS) st = gemm_impl(fix_a ? &da : a, fix_b ? &db : b, dst, scale, stream, stats, stats_done);
             if (ma) scratch_free(ma, s);
             if (mb) scratch_free(mb, s);
             return st;
         }
     }
-    return gemm_impl(a, b, dst, scale, stream);
+    return gemm_impl(a, b, dst, scale, stream, stats, stats_done);
 }
 
 tn_status tn_gemm(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream) {
@@ -480,6 +499,39 @@ tn_status tn_gemm_scaled(const tn_tensor_t* a, const tn_tensor_t* b, const tn_sc
     return gemm_entry(a, b, dst, scale, stream);
 }
 
+tn_status tn_gemm_scaled_stats(const tn_tensor_t* a, const tn_tensor_t* b, const tn_scalar_t* scale, tn_tensor_t* dst,
+                               tn_tensor_t* max_out, tn_tensor_t* sum_out, tn_tensor_t* argmax_out, tn_stream_t stream) {
+    if (!dst) return fail(TN_ERROR, "null tensor");
+    if (!max_out && !sum_out && !argmax_out) return fail(TN_ERROR, "gemm_scaled_stats: no statistic requested");
+    if (dst->rank < 2) return fail(TN_ERROR, "gemm_scaled_stats: the result must have rank >= 2");
+    const size_t rows = dst->shape.sizes[dst->rank - 1] ? dst->size / dst->shape.sizes[dst->rank - 1] : 0;
+    auto check_out = [&](const tn_tensor_t* t, int want_dtype, const char* what) -> tn_status {
+        if (!t) return TN_SUCCESS;
+        if ((int)t->dtype != want_dtype) return fail(TN_UNSUPPORTED_DTYPE, "gemm_scaled_stats: %s has dtype %d, expected %d", what, (int)t->dtype, want_dtype);
+        if (t->size != rows) return fail(TN_ERROR, "gemm_scaled_stats: %s has %zu elements, the result has %zu rows", what, t->size, rows);
+        if (t->environment.kind != TN_DEVICE || t->environment.resource.device.id != dst->environment.resource.device.id)
+            return fail(TN_INCOMPATIBLE_DEVICES, "operands must live on one device");
+        int64_t expect = 1;
+        for (int d = t->rank - 1; d >= 0; --d) {
+            if (t->shape.sizes[d] != 1 && t->strides.sizes[d] != expect) return fail(TN_ERROR, "gemm_scaled_stats: %s must be dense", what);
+            expect *= (int64_t)t->shape.sizes[d];
+        }
+        return TN_SUCCESS;
+    };
+    TN_TRY(check_out(max_out, (int)dst->dtype, "max"));
+    TN_TRY(check_out(sum_out, (int)dst->dtype, "sum"));
+    TN_TRY(check_out(argmax_out, TN_INT64, "argmax"));
+    StatsRequest request;
+    request.max = max_out;
+    request.sum = sum_out;
+    request.argmax = argmax_out;
+    bool fused = false;
+    TN_TRY(gemm_entry(a, b, dst, scale, stream, &request, &fused));
+    if (fused) return TN_SUCCESS;
+    // shapes the fused epilogue does not cover: the statistics take their own pass over the result
+    return tn_reduce_stats(dst, max_out, sum_out, argmax_out, stream, (uint8_t)(dst->rank - 1));
+}
+
 tn_status tn_device_errors(unsigned int* count) {
     if (!count) return fail(TN_ERROR, "null count");
     unsigned int tc = 0, red = 0;
@@ -487,6 +539,12 @@ tn_status tn_device_errors(unsigned int* count) {
     TN_TRY(reduce_abort_count(&red));
     *count = tc + red;
     return TN_SUCCESS;
+}
+
+tn_status tn_selftest_bounded_wait(const tn_device_t* device, tn_stream_t stream, unsigned int polls) {
+    if (!device) return fail(TN_ERROR, "null device");
+    TN_TRY(use_device(device->id));
+    return tc_wait_probe(as_cuda(stream), polls);
 }
 
 }  // extern "C"

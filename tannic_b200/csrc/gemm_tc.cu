@@ -43,6 +43,7 @@ constexpr int BN = 256;
 constexpr int BK = 64;            // 64 x 2 bytes = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int STAGES = 4;
+constexpr int PACKED_STAGES = 2;                 // operand stages of the packed-epilogue variant
 constexpr int kEpilogueWarps = 8;                // two per TMEM lane quarter, interleaved over 32-column chunks
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr uint32_t A_BYTES = BM * BK * 2;        // 16 KiB
@@ -53,6 +54,10 @@ constexpr int STAGING_PITCH = 17;                // words per staged row of the 
 constexpr uint32_t STAGING_WARP_BYTES = 4096;    // per epilogue warp: two 2 KiB boxes for TMA stores (or one 32 x 80 B block)
 constexpr uint32_t STAGING_BYTES = kEpilogueWarps * STAGING_WARP_BYTES;
 constexpr uint32_t SMEM_BYTES = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + STAGING_BYTES + 256 /*barriers*/;
+// packed epilogue: a warp stages 32 rows of up to BN 16-bit columns plus the offset from a 16-byte boundary
+constexpr uint32_t PACK_STAGE_MAX = (32 * BN * 2 + 16 + 127) & ~127u;
+constexpr uint32_t PACKED_SMEM_MAX = 1024 + PACKED_STAGES * STAGE_BYTES + kEpilogueWarps * PACK_STAGE_MAX + 256;
+static_assert(PACKED_SMEM_MAX <= 232448, "packed epilogue exceeds the shared memory of an SM");
 
 constexpr uint32_t kSpinFast = 2048;      // polls without sleeping
 constexpr uint32_t kSpinLimit = 1u << 20; // then ~64 ns sleeps: gives up after roughly 0.1 s
@@ -83,8 +88,8 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 // Bounded wait. Returns false when the CTA is aborting (this wait or another one ran out).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t limit = kSpinLimit) {
+    for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_test(bar, parity)) return true;
         if (it >= kSpinFast) {
             if (*abort_flag) return false;
@@ -114,6 +119,12 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
     asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
         ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+// Untiled copy of a 16-byte-aligned shared-memory range to a 16-byte-aligned global range.
+__device__ __forceinline__ void bulk_store_linear(void* dst, uint32_t src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+        ::"l"(reinterpret_cast<uint64_t>(dst)), "r"(src), "r"(bytes)
         : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
@@ -199,6 +210,10 @@ struct KernelArgs {
     // convolution geometry
     int cblocks, kw, pad_h, pad_w, hbox, str_h;
     int epi_warps;             // 4 or 8 epilogue warps take part (the others exit at once)
+    uint32_t pack_stage_bytes; // packed epilogue: bytes of one warp's staging block (multiple of 128)
+    void* stat_max;            // fused row statistics (packed epilogue only); each may be null
+    void* stat_sum;
+    int64_t* stat_argmax;
 };
 
 // Tiles are walked in groups of 16 row-tiles so that the CTAs running at the same time share
@@ -433,6 +448,213 @@ __device__ __forceinline__ void drain_tile(const EpilogueTile& e, uint8_t* stage
     }
 }
 
+// ---- packed epilogue -------------------------------------------------------------------
+// A result whose rows are NOT a multiple of 16 bytes (197 bfloat16 columns, say) defeats both the
+// TMA boxes and 16-byte row stores. But when the rows follow one another without a gap (pitch ==
+// columns) and one tile spans all columns, the 32 rows a warp drains are ONE contiguous byte range
+// of global memory. The warp builds that range in shared memory exactly as it will lie in global
+// memory, at the same offset from a 16-byte boundary, and hands its 16-byte-aligned middle to the
+// copy engine as a single untiled bulk store; the up to seven elements before and after the
+// aligned part are written with 2-byte stores. One warp drains all column chunks of its 32 rows,
+// so nothing is shared between warps: warps 2-5 take the tiles in accumulator 0, warps 6-9 those
+// in accumulator 1.
+
+// Both halves of a packed pair as float32.
+template <typename OutT> __device__ __forceinline__ void unpack_pair(uint32_t w, float& lo, float& hi);
+template <> __device__ __forceinline__ void unpack_pair<__nv_bfloat16>(uint32_t w, float& lo, float& hi) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xFFFF0000u);
+}
+template <> __device__ __forceinline__ void unpack_pair<__half>(uint32_t w, float& lo, float& hi) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    lo = f.x;
+    hi = f.y;
+}
+template <typename OutT> __device__ __forceinline__ uint32_t max_pair(uint32_t a, uint32_t b);
+template <> __device__ __forceinline__ uint32_t max_pair<__nv_bfloat16>(uint32_t a, uint32_t b) {
+    const __nv_bfloat162 m = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&m);
+}
+template <> __device__ __forceinline__ uint32_t max_pair<__half>(uint32_t a, uint32_t b) {
+    const __half2 m = __hmax2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&m);
+}
+
+// Row statistics of the rounded results, kept by the lane that drains the row: the sum in float32,
+// and for the maximum of the even and of the odd columns its value and the 32-column chunk in which
+// it first appeared (a strict, ordered comparison: a NaN is never selected, the first of equal
+// values stays). The column itself is looked up once, after the last chunk.
+struct RowStats {
+    float sum0, sum1;
+    float max_even, max_odd;
+    int chunk_even, chunk_odd;
+    __device__ __forceinline__ void init() {
+        sum0 = sum1 = 0.0f;
+        max_even = max_odd = -INFINITY;
+        chunk_even = chunk_odd = -1;
+    }
+    template <typename OutT>
+    __device__ __forceinline__ void update(const uint32_t (&w)[16], int ncols, int chunk) {
+        float lo, hi;
+        float best_even = -INFINITY, best_odd = -INFINITY;
+        if (ncols == 32) {  // warp-uniform
+            uint32_t m[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) m[j] = max_pair<OutT>(w[j], w[j + 8]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) m[j] = max_pair<OutT>(m[j], m[j + 4]);
+            m[0] = max_pair<OutT>(max_pair<OutT>(m[0], m[2]), max_pair<OutT>(m[1], m[3]));
+            unpack_pair<OutT>(m[0], best_even, best_odd);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                unpack_pair<OutT>(w[j], lo, hi);
+                sum0 += lo;
+                sum1 += hi;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                unpack_pair<OutT>(w[j], lo, hi);
+                if (2 * j < ncols) {
+                    sum0 += lo;
+                    best_even = fmaxf(best_even, lo);
+                }
+                if (2 * j + 1 < ncols) {
+                    sum1 += hi;
+                    best_odd = fmaxf(best_odd, hi);
+                }
+            }
+        }
+        if (best_even > max_even) {
+            max_even = best_even;
+            chunk_even = chunk;
+        }
+        if (best_odd > max_odd) {
+            max_odd = best_odd;
+            chunk_odd = chunk;
+        }
+    }
+};
+
+// Stages 32 consecutive columns of this lane's row at `dst` (2-byte aligned). Full chunks are
+// written as aligned 32-bit words: a lane whose row starts on an odd element shifts its packed
+// pairs by one element (funnel shift) and writes the first and last element on their own.
+template <typename OutT, bool SCALE, bool STATS>
+__device__ __forceinline__ void stage_packed_chunk(const uint32_t (&v)[32], uint8_t* dst, int ncols, bool has_bias, float bias, uint32_t scale2,
+                                                   RowStats& stats, int chunk) {
+    uint32_t w[16];
+    if (has_bias) {  // warp-uniform
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            w[j] = finish_pair<OutT, SCALE>(__uint_as_float(v[2 * j]) + bias, __uint_as_float(v[2 * j + 1]) + bias, scale2);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) w[j] = finish_pair<OutT, SCALE>(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), scale2);
+    }
+    if constexpr (STATS) stats.template update<OutT>(w, ncols, chunk);
+    if (ncols == 32) {  // warp-uniform
+        const uint32_t odd = (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(dst)) >> 1) & 1u;
+        uint32_t* words = reinterpret_cast<uint32_t*>(dst + 2 * odd);
+        const uint32_t shift = odd << 4;
+#pragma unroll
+        for (int j = 0; j < 15; ++j) words[j] = __funnelshift_r(w[j], w[j + 1], shift);
+        if (odd) {
+            *reinterpret_cast<uint16_t*>(dst) = static_cast<uint16_t>(w[0] & 0xFFFFu);
+            *reinterpret_cast<uint16_t*>(dst + 62) = static_cast<uint16_t>(w[15] >> 16);
+        } else {
+            words[15] = w[15];
+        }
+    } else {
+        uint16_t* out = reinterpret_cast<uint16_t*>(dst);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            if (2 * j < ncols) out[2 * j] = static_cast<uint16_t>(w[j] & 0xFFFFu);
+            if (2 * j + 1 < ncols) out[2 * j + 1] = static_cast<uint16_t>(w[j] >> 16);
+        }
+    }
+}
+
+// Where the row statistics of a fused call go (any pointer may be null); `row` indexes all rows of
+// all batches.
+struct StatsOut {
+    void* max;
+    void* sum;
+    int64_t* argmax;
+};
+
+// Drains rows [row0, row0 + rows) x all n columns of one accumulator into `stage` and sends them
+// to the contiguous global range that starts at `gptr`.
+template <typename OutT, bool SCALE, bool STATS>
+__device__ __forceinline__ void drain_packed(uint8_t* stage, uint8_t* gptr, int n, int rows, uint32_t taddr0, bool has_bias, float bias, float scale,
+                                             int lane, const StatsOut& so, int64_t first_row) {
+    const uint32_t phase = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(gptr)) & 15u;
+    const int chunks = (n + 31) >> 5;
+    const uint32_t scale2 = pair_of<OutT>(scale);
+    uint8_t* my_row = stage + phase + static_cast<size_t>(lane) * n * 2;
+    const bool mine = lane < rows;
+    RowStats stats;
+    stats.init();
+    uint32_t va[32], vb[32];
+    tmem_load_issue(taddr0, va);
+    for (int c = 0; c < chunks; c += 2) {
+        tmem_load_wait(va);
+        if (c + 1 < chunks) tmem_load_issue(taddr0 + (c + 1) * 32, vb);
+        if (mine) stage_packed_chunk<OutT, SCALE, STATS>(va, my_row + c * 64, min(32, n - c * 32), has_bias, bias, scale2, stats, c);
+        if (c + 1 >= chunks) break;
+        tmem_load_wait(vb);
+        if (c + 2 < chunks) tmem_load_issue(taddr0 + (c + 2) * 32, va);
+        if (mine) stage_packed_chunk<OutT, SCALE, STATS>(vb, my_row + (c + 1) * 64, min(32, n - (c + 1) * 32), has_bias, bias, scale2, stats, c + 1);
+    }
+    if constexpr (STATS) {
+        if (mine) {
+            // the chunk that holds the first occurrence of the row maximum: the even and the odd columns
+            // each know theirs; equal maxima resolve to the earlier chunk, the scan below to the column
+            int chunk = -1;
+            float best = -INFINITY;
+            if (stats.chunk_even >= 0) {
+                chunk = stats.chunk_even;
+                best = stats.max_even;
+            }
+            if (stats.chunk_odd >= 0 && (chunk < 0 || stats.max_odd > best || (stats.max_odd == best && stats.chunk_odd < chunk))) {
+                chunk = stats.chunk_odd;
+                best = stats.max_odd;
+            }
+            int index = 0;
+            const OutT* row = reinterpret_cast<const OutT*>(my_row);
+            if (chunk >= 0) {
+                const int base = chunk * 32, width = min(32, n - base);
+                index = base;
+#pragma unroll 8
+                for (int j = 31; j >= 0; --j)
+                    if (j < width && to_compute<float>(row[base + j]) == best) index = base + j;
+            }
+            const int64_t r = first_row + lane;
+            if (so.max) static_cast<OutT*>(so.max)[r] = row[index];  // the element itself: the sign of a zero survives
+            if (so.sum) static_cast<OutT*>(so.sum)[r] = from_compute<OutT, float>(stats.sum0 + stats.sum1);
+            if (so.argmax) so.argmax[r] = index;
+        }
+    }
+    fence_async_smem();  // generic-proxy writes become visible to the copy engine
+    __syncwarp();
+    const uintptr_t g0 = reinterpret_cast<uintptr_t>(gptr), g1 = g0 + static_cast<size_t>(rows) * n * 2;
+    const uintptr_t a0 = (g0 + 15) & ~uintptr_t(15), a1 = g1 & ~uintptr_t(15);
+    const uintptr_t origin = g0 - phase;  // global address that corresponds to stage[0]
+    if (lane == 0 && a1 > a0) {
+        bulk_store_linear(reinterpret_cast<void*>(a0), smem_u32(stage + (a0 - origin)), static_cast<uint32_t>(a1 - a0));
+        bulk_commit();
+    }
+    // elements before the first and after the last 16-byte boundary (at most seven each)
+    const uintptr_t head_end = a0 < g1 ? a0 : g1;
+    const uintptr_t tail_begin = a1 > a0 ? a1 : a0;
+    if (lane < 8) {
+        const uintptr_t x = g0 + 2 * lane;
+        if (x < head_end) *reinterpret_cast<uint16_t*>(x) = *reinterpret_cast<const uint16_t*>(stage + (x - origin));
+    } else if (lane < 16) {
+        const uintptr_t x = tail_begin + 2 * (lane - 8);
+        if (x < g1) *reinterpret_cast<uint16_t*>(x) = *reinterpret_cast<const uint16_t*>(stage + (x - origin));
+    }
+}
+
 enum { OUT_F16 = 0, OUT_BF16 = 1, OUT_F32 = 2 };
 template <int OUT> struct out_type { using type = __half; };
 template <> struct out_type<OUT_BF16> { using type = __nv_bfloat16; };
@@ -440,33 +662,40 @@ template <> struct out_type<OUT_F32> { using type = float; };
 
 // MODE: operand layout (see the top of the file); OUT: result element type; SCALE: multiply the
 // rounded result by a scalar. All three are compile-time so that the epilogue is branch-free.
-template <int MODE, int OUT, bool SCALE>
+// PACK: PACK_ROWS selects the packed epilogue above (16-bit results only); it trades two of the
+// four operand stages for 8 staging blocks of up to 16.5 KiB. PACK_STATS also produces the maximum,
+// sum and argmax of every result row in the same pass.
+enum { PACK_NONE = 0, PACK_ROWS = 1, PACK_STATS = 2 };
+template <int MODE, int OUT, bool SCALE, int PACK>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_d, const KernelArgs g) {
+    constexpr bool PACKED = PACK != PACK_NONE;
+    constexpr int kStages = PACKED ? PACKED_STAGES : STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
     uint8_t* base_ptr = smem_raw + (base - raw);
-    const uint32_t staging = base + STAGES * STAGE_BYTES;
-    uint8_t* staging_ptr = base_ptr + STAGES * STAGE_BYTES;
-    const uint32_t bars = staging + STAGING_BYTES;
-    // barrier layout (8 bytes each): full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
-    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, accf0 = bars + 16 * STAGES, acce0 = accf0 + 16;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + STAGES * STAGE_BYTES + STAGING_BYTES + 16 * STAGES + 32);
+    const uint32_t staging_bytes = PACKED ? kEpilogueWarps * g.pack_stage_bytes : STAGING_BYTES;
+    const uint32_t staging = base + kStages * STAGE_BYTES;
+    uint8_t* staging_ptr = base_ptr + kStages * STAGE_BYTES;
+    const uint32_t bars = staging + staging_bytes;
+    // barrier layout (8 bytes each): full[kStages], empty[kStages], acc_full[2], acc_empty[2]
+    const uint32_t full0 = bars, empty0 = bars + 8 * kStages, accf0 = bars + 16 * kStages, acce0 = accf0 + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + kStages * STAGE_BYTES + staging_bytes + 16 * kStages + 32);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_blocks = g.k_blocks;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < kStages; ++s) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(accf0 + 8 * b, 1);
-            mbar_init(acce0 + 8 * b, g.epi_warps);
+            mbar_init(acce0 + 8 * b, PACKED ? 4 : g.epi_warps);  // packed: four warps per accumulator
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -489,8 +718,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 int batch, mt, nt;
                 tile_coords(t, g.m_tiles, g.n_tiles, batch, mt, nt);
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t parity = ((it / STAGES) & 1) ^ 1;
+                    const int s = it % kStages;
+                    const uint32_t parity = ((it / kStages) & 1) ^ 1;
                     if (!mbar_wait(empty0 + 8 * s, parity, abort_flag)) { ok = false; break; }
                     const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
                     mbar_expect_tx(full0 + 8 * s, g.stage_tx);
@@ -536,8 +765,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tc_fence_after();
                 const uint32_t tmem_acc = tmem_base + buf * BN;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t parity = (it / STAGES) & 1;
+                    const int s = it % kStages;
+                    const uint32_t parity = (it / kStages) & 1;
                     if (!mbar_wait(full0 + 8 * s, parity, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = base + s * STAGE_BYTES, sb = sa + A_BYTES;
@@ -554,6 +783,42 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 if (ok) umma_commit(accf0 + 8 * buf);  // accumulator complete
             }
+        }
+    } else if (PACKED) {
+        // ------------------------------------------------------------ packed epilogue -
+        if constexpr (PACKED) {
+            const int ew = warp - 2;
+            const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter+32)
+            const int buf = ew >> 2;                 // this warp drains the tiles of one accumulator
+            uint8_t* stage = staging_ptr + static_cast<size_t>(ew) * g.pack_stage_bytes;
+            const int n = static_cast<int>(g.N);
+            uint32_t uses = 0;
+            bool ok = true;
+            for (uint64_t t = blockIdx.x + static_cast<uint64_t>(buf) * gridDim.x; ok && t < g.total_tiles; t += 2 * gridDim.x, ++uses) {
+                int batch, mt, nt;
+                tile_coords(static_cast<uint32_t>(t), g.m_tiles, g.n_tiles, batch, mt, nt);
+                if (!mbar_wait(accf0 + 8 * buf, uses & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const int64_t row0 = static_cast<int64_t>(mt) * BM + quarter * 32;
+                const int rows = static_cast<int>(min(static_cast<int64_t>(32), g.M - row0));
+                if (rows > 0) {  // warp-uniform
+                    float bias = 0.0f;
+                    if (g.bias != nullptr && lane < rows)
+                        bias = g.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(g.bias)[row0 + lane])
+                                         : __half2float(static_cast<const __half*>(g.bias)[row0 + lane]);
+                    if (lane == 0) bulk_wait_read_0();  // the previous tile's bulk store has read the staging block
+                    __syncwarp();
+                    uint8_t* gptr = static_cast<uint8_t*>(g.d) + (static_cast<size_t>(batch) * g.d_batch + static_cast<size_t>(row0) * n) * 2;
+                    const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+                    const StatsOut so = {g.stat_max, g.stat_sum, g.stat_argmax};
+                    drain_packed<typename out_type<OUT>::type, SCALE, PACK == PACK_STATS>(stage, gptr, n, rows, taddr0, g.bias != nullptr, bias, g.scale, lane,
+                                                                                          so, static_cast<int64_t>(batch) * g.M + row0);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acce0 + 8 * buf);
+            }
+            if (lane == 0) bulk_wait_all();  // shared memory stays valid until the last store has left
         }
     } else if (warp - 2 < g.epi_warps) {
         // ------------------------------------------------------------ epilogue --------
@@ -662,7 +927,8 @@ tn_status encode(CUtensorMap* map, const void* ptr, bool bf16, int rank, const c
 // on a 16-byte column boundary.
 bool can_tma_store(const void* d, int64_t ldd, int64_t d_batch, int64_t tile_n, bool f32) {
     const int64_t per16 = f32 ? 4 : 8;
-    if (getenv("TN_TC_NO_TMA_STORE")) return false;
+    static const bool disabled = getenv("TN_TC_NO_TMA_STORE") != nullptr;
+    if (disabled) return false;
     return aligned16(d) && ldd % per16 == 0 && d_batch % per16 == 0 && tile_n % per16 == 0;
 }
 tn_status make_result_map(CUtensorMap* map, void* d, bool f32, bool bf16, int64_t n, int64_t m, int64_t batches, int64_t ldd, int64_t d_batch) {
@@ -690,35 +956,64 @@ tn_status make_map(CUtensorMap* map, const void* ptr, bool bf16, int64_t inner, 
 }
 
 
-template <int MODE, int OUT, bool SCALE>
+// Environment knobs are read once per process (measurement aids; the defaults are the tuned values).
+int env_epilogue_warps() {
+    static const int value = [] {
+        const char* v = getenv("TN_TC_EPILOGUE_WARPS");
+        const int n = v ? atoi(v) : 0;
+        return (n == 4 || n == 8) ? n : 0;
+    }();
+    return value;
+}
+
+template <int MODE, int OUT, bool SCALE, int PACK>
 tn_status launch_one(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const KernelArgs& g, cudaStream_t stream) {
     // the opt-in shared-memory size is a per-device attribute of the kernel
     static thread_local int attr_device = -1;
+    constexpr bool PACKED = PACK != PACK_NONE;
+    constexpr uint32_t kSmemMax = PACKED ? PACKED_SMEM_MAX : SMEM_BYTES;
     int dev = 0;
     TN_CUDA(cudaGetDevice(&dev));
     if (attr_device != dev) {
-        TN_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<MODE, OUT, SCALE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        TN_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<MODE, OUT, SCALE, PACK>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax));
         attr_device = dev;
     }
     const int64_t sms = sm_count();
     const int grid = (int)(g.total_tiles < sms ? g.total_tiles : sms);
     KernelArgs args = g;
     // A long main loop hides a 4-warp epilogue completely; short ones (HBM-bound shapes) are paced
-    // by the epilogue and get all eight warps.
+    // by the epilogue and get all eight warps. The packed epilogue always runs eight.
     args.epi_warps = g.k_blocks >= 16 ? 4 : 8;
-    if (const char* v = getenv("TN_TC_EPILOGUE_WARPS")) {
-        const int n = atoi(v);
-        if (n == 4 || n == 8) args.epi_warps = n;
+    if (env_epilogue_warps()) args.epi_warps = env_epilogue_warps();
+    uint32_t smem = SMEM_BYTES;
+    if (PACKED) {
+        args.epi_warps = 8;
+        smem = 1024 + PACKED_STAGES * STAGE_BYTES + kEpilogueWarps * g.pack_stage_bytes + 256;
     }
-    tc_gemm_kernel<MODE, OUT, SCALE><<<grid, kThreads, SMEM_BYTES, stream>>>(map_a, map_b, map_d, args);
+    tc_gemm_kernel<MODE, OUT, SCALE, PACK><<<grid, kThreads, smem, stream>>>(map_a, map_b, map_d, args);
     return after_launch("tc_gemm_kernel");
+}
+
+template <int MODE, int OUT, int PACK>
+tn_status launch_scaled(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const KernelArgs& g, cudaStream_t stream) {
+    return g.has_scale ? launch_one<MODE, OUT, true, PACK>(map_a, map_b, map_d, g, stream)
+                       : launch_one<MODE, OUT, false, PACK>(map_a, map_b, map_d, g, stream);
 }
 
 template <int MODE>
 tn_status launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const KernelArgs& g, cudaStream_t stream) {
-    if (g.d_is_f32) return g.has_scale ? launch_one<MODE, OUT_F32, true>(map_a, map_b, map_d, g, stream) : launch_one<MODE, OUT_F32, false>(map_a, map_b, map_d, g, stream);
-    if (g.is_bf16) return g.has_scale ? launch_one<MODE, OUT_BF16, true>(map_a, map_b, map_d, g, stream) : launch_one<MODE, OUT_BF16, false>(map_a, map_b, map_d, g, stream);
-    return g.has_scale ? launch_one<MODE, OUT_F16, true>(map_a, map_b, map_d, g, stream) : launch_one<MODE, OUT_F16, false>(map_a, map_b, map_d, g, stream);
+    if (g.d_is_f32) return launch_scaled<MODE, OUT_F32, PACK_NONE>(map_a, map_b, map_d, g, stream);
+    if constexpr (MODE != MODE_CONV) {
+        if (g.pack_stage_bytes != 0) {
+            if (g.stat_max || g.stat_sum || g.stat_argmax)
+                return g.is_bf16 ? launch_scaled<MODE, OUT_BF16, PACK_STATS>(map_a, map_b, map_d, g, stream)
+                                 : launch_scaled<MODE, OUT_F16, PACK_STATS>(map_a, map_b, map_d, g, stream);
+            return g.is_bf16 ? launch_scaled<MODE, OUT_BF16, PACK_ROWS>(map_a, map_b, map_d, g, stream)
+                             : launch_scaled<MODE, OUT_F16, PACK_ROWS>(map_a, map_b, map_d, g, stream);
+        }
+    }
+    return g.is_bf16 ? launch_scaled<MODE, OUT_BF16, PACK_NONE>(map_a, map_b, map_d, g, stream)
+                     : launch_scaled<MODE, OUT_F16, PACK_NONE>(map_a, map_b, map_d, g, stream);
 }
 
 }  // namespace
@@ -735,6 +1030,10 @@ bool tc_gemm_eligible(const TcGemm& p) {
     if (p.M >= (int64_t(1) << 31) || p.N >= (int64_t(1) << 31) || p.K >= (int64_t(1) << 31) || p.batches >= (int64_t(1) << 31)) return false;
     const int64_t tiles = ceil_div(p.M, BM) * ceil_div(p.N, BN) * p.batches;
     return tiles < (int64_t(1) << 31);
+}
+
+bool tc_gemm_can_fuse_stats(const TcGemm& p) {
+    return tc_gemm_eligible(p) && p.d_dtype == p.ab_dtype && p.N <= BN && p.ldd == p.N;
 }
 
 static bool can_vector_store(const void* d, int64_t ldd, int64_t d_batch, int64_t n, int64_t tile_n, bool f32) {
@@ -773,6 +1072,19 @@ tn_status tc_gemm(const TcGemm& p, cudaStream_t stream) {
     CUtensorMap map_d = map_a;  // placeholder when the result does not leave through TMA
     g.tma_store = can_tma_store(p.d, p.ldd, p.d_batch, BN, g.d_is_f32 != 0);
     if (g.tma_store) TN_TRY(make_result_map(&map_d, p.d, g.d_is_f32 != 0, bf16, p.N, p.M, p.batches, p.ldd, p.d_batch));
+    // Rows that follow one another without a gap but are not 16-byte multiples: a tile that spans all
+    // columns is one contiguous byte range per 32 rows, which the packed epilogue writes in bulk.
+    static const bool no_packed = getenv("TN_TC_NO_PACKED") != nullptr;
+    const bool wants_stats = p.stat_max || p.stat_sum || p.stat_argmax;
+    const bool can_pack = !g.d_is_f32 && g.n_tiles == 1 && p.ldd == p.N;
+    if (wants_stats && !can_pack) return fail(TN_ERROR, "fused row statistics need a dense 16-bit result of at most %d columns", BN);
+    if (can_pack && (wants_stats || (!g.tma_store && !g.vec_store && !no_packed))) {
+        g.pack_stage_bytes = (uint32_t)((32 * p.N * 2 + 16 + 127) & ~int64_t(127));
+        g.tma_store = 0;
+        g.stat_max = p.stat_max;
+        g.stat_sum = p.stat_sum;
+        g.stat_argmax = p.stat_argmax;
+    }
     return p.b_n_major ? launch<MODE_N>(map_a, map_b, map_d, g, stream) : launch<MODE_K>(map_a, map_b, map_d, g, stream);
 }
 
@@ -837,6 +1149,32 @@ tn_status tc_conv(const TcConv& p, cudaStream_t stream) {
     g.tma_store = can_tma_store(p.y, g.ldd, g.d_batch, g.tile_n, false);
     if (g.tma_store) TN_TRY(make_result_map(&map_d, p.y, false, bf16, g.N, p.Cout, p.N, g.ldd, g.d_batch));
     return launch<MODE_CONV>(map_a, map_b, map_d, g, stream);
+}
+
+// One warp waits, with the kernels' own bounded wait, on a barrier that nothing will ever complete:
+// the wait runs out after `polls` polls, the abort flag goes up and the error counter is bumped,
+// exactly as in a GEMM CTA whose producer never delivers. Nothing faults and nothing hangs; the
+// kernel returns after at most polls x 64 ns.
+__global__ void __launch_bounds__(32) wait_probe_kernel(uint32_t polls) {
+    __shared__ __align__(8) uint64_t barrier;
+    __shared__ int abort_flag;
+    const uint32_t bar = smem_u32(&barrier);
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    bool ok = true;
+    if (threadIdx.x == 0) ok = mbar_wait(bar, 0, &abort_flag, polls);
+    __syncwarp();
+    if (threadIdx.x == 0 && !ok && abort_flag) atomicAdd(&g_tc_aborts, 1u);
+}
+
+tn_status tc_wait_probe(cudaStream_t stream, unsigned int polls) {
+    if (polls > kSpinLimit) polls = kSpinLimit;
+    wait_probe_kernel<<<1, 32, 0, stream>>>(polls);
+    return after_launch("wait_probe_kernel");
 }
 
 tn_status tc_abort_count(unsigned int* count) {

@@ -23,7 +23,15 @@ struct TcGemm {
     bool b_n_major = false;
     bool has_scale = false;      // d = round(round(acc) * scale)
     float scale = 1.0f;
+    // Optional fused row statistics of the (rounded, scaled) result along its last axis, indexed by
+    // batch * M + row; usable when tc_gemm_can_fuse_stats(p). Value outputs have the result's dtype.
+    void* stat_max = nullptr;
+    void* stat_sum = nullptr;
+    int64_t* stat_argmax = nullptr;
 };
+// True when the result is 16-bit, dense (ldd == N) and one tile wide (N <= 256): then each result row
+// is drained by one thread, which can keep the row's maximum, sum and argmax as it goes.
+bool tc_gemm_can_fuse_stats(const TcGemm& p);
 
 // Implicit-GEMM convolution (stride 1) on the same main loop. `x_nhwc` is the activation in
 // [N, H, W, C] order and `w_packed` the weights in [Kh*Kw, Cout, Cin] order (both produced by the

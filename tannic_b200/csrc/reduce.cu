@@ -52,6 +52,14 @@ template <typename C, bool MIN> __device__ __forceinline__ C cmp_init() {
 template <typename T> struct is_half16 { static constexpr bool value = false; };
 template <> struct is_half16<__half> { static constexpr bool value = true; };
 template <> struct is_half16<__nv_bfloat16> { static constexpr bool value = true; };
+template <typename T> struct pair_of_half { using type = __half2; };
+template <> struct pair_of_half<__nv_bfloat16> { using type = __nv_bfloat162; };
+// both halves of a word set to the 16-bit form of `v`
+template <typename T> __device__ __forceinline__ uint32_t pair_bits(float v) {
+    const T one = from_compute<T, float>(v);
+    const uint32_t b = *reinterpret_cast<const uint16_t*>(&one);
+    return b | (b << 16);
+}
 template <typename T> __device__ __forceinline__ float half_of_pair(uint32_t w, int h) {
     const uint16_t bits = static_cast<uint16_t>(h ? (w >> 16) : (w & 0xffffu));
     return to_compute<float>(*reinterpret_cast<const T*>(&bits));
@@ -362,33 +370,37 @@ __global__ void __launch_bounds__(kStagedThreads) reduce_rows_staged(const T* __
                     A sum_hi = A(0);
                     if (off && q == 0) feed(row[0], 0, sum);
                     if constexpr (ARG && is_half16<T>::value) {
-                        // Floats: one comparison per WORD. The better of the two halves (a NaN is dropped
-                        // by fmaxf / fminf) is compared strictly with the running extreme and only the
-                        // word's position is remembered; which half it was is settled once, afterwards.
-                        // (Eight elements per comparison on contiguous per-lane runs measured slower:
-                        // 4.07 against 4.39 TB/s for max + sum + argmax of 197-wide rows.)
-                        float ext = cmp_init<float, MIN>();
-                        int at = -1;
+                        // Floats: both halves of a word are compared at once with packed 16-bit
+                        // arithmetic. Each half keeps a running extreme and the (16-bit) word position
+                        // where it last improved; a strict ordered comparison never selects a NaN and
+                        // keeps the first of equal values. The two halves are merged once, afterwards.
+                        using T2 = typename pair_of_half<T>::type;
+                        uint32_t run = pair_bits<T>(cmp_init<float, MIN>());
+                        uint32_t at2 = 0xFFFFFFFFu;                       // 0xFFFF: this half never improved
+                        uint32_t pr2 = static_cast<uint32_t>(q) * 0x00010001u;
+                        const uint32_t step2 = static_cast<uint32_t>(lanes) * 0x00010001u;
 #pragma unroll 4
-                        for (int pr = q; pr < npairs; pr += lanes) {
+                        for (int pr = q; pr < npairs; pr += lanes, pr2 += step2) {
                             const uint32_t w = words[pr];
-                            const float lo = half_of_pair<T>(w, 0), hi = half_of_pair<T>(w, 1);
                             if constexpr (SUM) {
-                                sum += lo;
-                                sum_hi += hi;
+                                sum += half_of_pair<T>(w, 0);
+                                sum_hi += half_of_pair<T>(w, 1);
                             }
-                            const float m = MIN ? fminf(lo, hi) : fmaxf(lo, hi);
-                            if (MIN ? (m < ext) : (m > ext)) {
-                                ext = m;
-                                at = pr;
-                            }
+                            const T2 x = *reinterpret_cast<const T2*>(&w), r2 = *reinterpret_cast<const T2*>(&run);
+                            const uint32_t better = MIN ? __hlt2_mask(x, r2) : __hgt2_mask(x, r2);
+                            run = (w & better) | (run & ~better);
+                            at2 = (pr2 & better) | (at2 & ~better);
                         }
-                        if (at >= 0) {
-                            // the first half equal to the extreme (equality, so that -0 and +0 tie)
-                            const int j = off + 2 * at + (half_of_pair<T>(words[at], 0) == ext ? 0 : 1);
-                            if ((MIN ? (ext < best) : (ext > best)) || (ext == best && j < idx)) {
-                                best = ext;
-                                idx = j;
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const uint32_t at = (at2 >> (16 * h)) & 0xFFFFu;
+                            if (at != 0xFFFFu) {
+                                const float v = half_of_pair<T>(run, h);
+                                const int j = off + 2 * static_cast<int>(at) + h;
+                                if ((MIN ? (v < best) : (v > best)) || (v == best && j < idx)) {
+                                    best = v;
+                                    idx = j;
+                                }
                             }
                         }
                     } else {

@@ -36,7 +36,7 @@ namespace {
 
 struct DeviceState {
     std::vector<cudaStream_t> idle;  // LIFO: the most recently returned stream is handed out next
-    bool pool_ready = false;
+    cudaMemPool_t pool = nullptr;    // the backend's own stream-ordered pool (created on first use)
     int sms = 0;
 };
 
@@ -105,32 +105,38 @@ int sm_count() {
     return ds.sms;
 }
 
-// The default memory pool keeps freed blocks (release threshold = max) so that the
-// allocate/free pair around every expression temporary does not go back to the driver.
-static tn_status ensure_pool(int id) {
+// The backend allocates from a memory pool of its own, so that keeping freed blocks (release
+// threshold = unlimited: the allocate/free pair around every expression temporary never goes back
+// to the driver) does not change the behaviour of the process-wide default pool, which other
+// libraries in the process allocate from.
+static tn_status device_pool(int id, cudaMemPool_t* out) {
     Runtime& rt = runtime();
     std::lock_guard<std::mutex> lock(rt.mutex);
+    rt.ensure_counted();
+    if (id < 0 || id >= (int)rt.devices.size()) return fail(TN_ERROR, "device id %d out of range", id);
     DeviceState& ds = rt.devices[id];
-    if (ds.pool_ready) return TN_SUCCESS;
-    cudaMemPool_t pool;
-    TN_CUDA(cudaDeviceGetDefaultMemPool(&pool, id));
-    uint64_t threshold = UINT64_MAX;
-    TN_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold));
-    ds.pool_ready = true;
+    if (!ds.pool) {
+        cudaMemPoolProps props = {};
+        props.allocType = cudaMemAllocationTypePinned;
+        props.handleTypes = cudaMemHandleTypeNone;
+        props.location.type = cudaMemLocationTypeDevice;
+        props.location.id = id;
+        cudaMemPool_t pool = nullptr;
+        TN_CUDA(cudaMemPoolCreate(&pool, &props));
+        uint64_t threshold = UINT64_MAX;
+        TN_CUDA(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold));
+        ds.pool = pool;
+    }
+    *out = ds.pool;
     return TN_SUCCESS;
 }
 
 tn_status scratch_alloc(void** ptr, size_t nbytes, cudaStream_t stream) {
     int dev = 0;
     TN_CUDA(cudaGetDevice(&dev));
-    {
-        Runtime& rt = runtime();
-        std::lock_guard<std::mutex> lock(rt.mutex);
-        rt.ensure_counted();
-        if (dev < 0 || dev >= (int)rt.devices.size()) return fail(TN_ERROR, "no CUDA device is current");
-    }
-    TN_TRY(ensure_pool(dev));  // keep freed scratch in the pool instead of returning it to the driver
-    TN_CUDA(cudaMallocAsync(ptr, nbytes, stream));
+    cudaMemPool_t pool = nullptr;
+    TN_TRY(device_pool(dev, &pool));
+    TN_CUDA(cudaMallocFromPoolAsync(ptr, nbytes ? nbytes : 1, pool, stream));
     return TN_SUCCESS;
 }
 
@@ -151,7 +157,10 @@ static tn_status pop_stream(int id, cudaStream_t* out) {
             return TN_SUCCESS;
         }
     }
-    TN_CUDA(cudaStreamCreateWithFlags(out, cudaStreamNonBlocking));
+    // Blocking with respect to the legacy default stream, as the reference's pool streams are
+    // (cudaStreamCreate, src/cuda/streams.cu:27-33): work a caller puts on stream 0 is ordered after
+    // the copies and allocations this library queued on its pool stream.
+    TN_CUDA(cudaStreamCreate(out));
     return TN_SUCCESS;
 }
 
@@ -202,7 +211,7 @@ tn_status tn_stream_put(const tn_device_t* device, tn_stream_t stream) {
 
 tn_status tn_stream_synchronize(tn_stream_t stream) {
     TN_CUDA(cudaStreamSynchronize(as_cuda(stream)));
-    return TN_SUCCESS;
+    return surface_device_aborts();
 }
 
 tn_status tn_allocate(const tn_device_t* device, size_t nbytes, void** address) {
@@ -210,12 +219,14 @@ tn_status tn_allocate(const tn_device_t* device, size_t nbytes, void** address) 
     *address = nullptr;
     cudaStream_t s = nullptr;
     TN_TRY(pop_stream(device->id, &s));
-    tn_status st = ensure_pool(device->id);
+    cudaMemPool_t pool = nullptr;
+    tn_status st = device_pool(device->id, &pool);
     if (st == TN_SUCCESS) {
-        cudaError_t err = cudaMallocAsync(address, nbytes ? nbytes : 1, s);
+        cudaError_t err = cudaMallocFromPoolAsync(address, nbytes ? nbytes : 1, pool, s);
         if (err != cudaSuccess) {
             cudaGetLastError();
-            st = fail(TN_ERROR, "cudaMallocAsync(%zu) failed: %s", nbytes, cudaGetErrorString(err));
+            *address = nullptr;
+            st = fail(TN_ERROR, "device allocation of %zu bytes failed: %s", nbytes, cudaGetErrorString(err));
         }
     }
     put_stream(device->id, s);
@@ -240,8 +251,10 @@ tn_status tn_copy_from_host(const tn_device_t* device, const void* host, void* d
     if (!device) return fail(TN_ERROR, "null device");
     cudaStream_t s = nullptr;
     TN_TRY(pop_stream(device->id, &s));
-    // Pageable sources are staged by the runtime before the call returns, so the caller may
-    // reuse `host` immediately (the reference relies on the same property, src/cuda/mem.cu:38-44).
+    // A pageable source is staged by the CUDA runtime before the call returns, so the caller may reuse
+    // `host` at once (the reference relies on the same property, src/cuda/mem.cu:38-44). A PINNED
+    // source is read by the copy engine later, in stream order: it must stay unchanged until the pool
+    // stream has passed the copy (tn_stream_synchronize, or any synchronising call).
     cudaError_t err = cudaMemcpyAsync(dev, host, nbytes, cudaMemcpyHostToDevice, s);
     put_stream(device->id, s);
     if (err != cudaSuccess) return fail(TN_ERROR, "H2D copy failed: %s", cudaGetErrorString(err));
@@ -256,7 +269,7 @@ tn_status tn_copy_to_host(const tn_device_t* device, const void* dev, void* host
     if (err == cudaSuccess) err = cudaStreamSynchronize(s);
     put_stream(device->id, s);
     if (err != cudaSuccess) return fail(TN_ERROR, "D2H copy failed: %s", cudaGetErrorString(err));
-    return TN_SUCCESS;
+    return surface_device_aborts();
 }
 
 tn_status tn_copy_from_host_async(const tn_device_t* device, const void* host, void* dev, size_t nbytes, tn_stream_t stream) {

@@ -295,7 +295,7 @@ tn_status tn_allclose(const tn_tensor_t* a, const tn_tensor_t* b, tn_stream_t st
     scratch_free(flag, s);
     if (err != cudaSuccess) return fail(TN_ERROR, "allclose failed: %s", cudaGetErrorString(err));
     *close = mismatch ? 0 : 1;
-    return TN_SUCCESS;
+    return surface_device_aborts();
 }
 
 }  // extern "C"

@@ -132,68 +132,57 @@ def program(inputs: Sequence[torch.Tensor], nodes: Sequence[tuple], out: torch.T
     return out
 
 
-class HostPipeline:
-    """Host buffers in, host buffer out, for a fused elementwise program: the rows are cut into chunks and
-    the host-to-device copy of chunk c + 1, the kernel of chunk c and the device-to-host copy of chunk
-    c - 1 run at the same time on three streams (PCIe is full duplex), so a call costs about one
-    direction's transfer time instead of both plus the kernel. Inputs whose leading extent equals the
-    result's are chunked; smaller (broadcast) inputs are copied whole first. Host tensors should be
-    pinned, otherwise the copies are synchronous. Device staging memory is kept between calls.
+def program_host(inputs: Sequence[torch.Tensor], nodes: Sequence[tuple], out_host: torch.Tensor, device: int = 0, chunks: int = 0) -> torch.Tensor:
+    """Fused elementwise program over HOST tensors through tn_eltwise_program_host: chunked copy-in,
+    kernel and copy-out overlapped on three streams inside the library; returns when `out_host` is
+    complete. Host tensors should be pinned (see pinned_empty), otherwise the copies are synchronous."""
+    descs = [desc(t) for t in inputs]
+    ptrs = (C.POINTER(A.TensorT) * len(descs))(*[C.pointer(d) for d in descs])
+    arr = (A.EltwiseNode * len(nodes))()
+    for k, nd in enumerate(nodes):
+        arr[k].opcode, arr[k].lhs, arr[k].rhs = nd[0], nd[1], nd[2]
+        arr[k].imm = nd[3] if len(nd) > 3 else 0.0
+    dd = desc(out_host)
+    dev = A.DeviceT(device)
+    A.check(A.lib().tn_eltwise_program_host(C.byref(dev), ptrs, len(descs), arr, len(nodes), C.byref(dd), chunks))
+    return out_host
 
-    The reference moves data with one synchronous cudaMemcpy per call (src/cuda/mem.cu:54-90) and has no
-    pinned host allocator (src/resources.cpp:24-38 throws)."""
 
-    def __init__(self, device: int | torch.device | None = None, chunks: int = 8):
-        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-        self.chunks = chunks
-        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
-        self._staging: dict = {}
+class PinnedBuffer:
+    """Pinned host memory from the backend's allocator, preferably on the memory node of `device`
+    (tn_host_allocate_pinned_near), viewed as a torch tensor. Freed when the object is collected."""
 
-    def _dev(self, key, shape, dtype):
-        buf = self._staging.get(key)
-        if buf is None or tuple(buf.shape) != tuple(shape) or buf.dtype != dtype:
-            buf = torch.empty(tuple(shape), dtype=dtype, device=self.device)
-            self._staging[key] = buf
-        return buf
+    def __init__(self, shape, dtype: torch.dtype, device: int = 0):
+        self.nbytes = int(torch.empty((), dtype=dtype).element_size())
+        for n in shape:
+            self.nbytes *= int(n)
+        self.address = C.c_void_p()
+        dev = A.DeviceT(device)
+        A.check(A.lib().tn_host_allocate_pinned_near(C.byref(dev), _b.max(self.nbytes, 1), C.byref(self.address)))
+        raw = (C.c_uint8 * _b.max(self.nbytes, 1)).from_address(self.address.value)
+        self.tensor = torch.frombuffer(raw, dtype=torch.uint8, count=self.nbytes).view(dtype).reshape(tuple(shape))
 
-    def program(self, inputs: Sequence[torch.Tensor], nodes: Sequence[tuple], out_host: torch.Tensor) -> torch.Tensor:
-        shape = tuple(inputs[0].shape)
-        for t in inputs[1:]:
-            shape = broadcast_shape(shape, t.shape)
-        if tuple(out_host.shape) != shape:
-            raise ValueError("out_host must have the broadcast shape")
-        rows = shape[0] if len(shape) > 1 else 1
-        chunked = [len(shape) > 1 and t.dim() == len(shape) and t.shape[0] == rows and rows > 1 for t in inputs]
-        dev_in = [self._dev(("in", k), t.shape, t.dtype) for k, t in enumerate(inputs)]
-        dev_out = self._dev(("out",), shape, out_host.dtype)
-        caller = torch.cuda.current_stream(self.device)
-        for s in (self.s_in, self.s_run, self.s_out):
-            s.wait_stream(caller)
-        with torch.cuda.stream(self.s_in):
-            for k, t in enumerate(inputs):
-                if not chunked[k]:
-                    dev_in[k].copy_(t, non_blocking=True)
-        n = _b.max(1, _b.min(self.chunks, rows)) if any(chunked) else 1
-        bounds = [(rows * c) // n for c in range(n + 1)]
-        for c in range(n):
-            lo, hi = bounds[c], bounds[c + 1]
-            if hi == lo:
-                continue
-            with torch.cuda.stream(self.s_in):
-                for k, t in enumerate(inputs):
-                    if chunked[k]:
-                        dev_in[k][lo:hi].copy_(t[lo:hi], non_blocking=True)
-                arrived = self.s_in.record_event()
-            with torch.cuda.stream(self.s_run):
-                self.s_run.wait_event(arrived)
-                views = [dev_in[k][lo:hi] if chunked[k] else dev_in[k] for k in range(len(inputs))]
-                program(views, nodes, out=dev_out[lo:hi] if any(chunked) else dev_out)
-                done = self.s_run.record_event()
-            with torch.cuda.stream(self.s_out):
-                self.s_out.wait_event(done)
-                (out_host[lo:hi] if any(chunked) else out_host).copy_(dev_out[lo:hi] if any(chunked) else dev_out, non_blocking=True)
-        caller.wait_stream(self.s_out)
-        return out_host
+    def __del__(self):
+        if getattr(self, "address", None) is not None and self.address.value:
+            try:
+                A.lib().tn_host_free_pinned(self.address)
+            except Exception:
+                pass
+            self.address = None
+
+
+def numa_node(device: int = 0) -> int:
+    node = C.c_int(-1)
+    dev = A.DeviceT(device)
+    A.check(A.lib().tn_device_numa_node(C.byref(dev), C.byref(node)))
+    return node.value
+
+
+def bind_thread_near(device: int = 0) -> int:
+    node = C.c_int(-1)
+    dev = A.DeviceT(device)
+    A.check(A.lib().tn_bind_thread_near(C.byref(dev), C.byref(node)))
+    return node.value
 
 
 def _matmul_dtype(a: int, b: int) -> int:
@@ -223,15 +212,20 @@ def _matmul_dtype(a: int, b: int) -> int:
     raise A.TannicError(A.UNSUPPORTED_DTYPE, "Unsuported dtypes")
 
 
-def matmul(a: torch.Tensor, b: torch.Tensor, scale_by=None, out_dtype: int | None = None) -> torch.Tensor:
-    """matmul(a, b) [* scalar]; transposed operands arrive as strided views (`b.transpose(-1, -2)`)."""
+def matmul(a: torch.Tensor, b: torch.Tensor, scale_by=None, out_dtype: int | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """matmul(a, b) [* scalar]; transposed operands arrive as strided views (`b.transpose(-1, -2)`).
+    `out` (optional) is a preallocated result of the right shape and dtype, as the reference's
+    Callback hands one to the kernel."""
     if a.dim() < 2 or b.dim() < 2:
         raise ValueError("Inputs must have rank >= 2")
     if a.shape[-1] != b.shape[-2]:
         raise ValueError("Inner dimensions must match for matmul")
     batch = broadcast_shape(a.shape[:-2], b.shape[:-2])
     dt = out_dtype if out_dtype is not None else _matmul_dtype(TORCH_TO_TN[a.dtype], TORCH_TO_TN[b.dtype])
-    out = _empty(batch + (a.shape[-2], b.shape[-1]), dt, a)
+    if out is None:
+        out = _empty(batch + (a.shape[-2], b.shape[-1]), dt, a)
+    elif tuple(out.shape) != batch + (a.shape[-2], b.shape[-1]) or out.dtype != TN_TO_TORCH[dt]:
+        raise ValueError("out must have the result's shape and dtype")
     da, db, dd = desc(a), desc(b), desc(out)
     if scale_by is None:
         A.check(A.lib().tn_gemm(C.byref(da), C.byref(db), C.byref(dd), current_stream(a)))
@@ -239,6 +233,24 @@ def matmul(a: torch.Tensor, b: torch.Tensor, scale_by=None, out_dtype: int | Non
         holder, sc = _scalar(scale_by, dt)
         A.check(A.lib().tn_gemm_scaled(C.byref(da), C.byref(db), C.byref(sc), C.byref(dd), current_stream(a)))
     return out
+
+
+def matmul_stats(a: torch.Tensor, b: torch.Tensor, scale_by=None, out: torch.Tensor | None = None):
+    """(S, max, sum, argmax) with S = matmul(a, b) [* scalar] and the three statistics taken along S's
+    last axis in the same kernel where the shape allows (tn_gemm_scaled_stats)."""
+    batch = broadcast_shape(a.shape[:-2], b.shape[:-2])
+    dt = _matmul_dtype(TORCH_TO_TN[a.dtype], TORCH_TO_TN[b.dtype])
+    shape = batch + (a.shape[-2], b.shape[-1])
+    if out is None:
+        out = _empty(shape, dt, a)
+    mx, sm, am = _empty(shape[:-1], dt, a), _empty(shape[:-1], dt, a), _empty(shape[:-1], A.INT64, a)
+    da, db, dd, dmx, dsm, dam = desc(a), desc(b), desc(out), desc(mx), desc(sm), desc(am)
+    sc = None
+    if scale_by is not None:
+        holder, sc = _scalar(scale_by, dt)
+    A.check(A.lib().tn_gemm_scaled_stats(C.byref(da), C.byref(db), C.byref(sc) if sc is not None else None, C.byref(dd),
+                                         C.byref(dmx), C.byref(dsm), C.byref(dam), current_stream(a)))
+    return out, mx, sm, am
 
 
 def _pair(v):

@@ -231,19 +231,87 @@ def test_fused_program_matches_node_chain(dtype, shapes):
 
 
 @pytest.mark.parametrize("shapes", [((1000, 256), (1, 256)), ((37, 64), (37, 64)), ((5, 8), (5, 1)), ((64,), (64,))])
-def test_host_pipeline_matches_device_call(shapes):
-    """Pinned host buffers in and out through the chunked three-stream path == the device call on resident
-    tensors, bit for bit; two calls in a row reuse the staging memory."""
-    x, y = gen(shapes[0], torch.float16, 19, 0.1, 4.0).pin_memory(), gen(shapes[1], torch.float16, 20, -2.0, 2.0).pin_memory()
+@pytest.mark.parametrize("pinned", ["near", "torch", "pageable"])
+def test_host_program_matches_device_call(shapes, pinned):
+    """Host buffers in and out through the library's chunked three-stream path (tn_eltwise_program_host)
+    == the device call on resident tensors, bit for bit; two calls in a row reuse the staging memory.
+    Pinned memory from the backend's own allocator, from torch, and pageable memory all give the same."""
+    x, y = gen(shapes[0], torch.float16, 19, 0.1, 4.0), gen(shapes[1], torch.float16, 20, -2.0, 2.0)
     want = tb.program([dev(x), dev(y)], CFG2_NODES).cpu()
-    pipe = tb.HostPipeline(chunks=8)
-    out = torch.empty(want.shape, dtype=torch.float16).pin_memory()
-    for _ in range(2):
+    keep = []
+    if pinned == "near":
+        bx, by, bo = tb.PinnedBuffer(x.shape, x.dtype), tb.PinnedBuffer(y.shape, y.dtype), tb.PinnedBuffer(want.shape, want.dtype)
+        bx.tensor.copy_(x)
+        by.tensor.copy_(y)
+        keep = [bx, by, bo]
+        hx, hy, out = bx.tensor, by.tensor, bo.tensor
+    elif pinned == "torch":
+        hx, hy, out = x.pin_memory(), y.pin_memory(), torch.empty(want.shape, dtype=torch.float16).pin_memory()
+    else:
+        hx, hy, out = x, y, torch.empty(want.shape, dtype=torch.float16)
+    for chunks in (0, 3):
         out.zero_()
-        pipe.program([x, y], CFG2_NODES, out)
-        torch.cuda.current_stream().synchronize()
-        assert_same(out, want)
-    assert_close(out, _program_oracle(x, y))
+        tb.program_host([hx, hy], CFG2_NODES, out, chunks=chunks)
+        assert_same(out.clone(), want)
+    assert_close(out.clone(), _program_oracle(x, y))
+    del keep
+
+
+def test_host_program_refuses_device_and_strided_tensors():
+    x = gen((8, 16), torch.float16, 19, 0.1, 4.0)
+    out = torch.empty((8, 16), dtype=torch.float16)
+    with pytest.raises(A.TannicError):
+        tb.program_host([dev(x), x], CFG2_NODES, out)
+    with pytest.raises(A.TannicError):
+        tb.program_host([x.t(), x.t()], CFG2_NODES, torch.empty((16, 8), dtype=torch.float16))
+    assert isinstance(tb.numa_node(0), int)
+
+
+@pytest.mark.parametrize("dtype", HALVES)
+@pytest.mark.parametrize("batches,m,n,k,scale", [(5, 197, 197, 64, 0.125), (3, 300, 250, 128, None), (7, 33, 7, 64, 0.5), (2, 128, 256, 192, 2.0),
+                                                 (1, 5, 1, 8, None), (4, 130, 64, 64, 0.25), (2, 100, 300, 64, 0.5)])
+def test_matmul_with_fused_row_statistics(dtype, batches, m, n, k, scale):
+    """tn_gemm_scaled_stats: the product, and max / sum / argmax of each of its rows from the same kernel.
+    S must equal what tn_gemm_scaled writes, bit for bit; argmax and max must be exactly those of that S
+    (the oracle's reduction applied to it), the sum within the 16-bit tolerance. The last shape (300
+    columns) is wider than one tile and takes the product followed by one reduction pass."""
+    a, w = gen((batches, m, k), dtype, 64, -1, 1), gen((batches, n, k), dtype, 65, -1, 1)
+    da, dw = dev(a), dev(w).transpose(-1, -2)
+    plain = tb.matmul(da, dw, scale_by=scale)
+    s, mx, sm, am = tb.matmul_stats(da, dw, scale_by=scale)
+    assert_same(s, plain.cpu())
+    host = s.cpu()
+    assert torch.equal(am.cpu(), oracle.reduce("argmax", host, -1))
+    assert_same(mx, oracle.reduce("max", host, -1))
+    assert_close(sm, oracle.reduce("sum", host, -1, acc=oracle.ACC_WIDE))
+    want = oracle.matmul(a[0], w[0].t(), acc=oracle.ACC_WIDE)
+    assert_close(s[0], oracle.scale(want, scale) if scale is not None else want)
+    assert tb.device_errors() == 0
+
+
+def test_matmul_fused_statistics_ties_nan_and_infinities():
+    """Rows built so that the maximum repeats (first occurrence wins, across even/odd columns and across
+    32-column chunks), is -inf everywhere (index 0), or sits beside NaNs (never selected)."""
+    n, k = 197, 64
+    # batch b: A_b = e_0 (one row), W_b[:, 0] = the wanted row, other columns zero -> S_b[0, j] = W_b[j, 0]
+    rows = torch.full((8, n), -1.0)
+    rows[0, :] = 1.0                                          # every column equal: 0
+    rows[1, [5, 69, 133]] = 3.0                               # ties in three chunks: 5
+    rows[2, [63, 0]] = 2.0                                    # an odd and an even column tie: 0
+    rows[3, :] = float("-inf")                                # all -inf: index 0
+    rows[4, :] = float("nan"); rows[4, [40, 104]] = -5.0      # NaN is never selected: 40
+    rows[5, [33, 1]] = 7.0                                    # odd columns in two chunks: 1
+    rows[6, [62, 63]] = 1.5                                   # neighbours in one pair: 62
+    rows[7, [196, 4]] = 0.0                                   # the last column of the ragged chunk and 4: 4
+    w = torch.zeros((8, n, k), dtype=torch.bfloat16)
+    w[:, :, 0] = rows.to(torch.bfloat16)
+    a = torch.zeros((8, 1, k), dtype=torch.bfloat16)
+    a[:, 0, 0] = 1.0
+    s, mx, sm, am = tb.matmul_stats(dev(a), dev(w).transpose(-1, -2))
+    host = s.cpu()
+    assert torch.equal(am.cpu(), oracle.reduce("argmax", host, -1))
+    assert am.cpu().flatten().tolist() == [0, 5, 0, 0, 40, 1, 62, 4]
+    assert_same(mx, oracle.reduce("max", host, -1))
 
 
 def test_fused_program_dynamic_and_other_static_shapes():
@@ -451,6 +519,28 @@ def test_matmul_batched_broadcast_and_more_than_256_batches():
     # batch-broadcast first operand: falls back to the SIMT path
     a, b = gen((1, 40, 64), torch.float16, 36, -1, 1), gen((5, 64, 24), torch.float16, 37, -1, 1)
     assert_close(tb.matmul(dev(a), dev(b)), oracle.matmul(a, b, acc=oracle.ACC_WIDE))
+    assert tb.device_errors() == 0
+
+
+@pytest.mark.parametrize("dtype", HALVES)
+@pytest.mark.parametrize("batches,m,n,k,offset", [(5, 197, 197, 64, 0), (3, 300, 250, 128, 1), (7, 33, 7, 64, 3), (2, 128, 255, 192, 5),
+                                                  (1, 5, 1, 8, 2), (9, 1, 33, 64, 7), (2, 260, 100, 320, 4)])
+def test_matmul_rows_that_are_not_16_byte_multiples(dtype, batches, m, n, k, offset):
+    """Dense results whose rows are an odd number of bytes from a 16-byte multiple leave the tensor-core
+    kernel as one contiguous range per 32 rows (bulk store of the aligned middle, scalar head and tail).
+    The result is placed `offset` elements into a larger buffer, so every alignment of its first byte
+    is exercised, and the elements around it must stay untouched."""
+    a, w = gen((batches, m, k), dtype, 62, -1, 1), gen((batches, n, k), dtype, 63, -1, 1)
+    guard = 64
+    flat = torch.full((guard + offset + batches * m * n + guard,), 7.0, dtype=dtype, device="cuda")
+    out = flat[guard + offset:guard + offset + batches * m * n].view(batches, m, n)
+    tb.matmul(dev(a), dev(w).transpose(-1, -2), scale_by=0.5, out=out)
+    for i in sorted({0, batches - 1}):
+        want = oracle.scale(oracle.matmul(a[i], w[i].t(), acc=oracle.ACC_WIDE), 0.5)
+        assert_close(out[i], want)
+    ref = torch.matmul(dev(a).float(), dev(w).float().transpose(-1, -2)) * 0.5
+    assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2)
+    assert bool((flat[:guard + offset] == 7.0).all()) and bool((flat[guard + offset + batches * m * n:] == 7.0).all())
     assert tb.device_errors() == 0
 
 
@@ -816,3 +906,4 @@ def _add_host(a):
     out = torch.empty_like(a)
     da, dd = tb.desc(a), tb.desc(out)
     A.check(A.lib().tn_add(C.byref(da), C.byref(da), C.byref(dd), A.StreamT(0)))
+
