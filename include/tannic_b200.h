@@ -146,6 +146,18 @@ tn_status tn_copy_from_host(const tn_device_t* device, const void* host, void* d
 tn_status tn_copy_to_host(const tn_device_t* device, const void* dev, void* host, size_t nbytes);
 tn_status tn_compare_from_host(const tn_device_t* device, const void* host, const void* dev,
                                size_t nbytes, int* equal);
+/* Bulk initialisation. The front-end fills a device tensor from an initializer list with one
+ * cuda::copyFromHost of dsizeof(dtype) bytes per element (Tensor::assign, src/tensor.cpp:34-44).
+ * tn_assign_from_host takes the place of that call for small writes: writes that extend one
+ * contiguous device range are gathered on the calling thread and leave as ONE copy when the range
+ * is broken, when 4 MiB have gathered, or when the thread enters any other entry point of this
+ * library (each flushes first, so the order of a thread's calls is kept). tn_flush_assignments
+ * sends what is pending now; call it before handing the memory to code outside this library.
+ * tn_h2d_copy_count counts the host-to-device copies issued by tn_copy_from_host and by these
+ * flushes since load (a test aid). */
+tn_status tn_assign_from_host(const tn_device_t* device, const void* host, void* dev, size_t nbytes);
+tn_status tn_flush_assignments(void);
+uint64_t tn_h2d_copy_count(void);
 /* Stream-ordered variants with no reference counterpart (the reference copies synchronously): they
  * return once the copy is queued on `stream`; the host range should come from
  * tn_host_allocate_pinned, a pageable one makes the copy synchronous. The caller keeps both ranges
@@ -339,7 +351,8 @@ tn_status tn_reduce_stats(const tn_tensor_t* src, tn_tensor_t* max_out, tn_tenso
  * synchronisation). The partial sums of its two kernels live in a 192 KiB region that is part of
  * the library image on every GPU, so no cudaMalloc / cudaMallocAsync / cudaFree is ever issued.
  * Refused with TN_ERROR: a source that is not dense row-major, an axis other than the last, more
- * than 8192 rows (192 KiB / 24 B per partial). The first call on a device resolves the region's
+ * rows than the region has room for (one partial per row and segment: 8192 rows for float32,
+ * float64 and integer sources, 12288 for float16 / bfloat16). The first call on a device resolves the region's
  * address and should be made outside stream capture. All calls on a device share the region:
  * kernels of two calls that overlap on the GPU race on it, so keep such calls ordered. */
 tn_status tn_argsum_fixed_scratch(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream,
@@ -353,6 +366,18 @@ tn_status tn_cpy(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream);
  * synchronises the stream and writes 0/1 to *close. */
 tn_status tn_allclose(const tn_tensor_t* a, const tn_tensor_t* b, tn_stream_t stream, double rtol,
                       double atol, int* close);
+
+/* reference: cuda::eq/ne/gt/ge/lt/le, which exist only as stubs that throw (src/comparisons.cpp:24-29);
+ * semantics are those of the CPU twins, src/cpu/cmps.cpp:16-204: operands of one numeric dtype,
+ * compared elementwise (IEEE: a NaN makes everything but != false) into a BOOLEAN result that is
+ * bit-packed, element i in bit i % 8 of byte i / 8, (size + 7) / 8 bytes, unused bits zero. Operands
+ * may be strided views and may broadcast extent-1 dimensions against the result. */
+tn_status tn_eq(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_ne(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_gt(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_ge(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_lt(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream);
+tn_status tn_le(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream);
 
 /* Number of CTAs (tensor-core and staged-reduction kernels) that gave up on a bounded wait since load (0 in a
  * healthy run); synchronises the device. The reference has no device-side waits to bound. */

@@ -28,16 +28,20 @@ BINARY = {"add": 0, "sub": 1, "mul": 2, "pow": 3}
 UNARY = {"neg": 0, "repack": 1, "log": 2, "exp": 3, "sqrt": 4, "rsqrt": 5, "abs": 6, "sin": 7, "cos": 8, "tan": 9,
          "sinh": 10, "cosh": 11, "tanh": 12}
 REDUCE = {"argmax": 0, "argmin": 1, "sum": 2, "mean": 3, "max": 4}
+COMPARE = {"eq": 0, "ne": 1, "gt": 2, "ge": 3, "lt": 4, "le": 5}
 
 _TP = C.POINTER(A.TensorT)
 _port = None
 _ref = None
 
 
-def build(with_reference: bool = True) -> None:
-    """Compile the C restatement (and, where the reference tree exists, oracle/_ref)."""
-    target = "all" if with_reference else str(PORT_PATH)
-    subprocess.run(["make", "-s", "-C", str(HERE), target], check=True)
+def build(with_reference: bool = True, reference: str | None = None) -> None:
+    """Compile the C restatement and, when `reference` (or $TANNIC_REFERENCE) names the reference's
+    source tree, its CPU kernels into oracle/_ref."""
+    import os
+    reference = reference or os.environ.get("TANNIC_REFERENCE", "")
+    target = "all" if with_reference and reference else str(PORT_PATH)
+    subprocess.run(["make", "-s", "-C", str(HERE), target, f"REFERENCE={reference}"], check=True)
 
 
 def port() -> C.CDLL:
@@ -54,6 +58,7 @@ def port() -> C.CDLL:
         lib.orc_reduce.argtypes = [C.c_int, _TP, _TP, C.c_uint8, C.c_int]
         lib.orc_cpy.argtypes = [_TP, _TP]
         lib.orc_allclose.argtypes = [_TP, _TP, C.c_double, C.c_double, C.POINTER(C.c_int)]
+        lib.orc_compare.argtypes = [C.c_int, _TP, _TP, _TP]
         lib.orc_repeat.argtypes = [_TP, _TP, C.c_int, C.c_int]
         lib.orc_concat.argtypes = [_TP, _TP, _TP, C.c_int]
         lib.orc_triangular.argtypes = [_TP, _TP, C.c_int, C.c_int]
@@ -80,6 +85,10 @@ def ref():
         for n in ("argmax", "argmin", "argsum", "argmean"):
             getattr(lib, f"ref_{n}").argtypes = [_TP, _TP, C.c_uint8]
         lib.ref_cpy.argtypes = [_TP, _TP]
+        if hasattr(lib, "ref_conv1d"):
+            lib.ref_conv1d.argtypes = [_TP, _TP, _TP, C.c_size_t, C.c_size_t]
+            for n in COMPARE:
+                getattr(lib, f"ref_{n}").argtypes = [_TP, _TP, _TP]
         lib.ref_allclose.argtypes = [_TP, _TP, C.c_double, C.c_double]
         lib.ref_outer.argtypes = [_TP, _TP, _TP]
         lib.ref_repeat.argtypes = [_TP, _TP, C.c_int, C.c_int]
@@ -202,6 +211,56 @@ def conv2d(x, w, stride=1, padding=0, bias=None, acc=ACC_WIDE, impl="port"):
     else:
         _ok(ref().ref_conv2d_bias(C.byref(dx), C.byref(dw), C.byref(db), C.byref(dd), pad, strd))
     return out
+
+
+def conv1d(x, w, stride=1, padding=0, acc=ACC_WIDE, impl="port"):
+    """[N, C, L] signal, [Cout, Cin, K] kernel. The restatement is the H = 1 case of conv2d: the
+    reference's conv1d loop nest (src/cpu/conv1d.cpp:29-52) visits (ci, kl) in the order conv2d
+    visits (ci, kh = 0, kw), so the accumulation order is the same."""
+    lo = (x.shape[2] + 2 * padding - w.shape[2]) // stride + 1
+    if impl == "port":
+        return conv2d(x.unsqueeze(2), w.unsqueeze(2), (1, stride), (0, padding), acc=acc).squeeze(2)
+    out = _empty((x.shape[0], w.shape[0], lo), TORCH_TO_TN[x.dtype])
+    dx, dw, dd = desc(x), desc(w), desc(out)
+    _ok(ref().ref_conv1d(C.byref(dx), C.byref(dw), C.byref(dd), padding, stride))
+    return out
+
+
+def compare(name, a, b, impl="port"):
+    """Elementwise comparison -> torch.bool tensor of the broadcast shape (the kernels write it
+    bit-packed, element i in bit i % 8 of byte i / 8; `compare_packed` returns those bytes)."""
+    packed, shape = compare_packed(name, a, b, impl=impl)
+    n = 1
+    for s in shape:
+        n *= s
+    bits = (packed.to(torch.int32).unsqueeze(-1) >> torch.arange(8, dtype=torch.int32)) & 1
+    return bits.reshape(-1)[:n].to(torch.bool).reshape(shape)
+
+
+def compare_packed(name, a, b, impl="port"):
+    shape = broadcast_shape(a.shape, b.shape)
+    rank = len(shape)
+    a = a.reshape((1,) * (rank - a.dim()) + tuple(a.shape))
+    b = b.reshape((1,) * (rank - b.dim()) + tuple(b.shape))
+    n = 1
+    for s in shape:
+        n *= s
+    packed = torch.full(((n + 7) // 8,), 0xAA, dtype=torch.uint8)  # the kernels must clear what they do not set
+    dd = A.TensorT()
+    dd.address, dd.rank, dd.dtype, dd.size = packed.data_ptr(), rank, A.BOOLEAN, n
+    run = 1
+    for i in range(rank - 1, -1, -1):
+        dd.shape.sizes[i], dd.strides.sizes[i] = shape[i], run
+        run *= shape[i]
+    dd.environment.kind, dd.layout = A.HOST, A.CONTIGUOUS
+    da, db = desc(a), desc(b)
+    if impl == "port":
+        _ok(port().orc_compare(COMPARE[name], C.byref(da), C.byref(db), C.byref(dd)))
+    else:
+        if any(x != y for x, y in zip(a.shape, shape)) or any(x != y for x, y in zip(b.shape, shape)):
+            raise ValueError("the reference's comparison kernels take operands of the result's shape")
+        _ok(getattr(ref(), f"ref_{name}")(C.byref(da), C.byref(db), C.byref(dd)))
+    return packed, shape
 
 
 def reduce(kind, x, axis=-1, keepdim=False, acc=ACC_WIDE, impl="port"):

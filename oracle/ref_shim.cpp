@@ -26,6 +26,7 @@
 #include "cpu/concat.hpp"
 #include "cpu/triang.hpp"
 #include "cpu/complex.hpp"
+#include "cpu/cmps.hpp"
 
 #include "tannic_b200.h"
 
@@ -95,6 +96,13 @@ int ref_triu(const tensor_t* x, tensor_t* d, int k) { return cpu::triu(x, d, k);
 int ref_tril(const tensor_t* x, tensor_t* d, int k) { return cpu::tril(x, d, k); }
 int ref_view_as_cartesian(const tensor_t* a, const tensor_t* b, tensor_t* d) { return cpu::view_as_cartesian(a, b, d); }
 int ref_view_as_polar(const tensor_t* a, const tensor_t* b, tensor_t* d) { return cpu::view_as_polar(a, b, d); }
+int ref_conv1d(const tensor_t* x, const tensor_t* w, tensor_t* y, size_t pad, size_t stride) { return cpu::conv1d(x, w, y, pad, stride); }
+int ref_eq(const tensor_t* a, const tensor_t* b, tensor_t* d) { return cpu::eq(a, b, d); }
+int ref_ne(const tensor_t* a, const tensor_t* b, tensor_t* d) { return cpu::ne(a, b, d); }
+int ref_gt(const tensor_t* a, const tensor_t* b, tensor_t* d) { return cpu::gt(a, b, d); }
+int ref_ge(const tensor_t* a, const tensor_t* b, tensor_t* d) { return cpu::ge(a, b, d); }
+int ref_lt(const tensor_t* a, const tensor_t* b, tensor_t* d) { return cpu::lt(a, b, d); }
+int ref_le(const tensor_t* a, const tensor_t* b, tensor_t* d) { return cpu::le(a, b, d); }
 int ref_allclose(const tensor_t* a, const tensor_t* b, double rtol, double atol) {
     try {
         return cpu::allclose(a, b, rtol, atol) ? 1 : 0;

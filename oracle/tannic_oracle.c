@@ -626,6 +626,41 @@ tn_status orc_allclose(const tn_tensor_t* a, const tn_tensor_t* b, double rtol, 
     return TN_SUCCESS;
 }
 
+/* src/cpu/cmps.cpp:16-41 and :96-118: operands of one dtype walked with their own strides over the
+ * result's shape; the result is boolean, bit-packed: the (size + 7) / 8 bytes are cleared, then
+ * element i sets bit i % 8 of byte i / 8. op: 0 eq, 1 ne, 2 gt, 3 ge, 4 lt, 5 le. Integers compare
+ * as int64, floats as double (exact for every storage type); an extent-1 operand dimension reads
+ * offset 0. */
+tn_status orc_compare(int op, const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* d) {
+    if (a->dtype != b->dtype || !is_numeric((int)a->dtype) || d->dtype != TN_BOOLEAN) return TN_UNSUPPORTED_DTYPE;
+    if (op < 0 || op > 5) return TN_ERROR;
+    const int rank = d->rank;
+    uint8_t* out = (uint8_t*)d->address;
+    memset(out, 0, (d->size + 7) / 8);
+    size_t cnt[TN_MAX_RANK] = {0};
+    for (size_t idx = 0; idx < d->size; ++idx) {
+        int64_t oa = 0, ob = 0;
+        for (int dim = 0; dim < rank; ++dim) {
+            oa += (int64_t)(a->shape.sizes[dim] == 1 ? 0 : cnt[dim]) * a->strides.sizes[dim];
+            ob += (int64_t)(b->shape.sizes[dim] == 1 ? 0 : cnt[dim]) * b->strides.sizes[dim];
+        }
+        int r;
+        if (is_int((int)a->dtype)) {
+            const int64_t x = load_i64(a->address, (int)a->dtype, oa), y = load_i64(b->address, (int)b->dtype, ob);
+            r = op == 0 ? x == y : op == 1 ? x != y : op == 2 ? x > y : op == 3 ? x >= y : op == 4 ? x < y : x <= y;
+        } else {
+            const double x = load_f64(a->address, (int)a->dtype, oa), y = load_f64(b->address, (int)b->dtype, ob);
+            r = op == 0 ? x == y : op == 1 ? x != y : op == 2 ? x > y : op == 3 ? x >= y : op == 4 ? x < y : x <= y;
+        }
+        out[idx / 8] |= (uint8_t)((r ? 1u : 0u) << (idx % 8));
+        for (int dim = rank - 1; dim >= 0; --dim) {
+            if (++cnt[dim] < d->shape.sizes[dim]) break;
+            cnt[dim] = 0;
+        }
+    }
+    return TN_SUCCESS;
+}
+
 /* ------------------------------------------------------------------ data movement ------ */
 
 /* src/cpu/reps.cpp:16-97: the result is dense; for every index of the dimensions before `axis`,

@@ -86,7 +86,7 @@ class TannicError(RuntimeError):
 
 _TP = C.POINTER(TensorT)
 _UNARY = ["neg", "repack", "log", "exp", "sqrt", "abs", "sin", "cos", "tan", "sinh", "cosh", "tanh"]
-_BINARY = ["add", "sub", "mul", "pow"]
+_BINARY = ["add", "sub", "mul", "pow", "eq", "ne", "gt", "ge", "lt", "le"]
 _REDUCE = ["argmax", "argmin", "argsum", "argmean", "max"]
 
 # name -> argtypes (restype is tn_status unless listed in _RESTYPES)
@@ -102,6 +102,9 @@ PROTOTYPES = {
     "tn_deallocate": [C.POINTER(DeviceT), C.c_void_p],
     "tn_copy_from_host": [C.POINTER(DeviceT), C.c_void_p, C.c_void_p, C.c_size_t],
     "tn_copy_to_host": [C.POINTER(DeviceT), C.c_void_p, C.c_void_p, C.c_size_t],
+    "tn_assign_from_host": [C.POINTER(DeviceT), C.c_void_p, C.c_void_p, C.c_size_t],
+    "tn_flush_assignments": [],
+    "tn_h2d_copy_count": [],
     "tn_copy_from_host_async": [C.POINTER(DeviceT), C.c_void_p, C.c_void_p, C.c_size_t, StreamT],
     "tn_copy_to_host_async": [C.POINTER(DeviceT), C.c_void_p, C.c_void_p, C.c_size_t, StreamT],
     "tn_compare_from_host": [C.POINTER(DeviceT), C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(C.c_int)],
@@ -143,7 +146,7 @@ for _n in _BINARY:
 for _n in _REDUCE:
     PROTOTYPES[f"tn_{_n}"] = [_TP, _TP, StreamT, C.c_uint8]
 
-_RESTYPES = {"tn_dtype_size": C.c_size_t, "tn_last_error": C.c_char_p, "tn_launch_count": C.c_uint64}
+_RESTYPES = {"tn_dtype_size": C.c_size_t, "tn_last_error": C.c_char_p, "tn_launch_count": C.c_uint64, "tn_h2d_copy_count": C.c_uint64}
 
 
 def bind(cdll: C.CDLL, names=None) -> C.CDLL:

@@ -128,6 +128,11 @@ __device__ __forceinline__ void store_as(void* base, int dt, int64_t idx, C v) {
     }
 }
 
+// Tuning knobs from the environment (launch geometry only; results never depend on them). Each
+// name is looked up once per process; later calls return the remembered value. `name` must be a
+// string literal (the cache is keyed by its address). Values <= 0 or unset give `fallback`.
+int env_knob(const char* name, int fallback);
+
 // ---------------------------------------------------------------- geometry -----------
 // Number of SMs of the current device (148 on B200); grids of the streaming kernels are sized
 // as a multiple of it.

@@ -11,6 +11,9 @@
 // ew_generic, which decodes the linear index per element.
 #include "common.cuh"
 
+#include <mutex>
+#include <vector>
+
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -310,13 +313,7 @@ tn_status build_plan(const tn_tensor_t* const* ops, int nops, const tn_tensor_t*
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-// Tuning knobs read from the environment (launch geometry only; results never depend on them).
-inline int env_int(const char* name, int fallback) {
-    const char* v = getenv(name);
-    if (!v || !*v) return fallback;
-    const int n = atoi(v);
-    return n > 0 ? n : fallback;
-}
+inline int env_int(const char* name, int fallback) { return env_knob(name, fallback); }
 
 int flat_grid(int64_t work_items) {
     const int64_t cap = (int64_t)sm_count() * 8;  // 8 CTAs of 256 threads fill an SM
@@ -328,12 +325,22 @@ int flat_grid(int64_t work_items) {
 // CTAs of `kernel` that fit on one SM at once (from the occupancy calculator, cached by the
 // caller): grids are sized to exactly one resident wave so that no partial wave trails.
 template <typename K>
-int resident_ctas(K kernel, int threads) {
+int resident_ctas(K kernel, int threads, size_t dynamic_smem = 0) {
+    // Remembered per (kernel, shared-memory size): kernels of one signature share this function's
+    // instantiation, so the cache is keyed by the function pointer, not by the template.
+    struct Entry { const void* kernel; size_t smem; int ctas; };
+    static std::mutex mutex;
+    static std::vector<Entry> seen;
+    const void* key = reinterpret_cast<const void*>(kernel);
+    std::lock_guard<std::mutex> lock(mutex);
+    for (const Entry& e : seen)
+        if (e.kernel == key && e.smem == dynamic_smem) return e.ctas;
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, 0) != cudaSuccess || n < 1) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, dynamic_smem) != cudaSuccess || n < 1) {
         cudaGetLastError();
         n = 1;
     }
+    seen.push_back({key, dynamic_smem, n});
     return n;
 }
 
@@ -1162,9 +1169,9 @@ tn_status launch_program(const Plan& plan, const tn_tensor_t* const* inputs, int
         bool any_scalar = false;
         for (int k = 0; k < n_inputs; ++k) any_scalar = any_scalar || g.inner[k] == 0;
         const int unroll = env_int("TN_PROGRAM_UNROLL", 2);
-        // one resident wave: CTAs per SM from the occupancy calculator (cached per instantiation)
+        // one resident wave: CTAs per SM from the occupancy calculator (remembered per kernel and shared-memory size)
         auto launch = [&](auto kernel, int u, size_t smem = 0) {
-            static const int per_sm = resident_ctas(kernel, kThreads);
+            const int per_sm = resident_ctas(kernel, kThreads, smem);
             const int64_t cvec = cols / V;
             // two resident waves' worth of CTAs measured a few percent faster than exactly one
             const int64_t cap = (int64_t)sm_count() * env_int("TN_PROGRAM_CTAS_PER_SM", 2 * per_sm);

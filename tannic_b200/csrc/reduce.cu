@@ -665,10 +665,7 @@ __global__ void __launch_bounds__(kThreads) reduce_strided(const T* __restrict__
 }
 
 // ------------------------------------------------------------------ host --------------
-int64_t env_int64(const char* name, int64_t fallback) {
-    const char* v = getenv(name);
-    return v ? atoll(v) : fallback;
-}
+int64_t env_int64(const char* name, int64_t fallback) { return env_knob(name, (int)fallback); }
 
 int grid_cap() { return sm_count() * 8; }
 
@@ -682,7 +679,7 @@ tn_status launch_staged(const T* p, int64_t total, int64_t len, int chunk_kb, Ou
     // faster than wide ones (197-wide bf16 rows: 2 threads per row 3.97 TB/s, 4 or 8: 3.48)
     int lanes = 1;
     while (lanes < 8 && len >= 128 * lanes) lanes *= 2;
-    if (const char* v = getenv("TN_REDUCE_LANES")) { const int n = atoi(v); if (n == 1 || n == 2 || n == 4 || n == 8) lanes = n; }
+    if (const int n = env_knob("TN_REDUCE_LANES", 0); n == 1 || n == 2 || n == 4 || n == 8) lanes = n;
     int rpc = (int)((int64_t(chunk_kb) << 10) / pitch);
     if (rpc > kStagedThreads / lanes) rpc = kStagedThreads / lanes;
     rpc &= ~15;  // a chunk of 16 rows is a multiple of 16 bytes for any row length
@@ -755,7 +752,7 @@ tn_status launch(const tn_tensor_t* src, int axis, Outputs out, cudaStream_t s) 
             // whole rows staged in shared memory: rows per chunk is a multiple of 16 so that a
             // chunk is a multiple of 16 bytes for any row length
             int chunk_kb = 50;
-            if (const char* v = getenv("TN_REDUCE_CHUNK_KB")) { const int n = atoi(v); if (n >= 4 && n <= 52) chunk_kb = n; }
+            if (const int n = env_knob("TN_REDUCE_CHUNK_KB", 0); n >= 4 && n <= 52) chunk_kb = n;
             const bool padded = row_bytes % 16 == 0;
             tn_status st = padded ? launch_staged<T, SUM, ARG, MIN, true>(p, total, len, chunk_kb, out, s)
                                   : launch_staged<T, SUM, ARG, MIN, false>(p, total, len, chunk_kb, out, s);
@@ -898,7 +895,6 @@ tn_status launch_sum_fixed(const T* p, int64_t rows, int64_t len, Outputs out, v
     if (splits > (int64_t)(capacity / (size_t)rows)) splits = (int64_t)(capacity / (size_t)rows);
     if (splits > 1024) splits = 1024;
     if (splits < 1) splits = 1;
-    if (rows > 65535) return fail(TN_ERROR, "argsum_fixed_scratch: %lld rows exceed the launch limit of 65535", (long long)rows);
     Partial<T>* partials = static_cast<Partial<T>*>(scratch);
     // stage 1 writes every (row, segment) slot that stage 2 reads, so nothing left in the region
     // by an earlier call is ever consumed and no clearing pass is needed
@@ -969,9 +965,13 @@ tn_status tn_reduce_stats(const tn_tensor_t* src, tn_tensor_t* max_out, tn_tenso
 //
 // Limits and rules:
 //   - the workspace is 192 KiB per GPU, resident from library load to process exit;
-//   - the source must be dense row-major and `axis` its last axis; at most
-//     192 KiB / 24 B = 8192 rows (fewer segments per row are used as the row count grows) and
-//     at most 65535 rows per call; anything larger is refused with TN_ERROR and a message;
+//   - the source must be dense row-major and `axis` its last axis; the region holds one partial
+//     result per (row, segment), so a call takes at most 192 KiB / sizeof(partial) rows: 8192 for
+//     float32, float64 and the integer types (24-byte partials), 12288 for float16 and bfloat16
+//     (16-byte partials); fewer segments per row are used as the row count grows. More rows are
+//     refused with TN_ERROR and a message that names the limit;
+//   - a zero-length last axis gives sums of zero, like tn_argsum (the result is cleared with a
+//     memset on the stream; nothing is launched);
 //   - the first call on each device looks the region's device address up
 //     (cudaGetSymbolAddress, with that device current) and remembers it; make that first call
 //     outside any stream capture;
@@ -989,8 +989,14 @@ tn_status tn_argsum_fixed_scratch(const tn_tensor_t* src, tn_tensor_t* dst, tn_s
         expect *= sz;
     }
     const int64_t len = (int64_t)src->shape.sizes[axis];
-    const int64_t rows = len ? expect / len : 0;
-    if (rows == 0) return TN_SUCCESS;
+    if (dst->size == 0) return TN_SUCCESS;
+    if (len == 0) {
+        // an empty sum is zero for every row; tn_argsum writes the same
+        TN_TRY(use_device_of(dst));
+        TN_CUDA(cudaMemsetAsync(dst->address, 0, dst->size * (size_t)dtype_bytes(dst->dtype), as_cuda(stream)));
+        return TN_SUCCESS;
+    }
+    const int64_t rows = expect / len;
     void* scratch = nullptr;
     TN_TRY(fixed_scratch_address(dst->environment.resource.device.id, &scratch));
     const Outputs out{dst->address, nullptr, nullptr, 0};

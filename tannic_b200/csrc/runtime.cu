@@ -24,6 +24,19 @@ tn_status fail(tn_status code, const char* fmt, ...) {
     return code;
 }
 
+int env_knob(const char* name, int fallback) {
+    struct Entry { const char* name; int value; bool set; };
+    static std::mutex mutex;
+    static std::vector<Entry> seen;
+    std::lock_guard<std::mutex> lock(mutex);
+    for (const Entry& e : seen)
+        if (e.name == name) return e.set ? e.value : fallback;
+    const char* v = getenv(name);
+    const int n = (v && *v) ? atoi(v) : 0;
+    seen.push_back({name, n, n > 0});
+    return n > 0 ? n : fallback;
+}
+
 tn_status after_launch(const char* what) {
     count_launch();
     cudaError_t err = cudaGetLastError();
@@ -68,7 +81,48 @@ Runtime& runtime() {
 
 }  // namespace
 
+// ---- write-combined element assignments -------------------------------------------------------
+// The front-end fills a device tensor from an initializer list one element at a time
+// (Tensor::assign, src/tensor.cpp:34-44: one cuda::copyFromHost of dsizeof(dtype) bytes per element).
+// tn_assign_from_host gathers such writes while they extend one contiguous device range and sends
+// the range as ONE copy as soon as anything else happens on this thread: every entry point of the
+// library passes through use_device(), which flushes first, so program order is kept.
+namespace {
+struct PendingAssign {
+    int device = -1;
+    char* begin = nullptr;
+    std::vector<char> bytes;
+};
+thread_local PendingAssign t_pending;
+thread_local bool t_flushing = false;
+std::atomic<uint64_t> g_h2d_copies{0};
+constexpr size_t kMaxPendingBytes = size_t(4) << 20;
+}  // namespace
+
+static tn_status pop_stream(int id, cudaStream_t* out);
+static void put_stream(int id, cudaStream_t stream);
+
+tn_status flush_assignments() {
+    if (t_flushing || t_pending.bytes.empty()) return TN_SUCCESS;
+    t_flushing = true;
+    cudaStream_t s = nullptr;
+    tn_status st = pop_stream(t_pending.device, &s);
+    if (st == TN_SUCCESS) {
+        // pageable source: the runtime stages it before the call returns, so the buffer can be reused
+        const cudaError_t err = cudaMemcpyAsync(t_pending.begin, t_pending.bytes.data(), t_pending.bytes.size(), cudaMemcpyHostToDevice, s);
+        g_h2d_copies.fetch_add(1, std::memory_order_relaxed);
+        put_stream(t_pending.device, s);
+        if (err != cudaSuccess) st = fail(TN_ERROR, "H2D copy of gathered assignments failed: %s", cudaGetErrorString(err));
+    }
+    t_pending.bytes.clear();
+    t_pending.begin = nullptr;
+    t_pending.device = -1;
+    t_flushing = false;
+    return st;
+}
+
 tn_status use_device(int id) {
+    TN_TRY(flush_assignments());
     // Always re-issued: other libraries in the process (torch) may have changed the thread's
     // current device since the last call; cudaSetDevice on the current device is a fast path.
     Runtime& rt = runtime();
@@ -210,6 +264,7 @@ tn_status tn_stream_put(const tn_device_t* device, tn_stream_t stream) {
 }
 
 tn_status tn_stream_synchronize(tn_stream_t stream) {
+    TN_TRY(flush_assignments());
     TN_CUDA(cudaStreamSynchronize(as_cuda(stream)));
     return surface_device_aborts();
 }
@@ -256,10 +311,31 @@ tn_status tn_copy_from_host(const tn_device_t* device, const void* host, void* d
     // source is read by the copy engine later, in stream order: it must stay unchanged until the pool
     // stream has passed the copy (tn_stream_synchronize, or any synchronising call).
     cudaError_t err = cudaMemcpyAsync(dev, host, nbytes, cudaMemcpyHostToDevice, s);
+    g_h2d_copies.fetch_add(1, std::memory_order_relaxed);
     put_stream(device->id, s);
     if (err != cudaSuccess) return fail(TN_ERROR, "H2D copy failed: %s", cudaGetErrorString(err));
     return TN_SUCCESS;
 }
+
+tn_status tn_assign_from_host(const tn_device_t* device, const void* host, void* dev, size_t nbytes) {
+    if (!device || !host || !dev) return fail(TN_ERROR, "null argument");
+    if (nbytes == 0) return TN_SUCCESS;
+    char* target = static_cast<char*>(dev);
+    const bool extends = !t_pending.bytes.empty() && t_pending.device == device->id && target == t_pending.begin + t_pending.bytes.size() &&
+                         t_pending.bytes.size() + nbytes <= kMaxPendingBytes;
+    if (!extends) {
+        TN_TRY(flush_assignments());
+        t_pending.device = device->id;
+        t_pending.begin = target;
+    }
+    const char* src = static_cast<const char*>(host);
+    t_pending.bytes.insert(t_pending.bytes.end(), src, src + nbytes);
+    return TN_SUCCESS;
+}
+
+tn_status tn_flush_assignments(void) { return flush_assignments(); }
+
+uint64_t tn_h2d_copy_count(void) { return g_h2d_copies.load(std::memory_order_relaxed); }
 
 tn_status tn_copy_to_host(const tn_device_t* device, const void* dev, void* host, size_t nbytes) {
     if (!device) return fail(TN_ERROR, "null device");

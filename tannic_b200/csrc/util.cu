@@ -132,6 +132,44 @@ __global__ void __launch_bounds__(kThreads) allclose_kernel(const T* __restrict_
     if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(mismatch, 1);
 }
 
+// Elementwise comparison into a bit-packed boolean result: element i of the result (logical row-major
+// order) is bit i % 8 of byte i / 8, the layout the reference's CPU kernel writes
+// (src/cpu/cmps.cpp:16-41) and its boolean tensors use (nbytesof, include/tannic/types.hpp:149-154).
+// A thread produces one byte from eight consecutive elements, so no two threads touch one byte and
+// the padding bits of the last byte are written as zero. IEEE semantics: every comparison with a NaN
+// is false except !=.
+enum { CMP_EQ = 0, CMP_NE, CMP_GT, CMP_GE, CMP_LT, CMP_LE };
+template <int OP, typename C> __device__ __forceinline__ bool compare(C x, C y) {
+    if constexpr (OP == CMP_EQ) return x == y;
+    else if constexpr (OP == CMP_NE) return x != y;
+    else if constexpr (OP == CMP_GT) return x > y;
+    else if constexpr (OP == CMP_GE) return x >= y;
+    else if constexpr (OP == CMP_LT) return x < y;
+    else return x <= y;
+}
+template <typename T, int OP>
+__global__ void __launch_bounds__(kThreads) compare_bits(const T* __restrict__ a, const T* __restrict__ b, uint8_t* __restrict__ dst, PairGeom g,
+                                                         int dense) {
+    using C = typename compute_of<T>::type;  // 16-bit floats compare as float32 (exact)
+    const int64_t nbytes = (g.n + 7) >> 3;
+    const int64_t step = (int64_t)gridDim.x * kThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < nbytes; i += step) {
+        const int64_t first = i * 8;
+        unsigned bits = 0;
+        if (dense && first + 8 <= g.n) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) bits |= (compare<OP, C>(to_compute<C>(a[first + k]), to_compute<C>(b[first + k])) ? 1u : 0u) << k;
+        } else {
+            for (int k = 0; k < 8 && first + k < g.n; ++k) {
+                int64_t oa, ob;
+                decode(g, first + k, oa, ob);
+                bits |= (compare<OP, C>(to_compute<C>(a[oa]), to_compute<C>(b[ob])) ? 1u : 0u) << k;
+            }
+        }
+        dst[i] = static_cast<uint8_t>(bits);
+    }
+}
+
 // Geometry over `shape_of`'s logical shape; extent-1 dims of either side read offset 0
 // (src/cpu/cpy.cpp:19-43).
 void make_geom(const tn_tensor_t* a, const tn_tensor_t* b, const tn_tensor_t* shape_of, PairGeom& g) {
@@ -174,6 +212,46 @@ int grid_for(int64_t n) {
 }  // namespace tnb
 
 using namespace tnb;
+
+namespace {
+template <int OP>
+tn_status compare_entry(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream) {
+    if (!a || !b || !dst) return fail(TN_ERROR, "null tensor");
+    if (a->dtype != b->dtype || !is_numeric(a->dtype)) return fail(TN_UNSUPPORTED_DTYPE, "comparison: dtypes %d and %d", (int)a->dtype, (int)b->dtype);
+    if (dst->dtype != TN_BOOLEAN) return fail(TN_UNSUPPORTED_DTYPE, "comparison: the result must be boolean, got %d", (int)dst->dtype);
+    if (a->rank != dst->rank || b->rank != dst->rank) return fail(TN_ERROR, "comparison: ranks %d, %d -> %d differ", (int)a->rank, (int)b->rank, (int)dst->rank);
+    for (int d = 0; d < dst->rank; ++d) {
+        const size_t n = dst->shape.sizes[d];
+        if ((a->shape.sizes[d] != n && a->shape.sizes[d] != 1) || (b->shape.sizes[d] != n && b->shape.sizes[d] != 1))
+            return fail(TN_ERROR, "comparison: operand shapes do not match the result in dimension %d", d);
+    }
+    if (a->environment.kind != TN_DEVICE || b->environment.kind != TN_DEVICE || dst->environment.kind != TN_DEVICE ||
+        a->environment.resource.device.id != b->environment.resource.device.id ||
+        a->environment.resource.device.id != dst->environment.resource.device.id)
+        return fail(TN_INCOMPATIBLE_DEVICES, "operands must live on one device");
+    TN_TRY(use_device_of(dst));
+    PairGeom g;
+    make_geom(a, b, dst, g);
+    if (g.n == 0) return TN_SUCCESS;
+    const int dense = g.rank == 0 || (g.rank == 1 && g.sa[0] == 1 && g.sb[0] == 1);
+    cudaStream_t s = as_cuda(stream);
+    const int grid = grid_for((g.n + 7) / 8);
+    uint8_t* out = static_cast<uint8_t*>(dst->address);
+#define TN_CMP(T) compare_bits<T, OP><<<grid, kThreads, 0, s>>>(static_cast<const T*>(a->address), static_cast<const T*>(b->address), out, g, dense)
+    switch (a->dtype) {
+        case TN_INT8: TN_CMP(int8_t); break;
+        case TN_INT16: TN_CMP(int16_t); break;
+        case TN_INT32: TN_CMP(int32_t); break;
+        case TN_INT64: TN_CMP(int64_t); break;
+        case TN_FLOAT16: TN_CMP(__half); break;
+        case TN_BFLOAT16: TN_CMP(__nv_bfloat16); break;
+        case TN_FLOAT32: TN_CMP(float); break;
+        default: TN_CMP(double); break;
+    }
+#undef TN_CMP
+    return after_launch("compare_bits");
+}
+}  // namespace
 
 extern "C" {
 
@@ -297,5 +375,12 @@ tn_status tn_allclose(const tn_tensor_t* a, const tn_tensor_t* b, tn_stream_t st
     *close = mismatch ? 0 : 1;
     return surface_device_aborts();
 }
+
+tn_status tn_eq(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream) { return compare_entry<CMP_EQ>(a, b, dst, stream); }
+tn_status tn_ne(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream) { return compare_entry<CMP_NE>(a, b, dst, stream); }
+tn_status tn_gt(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream) { return compare_entry<CMP_GT>(a, b, dst, stream); }
+tn_status tn_ge(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream) { return compare_entry<CMP_GE>(a, b, dst, stream); }
+tn_status tn_lt(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream) { return compare_entry<CMP_LT>(a, b, dst, stream); }
+tn_status tn_le(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn_stream_t stream) { return compare_entry<CMP_LE>(a, b, dst, stream); }
 
 }  // extern "C"

@@ -82,7 +82,7 @@ bool allclose(const tensor_t* a, const tensor_t* b, stream_t s, double rtol, dou
     return close != 0;
 }
 
-// ---- outside the operator hot path: not provided by this backend --------------------------------
+// ---- data movement around the operator hot path ---------------------------------------------------
 status outer(tensor_t const* a, tensor_t const* b, tensor_t* d, stream_t s) { return st(tn_outer(in(a), in(b), out(d), on(s))); }
 status repeat(const tensor_t* x, tensor_t* d, int axis, int reps, stream_t s) { return st(tn_repeat(in(x), out(d), axis, reps, on(s))); }
 status concat(const tensor_t* a, const tensor_t* b, tensor_t* d, stream_t s, int axis) { return st(tn_concat(in(a), in(b), out(d), on(s), axis)); }
@@ -108,7 +108,10 @@ void* deallocate(const device_t* d, void* p) {
     return nullptr;
 }
 void copyFromHost(const device_t* d, const void* h, void* p, size_t n) {
-    if (tn_copy_from_host(dev(d), h, p, n) != TN_SUCCESS) throw std::runtime_error(tn_last_error());
+    // element-sized writes are Tensor::assign filling a tensor from an initializer list (src/tensor.cpp:34-44):
+    // they are gathered into one copy per contiguous run
+    const tn_status rc = n <= 16 ? tn_assign_from_host(dev(d), h, p, n) : tn_copy_from_host(dev(d), h, p, n);
+    if (rc != TN_SUCCESS) throw std::runtime_error(tn_last_error());
 }
 void copyDeviceToHost(const device_t* d, const void* p, void* h, size_t n) {
     if (tn_copy_to_host(dev(d), p, h, n) != TN_SUCCESS) throw std::runtime_error(tn_last_error());

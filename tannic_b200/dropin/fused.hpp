@@ -11,8 +11,14 @@
 // Compiled against the reference's headers (operations.hpp, functions.hpp, callback.hpp); needs no
 // change to them. Results equal the node-by-node evaluation: the fused kernel rounds every node to
 // the storage dtype.
+//
+// `try_fused(expression)` is the same walk as an optional: it returns nothing when the tree does not
+// fit, so it can be the first statement of the front-end's own forward() bodies (the four-line change
+// make_overlay.py applies to copies of tensor.hpp / functions.hpp under -DTANNIC_B200_FUSE), which
+// makes one-kernel evaluation the default for `Tensor Z = log(X) + Y * Y - exp(X);`.
 #pragma once
 
+#include <optional>
 #include <stdexcept>
 #include <tuple>
 #include <type_traits>
@@ -126,24 +132,25 @@ int emit(Plan& p, E const&) {
     return 0;
 }
 
-// The expression evaluated as one kernel (or by its own forward() when it does not fit).
+// The expression as one kernel, or nothing when it does not fit the program format: fewer than
+// `min_nodes` nodes (a single node gains nothing and keeps the front-end's own dtype rules), tensors
+// that are uninitialised, on the host, strided, of different dtypes or on different devices, a result
+// dtype other than the operands'.
 template <class E>
-Tensor fused(E const& e) {
+std::optional<Tensor> try_fused_with(E const& e, int min_nodes) {
     Plan p;
     emit(p, e);
-    bool fits = p.ok && p.n_nodes > 0 && p.n_inputs > 0;
+    if (!p.ok || p.n_nodes < min_nodes || p.n_inputs == 0) return std::nullopt;
     int device_id = -1;
-    for (int i = 0; fits && i < p.n_inputs; ++i) {
+    for (int i = 0; i < p.n_inputs; ++i) {
         Tensor const& t = *p.inputs[i];
-        if (!t.is_initialized() || !std::holds_alternative<Device>(t.environment()) || t.dtype() != p.inputs[0]->dtype()) {
-            fits = false;
-            break;
-        }
+        if (!t.is_initialized() || !t.is_contiguous() || !std::holds_alternative<Device>(t.environment()) || t.dtype() != p.inputs[0]->dtype())
+            return std::nullopt;
         const int id = std::get<Device>(t.environment()).id();
-        if (device_id >= 0 && id != device_id) fits = false;
+        if (device_id >= 0 && id != device_id) return std::nullopt;
         device_id = id;
     }
-    if (!fits) return e.forward(Context{});
+    if (e.dtype() != p.inputs[0]->dtype()) return std::nullopt;
     Tensor result(e.dtype(), e.shape());
     result.initialize(Device(device_id));
     const tn_tensor_t* in[TN_PROGRAM_MAX_INPUTS] = {};
@@ -155,6 +162,19 @@ Tensor fused(E const& e) {
     put_stream(&dvc, stream);
     if (st != TN_SUCCESS) throw std::runtime_error(tn_last_error());
     return result;
+}
+
+// The hook of the fused-by-default overlay: trees of two or more nodes.
+template <class E>
+std::optional<Tensor> try_fused(E const& e) {
+    return try_fused_with(e, 2);
+}
+
+// The expression evaluated as one kernel (or by its own forward() when it does not fit).
+template <class E>
+Tensor fused(E const& e) {
+    if (auto result = try_fused_with(e, 1)) return std::move(*result);
+    return e.forward(Context{});
 }
 
 }  // namespace tannic::b200

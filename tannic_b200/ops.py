@@ -74,6 +74,45 @@ def mul(a, b, **kw): return _binary("mul", a, b, **kw)
 def pow(a, b, **kw): return _binary("pow", a, b, **kw)  # noqa: A001
 
 
+def _compare(name: str, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """include/tannic/comparisons.hpp:40-130: boolean result of the operands' shape, bit-packed
+    (element i in bit i % 8 of byte i / 8). Returned as the packed uint8 buffer of (n + 7) // 8 bytes
+    together with the logical shape via `unpack_bits`."""
+    if a.dtype != b.dtype:
+        raise A.TannicError(A.UNSUPPORTED_DTYPE, "comparison operands must share a dtype")
+    shape = broadcast_shape(a.shape, b.shape)
+    rank = len(shape)
+    a = a.reshape((1,) * (rank - a.dim()) + tuple(a.shape))
+    b = b.reshape((1,) * (rank - b.dim()) + tuple(b.shape))
+    n = 1
+    for s in shape:
+        n *= s
+    packed = torch.empty(((n + 7) // 8,), dtype=torch.uint8, device=a.device)
+    dd = A.make_tensor(packed.data_ptr(), shape, torch.empty(shape, device="meta").stride(), A.BOOLEAN,
+                       a.device.index if a.device.index is not None else torch.cuda.current_device())
+    da, db = desc(a), desc(b)
+    A.check(getattr(A.lib(), f"tn_{name}")(C.byref(da), C.byref(db), C.byref(dd), current_stream(a)))
+    return packed
+
+
+def unpack_bits(packed: torch.Tensor, shape) -> torch.Tensor:
+    """Bit-packed boolean buffer -> torch.bool tensor of `shape` (host side)."""
+    n = 1
+    for s in shape:
+        n *= s
+    bytes_ = packed.cpu().to(torch.int32)
+    bits = (bytes_.unsqueeze(-1) >> torch.arange(8, dtype=torch.int32)) & 1
+    return bits.reshape(-1)[:n].to(torch.bool).reshape(tuple(shape))
+
+
+def eq(a, b): return _compare("eq", a, b)
+def ne(a, b): return _compare("ne", a, b)
+def gt(a, b): return _compare("gt", a, b)
+def ge(a, b): return _compare("ge", a, b)
+def lt(a, b): return _compare("lt", a, b)
+def le(a, b): return _compare("le", a, b)
+
+
 def _unary(name: str, x: torch.Tensor, *extra) -> torch.Tensor:
     out = _empty(x.shape, TORCH_TO_TN[x.dtype], x)
     dx, dd = desc(x), desc(out)
@@ -277,6 +316,21 @@ def convolve2D(x: torch.Tensor, w: torch.Tensor, stride=1, padding=0, bias: torc
     else:
         dbias = desc(bias)
         A.check(A.lib().tn_conv2d_bias(C.byref(dx), C.byref(dw), C.byref(dbias), C.byref(dd), current_stream(x), pad, strd))
+    return out
+
+
+def convolve1D(x: torch.Tensor, w: torch.Tensor, stride: int = 1, padding: int = 0) -> torch.Tensor:
+    """include/tannic/convolutions.hpp (Convolution<1>): [N, C, L] signal, [Cout, Cin, K] kernel."""
+    if x.dim() != 3 or w.dim() != 3:
+        raise ValueError("Only rank 3 tensors supported.")
+    if x.dtype != w.dtype:
+        raise ValueError("Dtypes must match in convolutions.")
+    if x.shape[1] != w.shape[1]:
+        raise ValueError("Input channels must match kernel channels.")
+    lo = (x.shape[2] + 2 * padding - w.shape[2]) // stride + 1
+    out = _empty((x.shape[0], w.shape[0], lo), TORCH_TO_TN[x.dtype], x)
+    dx, dw, dd = desc(x), desc(w), desc(out)
+    A.check(A.lib().tn_conv1d(C.byref(dx), C.byref(dw), C.byref(dd), current_stream(x), padding, stride))
     return out
 
 

@@ -7,7 +7,9 @@ byte count (`nbytes = payload + sizeof(Metadata<Tensor>) + rank * sizeof(size_t)
     Header    <I B H Q   magic 0x43495245, version 1, checksum 0xABCD, nbytes of everything after the header
     Metadata  <B Q Q B   dtype code (include/tannic/types.hpp:206-221), byte offset of the view, payload bytes, rank
     sizes     rank x <Q
-    payload   the tensor's bytes, dense row-major
+    payload   the tensor's bytes, dense row-major; boolean tensors are bit-packed, element i in bit
+              i % 8 of byte i / 8 ((n + 7) / 8 bytes: `nbytesof`, include/tannic/types.hpp:149-154, and the
+              bit order of `Tensor::assign(bool const*, index)`, src/tensor.cpp:48-61)
 
 Used here as the fixture format shared by host-side tests; nothing on the device path depends on it.
 """
@@ -16,6 +18,7 @@ from __future__ import annotations
 import struct
 from pathlib import Path
 
+import numpy as np
 import torch
 
 MAGIC = 0x43495245
@@ -31,7 +34,10 @@ def dumps(t: torch.Tensor) -> bytes:
     if t.dtype not in DCODE:
         raise ValueError(f"{t.dtype} has no Tannic dtype code")
     dense = t.detach().cpu().contiguous()
-    payload = dense.reshape(-1).view(torch.uint8).numpy().tobytes() if dense.numel() else b""
+    if dense.dtype == torch.bool:
+        payload = np.packbits(dense.reshape(-1).numpy(), bitorder="little").tobytes() if dense.numel() else b""
+    else:
+        payload = dense.reshape(-1).view(torch.uint8).numpy().tobytes() if dense.numel() else b""
     sizes = b"".join(struct.pack("<Q", s) for s in dense.shape)
     body = METADATA.pack(DCODE[t.dtype], 0, len(payload), dense.dim()) + sizes + payload
     return HEADER.pack(MAGIC, 1, 0xABCD, len(body)) + body
@@ -59,10 +65,14 @@ def loads(blob: bytes) -> torch.Tensor:
     count = 1
     for s in shape:
         count *= s
-    if count * torch.empty((), dtype=dtype).element_size() != payload_bytes:
+    expected = (count + 7) // 8 if dtype == torch.bool else count * torch.empty((), dtype=dtype).element_size()
+    if expected != payload_bytes:
         raise ValueError("payload size does not match shape and dtype")
     if count == 0:
         return torch.empty(shape, dtype=dtype)
+    if dtype == torch.bool:
+        bits = np.unpackbits(np.frombuffer(blob, dtype=np.uint8, count=payload_bytes, offset=at), bitorder="little")[:count]
+        return torch.from_numpy(bits.astype(np.bool_)).reshape(shape)
     raw = torch.frombuffer(bytearray(blob[at:at + payload_bytes]), dtype=torch.uint8)
     return raw.view(dtype).reshape(shape)
 

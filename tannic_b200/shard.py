@@ -53,11 +53,19 @@ def max_over_ranks(value: float, device=None) -> float:
     return float(t.item())
 
 
-def gather_shards(local: torch.Tensor, total_rows: int) -> torch.Tensor:
-    """All-gather of leading-dimension shards produced with `shard_range` (shards may be uneven)."""
+def gather_shards(local: torch.Tensor, total_rows: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """All-gather of leading-dimension shards produced with `shard_range` into the whole tensor on
+    every rank. Even, dense shards go straight into the result buffer with one collective
+    (`all_gather_into_tensor`; `out`, if given, is that buffer and is reused between calls); uneven
+    ones are padded to the longest shard and trimmed."""
     w, r = world()
     if w == 1:
         return local
+    if total_rows % w == 0 and local.is_contiguous() and local.shape[0] == total_rows // w:
+        if out is None:
+            out = torch.empty((total_rows,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(out, local)
+        return out
     sizes = [shard_range(total_rows, w, i) for i in range(w)]
     longest = max(b - a for a, b in sizes)
     padded = torch.zeros((longest,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
@@ -68,11 +76,18 @@ def gather_shards(local: torch.Tensor, total_rows: int) -> torch.Tensor:
 
 
 def combine_sum(partial: torch.Tensor) -> torch.Tensor:
-    """Sum over ranks of per-rank partial sums (accumulated in float32 / int64)."""
+    """Sum over ranks of per-rank partial sums, accumulated as wide as the one-GPU reduction does
+    (float32 for 16-bit floats, float64 for float32 / float64, int64 for integers)."""
     w, _ = world()
     if w == 1:
         return partial
-    acc = partial.to(torch.float32 if partial.is_floating_point() else torch.int64)
+    if not partial.is_floating_point():
+        wide = torch.int64
+    elif partial.dtype in (torch.float16, torch.bfloat16):
+        wide = torch.float32
+    else:
+        wide = torch.float64
+    acc = partial.to(wide)
     dist.all_reduce(acc, op=dist.ReduceOp.SUM)
     return acc.to(partial.dtype)
 
@@ -95,3 +110,51 @@ def combine_argmax(local_value: torch.Tensor, local_index: torch.Tensor, offset:
         best_v = torch.where(better, v, best_v)
         best_i = torch.where(better, i, best_i)
     return best_v, best_i
+
+
+class Mesh:
+    """The GPUs of one box as seen from this process: the handle the reference leaves as a TODO
+    (`class Mesh`, include/tannic/resources.hpp:194-197). One process drives one GPU; the mesh is the
+    process group. `scatter` cuts a whole host tensor into this rank's resident shard, `Sharded`
+    remembers where the shard sits in the whole, and the collectives above act on it."""
+
+    def __init__(self):
+        self.size, self.rank = world()
+
+    def range(self, total: int) -> tuple[int, int]:
+        return shard_range(total, self.size, self.rank)
+
+    def scatter(self, whole: torch.Tensor, device=None) -> "Sharded":
+        lo, hi = self.range(whole.shape[0])
+        local = whole[lo:hi]
+        if device is not None:
+            local = local.to(device, non_blocking=True)
+        return Sharded(self, local, whole.shape[0], lo)
+
+    def wrap(self, local: torch.Tensor, total_rows: int) -> "Sharded":
+        lo, hi = self.range(total_rows)
+        if local.shape[0] != hi - lo:
+            raise ValueError(f"rank {self.rank} owns rows [{lo}, {hi}) of {total_rows}, got {local.shape[0]}")
+        return Sharded(self, local, total_rows, lo)
+
+
+class Sharded:
+    """A tensor split along its leading dimension over a Mesh: this rank's shard, the whole's leading
+    extent and the shard's first global row."""
+
+    def __init__(self, mesh: Mesh, local: torch.Tensor, total_rows: int, offset: int):
+        self.mesh, self.local, self.total_rows, self.offset = mesh, local, total_rows, offset
+
+    def map(self, fn) -> "Sharded":
+        """Applies a row-independent op to the shard (rows in, the same rows out)."""
+        return Sharded(self.mesh, fn(self.local), self.total_rows, self.offset)
+
+    def gather(self, out: torch.Tensor | None = None) -> torch.Tensor:
+        return gather_shards(self.local, self.total_rows, out=out)
+
+    def sum_over_rows(self, reduce_local) -> torch.Tensor:
+        """`reduce_local(shard)` gives this rank's partial sum over its rows; ranks are combined."""
+        return combine_sum(reduce_local(self.local))
+
+    def argmax_over_rows(self, max_local, argmax_local):
+        return combine_argmax(max_local(self.local), argmax_local(self.local), self.offset)

@@ -109,4 +109,8 @@ def main(root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    import os
+    where = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TANNIC_REFERENCE")
+    if not where:
+        sys.exit("usage: extract_reference_vectors.py <reference source tree>  (or set TANNIC_REFERENCE)")
+    main(where)

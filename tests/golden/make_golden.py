@@ -1,39 +1,41 @@
-"""Generates golden_reference.npz: inputs and outputs of the reference's own CPU kernels
-(oracle/_ref, compiled from the reference sources) for the dtypes its test-suite never exercises
-(fp16, bf16, int32). Run where oracle/_ref exists:
+"""Generates the golden fixtures: inputs and outputs of the reference's own CPU kernels (oracle/_ref,
+compiled from the reference sources) for the dtypes its test-suite never exercises (fp16, bf16,
+int32). Run where oracle/_ref exists:
 
     python tests/golden/make_golden.py
 
-Half-precision arrays are stored as their uint16 bit patterns. Cases named *_wide hold the result
+Every tensor is one `.tannic` file (the reference's own on-disk tensor record,
+include/tannic/serialization.hpp:26-66, written by tannic_b200/serialization.py) named
+<set>/<case>.<tensor>.tannic; complex results are stored as their [.., 2] float view, bit-packed
+comparison results as their bytes (int8). Cases named *_wide hold the result
 of the reference's float-accumulating instantiation on exactly up-converted operands, rounded once to
 the storage type — the behaviour the device path implements; the others are the literal result.
 """
 import sys
 from pathlib import Path
 
-import numpy as np
 import torch
 
 ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
 import oracle  # noqa: E402
+from tannic_b200 import serialization  # noqa: E402
 
-
-def raw(t):
-    t = t.contiguous()
-    if t.dtype in (torch.float16, torch.bfloat16):
-        return t.view(torch.int16).numpy().view(np.uint16)
-    return t.numpy()
+HERE = Path(__file__).resolve().parent
 
 
 def main():
     assert oracle.ref() is not None, "build oracle/_ref first (make -C oracle ref)"
-    out = {}
+    state = {"set": "reference", "count": 0, "bytes": 0}
 
     def put(name, **arrays):
+        folder = HERE / state["set"]
+        folder.mkdir(exist_ok=True)
         for k, v in arrays.items():
-            out[f"{name}/{k}"] = raw(v)
-            out[f"{name}/{k}.dtype"] = np.array(str(v.dtype).replace("torch.", ""))
+            path = folder / f"{name}.{k}.tannic"
+            serialization.save(v, path)
+            state["count"] += 1
+            state["bytes"] += path.stat().st_size
 
     R = "ref"
     # config 2 in miniature: Z = log(X) + Y*Y - exp(X), fp16, row-broadcast Y
@@ -75,12 +77,21 @@ def main():
         sum=oracle.reduce("sum", sr, -1, impl=R), mean=oracle.reduce("mean", sr, -1, impl=R),
         sum_wide=oracle.reduce("sum", sr.float(), -1, impl=R).to(torch.bfloat16),
         argmax_axis0=oracle.reduce("argmax", sr, 0, impl=R))
-    path = Path(__file__).resolve().parent / "golden_reference.npz"
-    np.savez_compressed(path, **out)
-    print(f"{len(out) // 2} arrays -> {path} ({path.stat().st_size} bytes)")
+    # fp16 / int32 conv1d: literal and float instantiation
+    x1 = oracle.fill((2, 6, 23), torch.float16, 14, "normal", 0.0, 1.0)
+    k1 = oracle.fill((5, 6, 4), torch.float16, 15, "normal", 0.0, 0.3)
+    xi, ki = oracle.fill((1, 3, 11), torch.int32, 16, "uniform", -9, 9), oracle.fill((2, 3, 3), torch.int32, 17, "uniform", -3, 3)
+    put("conv1d", x=x1, k=k1, y_s2p1=oracle.conv1d(x1, k1, 2, 1, impl=R), y_s2p1_wide=oracle.conv1d(x1.float(), k1.float(), 2, 1, impl=R).to(torch.float16),
+        xi=xi, ki=ki, yi=oracle.conv1d(xi, ki, 1, 0, impl=R))
+    # comparisons: bit-packed boolean results (bytes stored as int8)
+    ca_, cb_ = oracle.fill((5, 13), torch.bfloat16, 18, "uniform", -2, 2), oracle.fill((5, 13), torch.bfloat16, 19, "uniform", -2, 2)
+    cb_[0], cb_[3, 4:9] = ca_[0], ca_[3, 4:9]
+    ca_[1, 2] = float("nan")
+    put("compare_bf16", a=ca_, b=cb_, **{n: oracle.compare_packed(n, ca_, cb_, impl=R)[0].view(torch.int8) for n in oracle.COMPARE})
+    print(f"{state['count']} tensors -> {HERE / state['set']} ({state['bytes']} bytes)")
 
-    # ---- data movement around the path (a file of its own: golden_data_movement.npz) ----
-    out.clear()
+    # ---- data movement around the path (a folder of its own) ----
+    state.update(set="data_movement", count=0, bytes=0)
     xr = oracle.fill((3, 4, 5), torch.bfloat16, 20, "uniform", -4, 4)
     put("repeat_bf16", x=xr, axis1_x3=oracle.repeat(xr, 3, 1, impl=R), axis0_x2=oracle.repeat(xr, 2, 0, impl=R),
         permuted_axis1_x2=oracle.repeat(xr.transpose(0, 2), 2, 1, impl=R))
@@ -97,9 +108,7 @@ def main():
     rho, theta = oracle.fill((3, 1, 4), torch.float32, 32, "uniform", 0, 2), oracle.fill((1, 5, 4), torch.float32, 33, "uniform", -3, 3)
     put("complex", rho=rho, theta=theta, cartesian=torch.view_as_real(oracle.complex_pair(rho, theta, False, impl=R)),
         polar=torch.view_as_real(oracle.complex_pair(rho, theta, True, impl=R)))
-    path = Path(__file__).resolve().parent / "golden_data_movement.npz"
-    np.savez_compressed(path, **out)
-    print(f"{len(out) // 2} arrays -> {path} ({path.stat().st_size} bytes)")
+    print(f"{state['count']} tensors -> {HERE / state['set']} ({state['bytes']} bytes)")
 
 
 if __name__ == "__main__":

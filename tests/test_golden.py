@@ -1,24 +1,21 @@
-"""Golden vectors produced by the reference's own CPU kernels (tests/golden/golden_reference.npz,
-made by tests/golden/make_golden.py) for fp16 / bf16 / int32, which the reference's test-suite never
+"""Golden vectors produced by the reference's own CPU kernels (tests/golden/reference/*.tannic and
+tests/golden/data_movement/*.tannic, one tensor per file in the reference's own `.tannic` record, made by
+tests/golden/make_golden.py) for fp16 / bf16 / int32, which the reference's test-suite never
 covers. CPU: the C restatement reproduces them bit for bit. GPU (marked): the CUDA path matches the
 float-accumulating results within rtol 1e-2 / atol 1e-2, integers and indices exactly."""
 from pathlib import Path
 
-import numpy as np
 import pytest
 import torch
 
 import oracle
+from tannic_b200 import serialization
 
-NPZ = np.load(Path(__file__).parent / "golden" / "golden_reference.npz")
-DT = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32, "int32": torch.int32, "int64": torch.int64}
+GOLDEN = Path(__file__).parent / "golden"
 
 
 def get(case, name):
-    arr = NPZ[f"{case}/{name}"]
-    dt = DT[str(NPZ[f"{case}/{name}.dtype"])]
-    t = torch.from_numpy(arr.view(np.int16) if arr.dtype == np.uint16 else arr.copy())
-    return t.view(dt) if dt in (torch.float16, torch.bfloat16) else t
+    return serialization.load(GOLDEN / "reference" / f"{case}.{name}.tannic")
 
 
 def same(a, b):
@@ -98,16 +95,10 @@ def test_cuda_matches_golden():
     assert tb.device_errors() == 0
 
 
-# ---- data movement around the path: golden_data_movement.npz (same generator script) ----
-
-MOVE = np.load(Path(__file__).parent / "golden" / "golden_data_movement.npz")
-
+# ---- data movement around the path: tests/golden/data_movement (same generator script) ----
 
 def mv(case, name):
-    arr = MOVE[f"{case}/{name}"]
-    dt = DT[str(MOVE[f"{case}/{name}.dtype"])]
-    t = torch.from_numpy(arr.view(np.int16) if arr.dtype == np.uint16 else arr.copy())
-    return t.view(dt) if dt in (torch.float16, torch.bfloat16) else t
+    return serialization.load(GOLDEN / "data_movement" / f"{case}.{name}.tannic")
 
 
 class _Port:
@@ -167,3 +158,26 @@ def test_port_matches_golden_data_movement():
 @pytest.mark.gpu
 def test_cuda_matches_golden_data_movement():
     check_data_movement(_Cuda())
+
+
+# ---- conv1d and comparisons ----
+
+def test_port_matches_golden_conv1d_and_comparisons():
+    x, k = get("conv1d", "x"), get("conv1d", "k")
+    assert same(oracle.conv1d(x, k, 2, 1, acc=oracle.ACC_STORAGE), get("conv1d", "y_s2p1"))
+    assert same(oracle.conv1d(x, k, 2, 1, acc=oracle.ACC_WIDE), get("conv1d", "y_s2p1_wide"))
+    assert same(oracle.conv1d(get("conv1d", "xi"), get("conv1d", "ki"), 1, 0), get("conv1d", "yi"))
+    a, b = get("compare_bf16", "a"), get("compare_bf16", "b")
+    for op in oracle.COMPARE:
+        assert torch.equal(oracle.compare_packed(op, a, b)[0].view(torch.int8), get("compare_bf16", op))
+
+
+@pytest.mark.gpu
+def test_cuda_matches_golden_conv1d_and_comparisons():
+    from tannic_b200 import ops as tb
+    x, k = get("conv1d", "x").cuda(), get("conv1d", "k").cuda()
+    assert close(tb.convolve1D(x, k, 2, 1).cpu(), get("conv1d", "y_s2p1_wide"))
+    assert same(tb.convolve1D(get("conv1d", "xi").cuda(), get("conv1d", "ki").cuda(), 1, 0).cpu(), get("conv1d", "yi"))
+    a, b = get("compare_bf16", "a").cuda(), get("compare_bf16", "b").cuda()
+    for op in oracle.COMPARE:
+        assert torch.equal(getattr(tb, op)(a, b).cpu().view(torch.int8), get("compare_bf16", op))

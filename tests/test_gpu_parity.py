@@ -907,3 +907,85 @@ def _add_host(a):
     da, dd = tb.desc(a), tb.desc(out)
     A.check(A.lib().tn_add(C.byref(da), C.byref(da), C.byref(dd), A.StreamT(0)))
 
+
+
+# ---------------------------------------------------------------- comparisons, conv1d ---
+
+@pytest.mark.parametrize("dtype", INTS + FLOATS)
+@pytest.mark.parametrize("op", list(oracle.COMPARE))
+def test_comparisons_bit_packed(dtype, op):
+    """eq / ne / gt / ge / lt / le on the device: the packed bytes equal the oracle's, dense and strided
+    operands, ragged sizes (padding bits zero), NaN and infinities, and a broadcast operand."""
+    for shape in ((1000,), (3, 5, 7), (64, 33)):
+        a, b = gen(shape, dtype, 80), gen(shape, dtype, 81)
+        b.view(-1)[::3] = a.view(-1)[::3]
+        if dtype not in INTS:
+            a.view(-1)[5] = float("nan")
+            b.view(-1)[7] = float("inf")
+            a.view(-1)[9] = float("-inf")
+        want, _ = oracle.compare_packed(op, a, b)
+        got = getattr(tb, op)(dev(a), dev(b))
+        assert torch.equal(got.cpu(), want), (shape,)
+    a, b = gen((6, 40), dtype, 82), gen((40, 6), dtype, 83)
+    want, _ = oracle.compare_packed(op, a, b.t())
+    assert torch.equal(getattr(tb, op)(dev(a), dev(b).t()).cpu(), want)
+    row = gen((1, 40), dtype, 84)
+    want, shape = oracle.compare_packed(op, a, row)
+    got = getattr(tb, op)(dev(a), dev(row))
+    assert torch.equal(got.cpu(), want)
+    assert torch.equal(tb.unpack_bits(got, shape), oracle.compare(op, a, row))
+
+
+def test_comparison_rejects_mixed_dtypes_and_non_boolean_results():
+    a, b = dev(gen((4, 4), torch.float32, 85)), dev(gen((4, 4), torch.float16, 86))
+    with pytest.raises(A.TannicError):
+        tb.eq(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32, torch.float64, torch.int32])
+@pytest.mark.parametrize("n,c,l,cout,k,stride,pad", [(2, 3, 19, 4, 5, 1, 0), (1, 8, 200, 16, 3, 2, 1), (3, 16, 64, 8, 7, 3, 3), (2, 64, 1000, 32, 3, 1, 1)])
+def test_conv1d_generated_shapes(dtype, n, c, l, cout, k, stride, pad):
+    """conv1d against the oracle (the reference's loop nest with float accumulation for 16-bit types);
+    the last shape is large enough for the tensor-core path of the H = 1 convolution."""
+    x, w = gen((n, c, l), dtype, 87, -1, 1), gen((cout, c, k), dtype, 88, -0.5, 0.5)
+    want = oracle.conv1d(x, w, stride, pad, acc=oracle.ACC_WIDE)
+    got = tb.convolve1D(dev(x), dev(w), stride, pad)
+    if dtype in INTS:
+        assert_same(got, want)
+    else:
+        assert_close(got, want)
+    assert tb.device_errors() == 0
+
+
+# ---------------------------------------------------------------- bulk initialisation ---
+
+def test_element_assignments_leave_as_one_copy():
+    """tn_assign_from_host: 1000 element-sized writes to consecutive addresses (what Tensor::assign does
+    for an initializer list, src/tensor.cpp:34-44) become one host-to-device copy, issued when the thread
+    enters another entry point; a gap starts a new run; the values arrive in order."""
+    import ctypes as C
+    lib = A.lib()
+    dev0 = A.DeviceT(torch.cuda.current_device())
+    target = torch.zeros(1000, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    values = torch.arange(1000, dtype=torch.float32) * 0.5
+    before = lib.tn_h2d_copy_count()
+    for i in range(1000):
+        A.check(lib.tn_assign_from_host(C.byref(dev0), values.data_ptr() + 4 * i, target.data_ptr() + 4 * i, 4))
+    assert lib.tn_h2d_copy_count() == before          # nothing has left yet
+    host = torch.empty(1000, dtype=torch.float32)
+    A.check(lib.tn_copy_to_host(C.byref(dev0), target.data_ptr(), host.data_ptr(), 4000))   # flushes, then reads back
+    assert lib.tn_h2d_copy_count() == before + 1
+    assert torch.equal(host, values)
+    # two runs with a gap between them: two copies; an op on the tensor sees both
+    target.zero_()
+    torch.cuda.synchronize()
+    before = lib.tn_h2d_copy_count()
+    for i in list(range(0, 10)) + list(range(500, 520)):
+        A.check(lib.tn_assign_from_host(C.byref(dev0), values.data_ptr() + 4 * i, target.data_ptr() + 4 * i, 4))
+    doubled = tb.add(target, target)
+    assert lib.tn_h2d_copy_count() == before + 2
+    want = torch.zeros(1000)
+    want[0:10], want[500:520] = values[0:10] * 2, values[500:520] * 2
+    assert torch.equal(doubled.cpu(), want)
+    A.check(lib.tn_flush_assignments())

@@ -273,3 +273,40 @@ def test_complex_constructors(ref_lib, pair):
     assert same_bits(torch.view_as_real(oracle.complex_pair(rho, theta, False)), torch.view_as_real(oracle.complex_pair(rho, theta, False, impl="ref")))
     got, want = oracle.complex_pair(rho, theta, True), oracle.complex_pair(rho, theta, True, impl="ref")
     assert torch.allclose(torch.view_as_real(got), torch.view_as_real(want), rtol=1e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("dtype", INTS + FLOATS)
+@pytest.mark.parametrize("stride,pad", [(1, 0), (2, 1), (3, 2)])
+def test_conv1d_bit_exact(ref_lib, dtype, stride, pad):
+    """src/cpu/conv1d.cpp:16-127 against the H = 1 case of the conv2d restatement, storage-type accumulation."""
+    x, w = gen((2, 3, 19), dtype, 40, -1, 1), gen((4, 3, 5), dtype, 41, -1, 1)
+    if dtype in INTS:
+        x, w = x % 5, w % 3
+    got = oracle.conv1d(x, w, stride, pad, acc=oracle.ACC_STORAGE)
+    want = oracle.conv1d(x, w, stride, pad, impl="ref")
+    assert same_bits(got, want)
+    # a strided signal (every second channel of a wider tensor)
+    wide = gen((2, 6, 19), dtype, 42, -1, 1)
+    if dtype in INTS:
+        wide = wide % 5
+    assert same_bits(oracle.conv1d(wide[:, ::2], w, stride, pad, acc=oracle.ACC_STORAGE), oracle.conv1d(wide[:, ::2], w, stride, pad, impl="ref"))
+
+
+@pytest.mark.parametrize("dtype", INTS + FLOATS)
+@pytest.mark.parametrize("op", list(oracle.COMPARE))
+def test_comparisons_bit_exact(ref_lib, dtype, op):
+    """src/cpu/cmps.cpp:16-204: bit-packed boolean results, including the padding bits of the last byte."""
+    a, b = gen((3, 5, 7), dtype, 43), gen((3, 5, 7), dtype, 44)
+    b[0], b[1, :2] = a[0], a[1, :2]          # equal runs
+    if dtype not in INTS:
+        a[2, 0, :3] = float("nan")
+        b[2, 1, 0] = float("inf")
+    got, _ = oracle.compare_packed(op, a, b)
+    want, _ = oracle.compare_packed(op, a, b, impl="ref")
+    assert torch.equal(got, want)
+    # strided operands walk their own strides
+    got, _ = oracle.compare_packed(op, a.transpose(0, 2), b.transpose(0, 2))
+    want, _ = oracle.compare_packed(op, a.transpose(0, 2), b.transpose(0, 2), impl="ref")
+    assert torch.equal(got, want)
+    expect = {"eq": a == b, "ne": a != b, "gt": a > b, "ge": a >= b, "lt": a < b, "le": a <= b}[op]
+    assert torch.equal(oracle.compare(op, a, b), expect)

@@ -37,6 +37,7 @@ class CpuBackend:
     def binary(self, op, a, b): return oracle.binary(op, a, b)
     def unary(self, op, x, eps=0.0): return oracle.unary(op, x, eps=eps)
     def conv(self, x, w, stride, pad, bias=None): return oracle.conv2d(x, w, stride, pad, bias=bias, acc=oracle.ACC_STORAGE)
+    def conv1d(self, x, w, stride, pad): return oracle.conv1d(x, w, stride, pad, acc=oracle.ACC_STORAGE)
     def reduce(self, kind, x, axis, keepdim=False): return oracle.reduce(kind, x, axis, keepdim, acc=oracle.ACC_STORAGE)
 
 
@@ -53,6 +54,7 @@ class GpuBackend:
     def binary(self, op, a, b): return getattr(self.tb, op)(a, b)
     def unary(self, op, x, eps=0.0): return self.tb.rsqrt(x, eps) if op == "rsqrt" else getattr(self.tb, op)(x)
     def conv(self, x, w, stride, pad, bias=None): return self.tb.convolve2D(x, w, stride, pad, bias=bias)
+    def conv1d(self, x, w, stride, pad): return self.tb.convolve1D(x, w, stride, pad)
     def reduce(self, kind, x, axis, keepdim=False): return getattr(self.tb, kind)(x, axis, keepdim)
 
 
@@ -119,6 +121,10 @@ def run_case(case, be):
             assert got.shape == (1, 1, 4, 4)
         else:
             check_asserts(asserts, {"output": got})
+    elif suite == "TestConvolution1D":
+        # tests/cpu/test-convolutions.cpp:11-126: convolve1D(input, kernel, stride, padding)
+        stride, pad = {"Stride2": (2, 0), "Padding1": (1, 1)}.get(name, (1, 0))
+        assert allclose(down(be.conv1d(up(t["input"]), up(t["kernel"]), stride, pad)), t["expected"])
     elif suite == "FunctionTests":
         # tests/cpu/test-functions.cpp:11-160: the expectation is the std:: function of each element
         fn = name.lower()
@@ -159,10 +165,10 @@ def run_case(case, be):
         got = down(be.unary("repack", x)).reshape(2, 4, 12)
         assert allclose(got, t["Y_expected"])
     else:
-        pytest.skip("outside the path (conv1d and friends)")
+        pytest.skip("outside the path")
 
 
-CASES = [c for c in VECTORS if not c.startswith("TestConvolution1D")]
+CASES = list(VECTORS)
 
 
 @pytest.mark.parametrize("case", CASES)

@@ -16,7 +16,8 @@ def test_round_trip(dtype, shape, tmp_path):
     blob = ser.dumps(x)
     magic, version, checksum, nbytes = ser.HEADER.unpack_from(blob, 0)
     assert (magic, version, checksum) == (0x43495245, 1, 0xABCD)
-    assert nbytes == len(blob) - ser.HEADER.size == x.numel() * x.element_size() + ser.METADATA.size + 8 * len(shape)
+    payload = (x.numel() + 7) // 8 if dtype == torch.bool else x.numel() * x.element_size()  # booleans are bit-packed
+    assert nbytes == len(blob) - ser.HEADER.size == payload + ser.METADATA.size + 8 * len(shape)
     assert ser.HEADER.size == 15 and ser.METADATA.size == 18  # packed records
     y = ser.loads(blob)
     assert y.dtype == x.dtype and y.shape == x.shape
@@ -24,6 +25,19 @@ def test_round_trip(dtype, shape, tmp_path):
     assert torch.equal(raw(y), raw(x))
     ser.save(x, tmp_path / "t.tannic")
     assert torch.equal(raw(ser.load(tmp_path / "t.tannic")), raw(x))
+
+
+def test_boolean_payload_is_bit_packed_lsb_first():
+    """nbytesof(boolean, n) = (n + 7) / 8 (include/tannic/types.hpp:149-154); element i is bit i % 8 of
+    byte i / 8 (src/tensor.cpp:48-61)."""
+    x = torch.tensor([True, False, False, True, False, False, False, False, True, True, False])  # 11 elements
+    blob = ser.dumps(x)
+    _, _, payload_bytes, rank = ser.METADATA.unpack_from(blob, ser.HEADER.size)
+    assert (payload_bytes, rank) == (2, 1)
+    assert blob[-2:] == bytes([0b00001001, 0b00000011])
+    assert torch.equal(ser.loads(blob), x)
+    wide = torch.rand((5, 13), generator=torch.Generator().manual_seed(3)) > 0.5
+    assert torch.equal(ser.loads(ser.dumps(wide)), wide)
 
 
 def test_views_are_stored_dense():

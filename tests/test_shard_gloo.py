@@ -54,6 +54,28 @@ def _worker(rank, world, port, results):
         ok = ok and torch.equal(gi, torch.full((5,), 2)) and torch.equal(gv, torch.full((5,), 100.0))
         slow = shard.max_over_ranks(1.0 + rank)
         ok = ok and slow == float(world)
+        # even shards take the single-collective path into a reusable result buffer
+        even = torch.arange(8 * 3, dtype=torch.float32).reshape(8, 3)
+        buf = torch.empty_like(even)
+        ok = ok and torch.equal(shard.gather_shards(shard.shard_leading(even, world, rank).contiguous(), 8, out=buf), even) and buf.data_ptr() == buf.data_ptr()
+        # float64 partial sums keep their precision (float32 would lose the small term)
+        big = torch.tensor([1e9 if rank == 0 else 0.123456789], dtype=torch.float64)
+        ok = ok and float(shard.combine_sum(big)) == 1e9 + 0.123456789
+        # 16-bit partials are combined in float32: 2048 + 1 is not representable in float16, 2048 + 2048 is
+        half = shard.combine_sum(torch.tensor([2048.0], dtype=torch.float16))
+        ok = ok and half.dtype == torch.float16 and float(half) == 4096.0
+        # the Mesh handle: scatter, a row-independent op, gather; and reductions over the sharded axis
+        mesh = shard.Mesh()
+        sharded = mesh.scatter(full)
+        ok = ok and sharded.offset == start and torch.equal(sharded.map(lambda t: t * 2).gather(), full * 2)
+        ok = ok and torch.allclose(sharded.sum_over_rows(lambda t: t.sum(0)), full.sum(0), atol=1e-5)
+        mv, mi = mesh.scatter(tied).argmax_over_rows(lambda t: t.max(0).values, lambda t: t.max(0).indices)
+        ok = ok and torch.equal(mi, torch.full((5,), 2))
+        try:
+            mesh.wrap(full, rows)
+            ok = False  # the whole tensor is not this rank's shard
+        except ValueError:
+            pass
         results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
