@@ -1136,6 +1136,89 @@ bool matches(const tn_eltwise_node_t* nodes, int n) {
     return true;
 }
 
+// A program that computes the same expression as a compiled one, with its nodes listed in another
+// order, its inputs numbered differently or the operands of an add / multiply swapped, is rewritten
+// into the compiled program's own form, so that what reaches the fast path does not depend on how the
+// caller walked its expression tree. The two DAGs are unified from the result downwards: node against
+// node of the same opcode (both operand orders for the commutative ones, which give bit-identical
+// results), input against input. Every node of the caller's program must take part.
+template <typename P>
+struct Unifier {
+    const tn_eltwise_node_t* nodes;
+    int n_inputs;
+    int node_of[P::N];   // pattern node -> program node
+    int input_of[kMaxIn];  // pattern input -> program input
+
+    bool value(int pv, int gv) {
+        if (pv < kMaxIn) {
+            if (gv >= kMaxIn || gv >= n_inputs) return false;
+            if (input_of[pv] >= 0) return input_of[pv] == gv;
+            input_of[pv] = gv;
+            return true;
+        }
+        if (gv < kMaxIn) return false;
+        return node(pv - kMaxIn, gv - kMaxIn);
+    }
+    bool node(int pk, int gk) {
+        if (node_of[pk] >= 0) return node_of[pk] == gk;
+        const NodeSpec want = P::nodes[pk];
+        const tn_eltwise_node_t& got = nodes[gk];
+        if (got.opcode != want.op) return false;
+        const Unifier saved = *this;
+        node_of[pk] = gk;
+        if (!op_is_binary(want.op)) {
+            if (value(want.lhs, got.lhs)) return true;
+            *this = saved;
+            return false;
+        }
+        if (value(want.lhs, got.lhs) && value(want.rhs, got.rhs)) return true;
+        *this = saved;
+        if (want.op == TN_OP_ADD || want.op == TN_OP_MUL) {
+            node_of[pk] = gk;
+            if (value(want.lhs, got.rhs) && value(want.rhs, got.lhs)) return true;
+            *this = saved;
+        }
+        return false;
+    }
+};
+
+// On success `nodes` holds the compiled program's node list (immediates carried over) and `inputs`
+// its inputs in the compiled program's numbering.
+template <typename P>
+bool rewrite_as(tn_eltwise_node_t* nodes, int n_nodes, const tn_tensor_t** inputs, int* n_inputs) {
+    if (n_nodes != P::N) return false;
+    Unifier<P> u;
+    u.nodes = nodes;
+    u.n_inputs = *n_inputs;
+    for (int k = 0; k < P::N; ++k) u.node_of[k] = -1;
+    for (int k = 0; k < kMaxIn; ++k) u.input_of[k] = -1;
+    if (!u.node(P::N - 1, n_nodes - 1)) return false;
+    bool used[kMaxNodes] = {};
+    for (int k = 0; k < P::N; ++k) {
+        if (u.node_of[k] < 0 || used[u.node_of[k]]) return false;
+        used[u.node_of[k]] = true;
+    }
+    for (int k = 0; k < P::NIN; ++k)
+        if (u.input_of[k] < 0) return false;
+    tn_eltwise_node_t out[P::N];
+    const tn_tensor_t* in[kMaxIn] = {};
+    for (int k = 0; k < P::N; ++k) {
+        out[k] = nodes[u.node_of[k]];
+        out[k].lhs = static_cast<uint8_t>(P::nodes[k].lhs);
+        out[k].rhs = static_cast<uint8_t>(op_is_binary(P::nodes[k].op) ? P::nodes[k].rhs : P::nodes[k].lhs);
+    }
+    for (int k = 0; k < P::NIN; ++k) in[k] = inputs[u.input_of[k]];
+    for (int k = 0; k < P::N; ++k) nodes[k] = out[k];
+    for (int k = 0; k < P::NIN; ++k) inputs[k] = in[k];
+    *n_inputs = P::NIN;
+    return true;
+}
+
+bool rewrite_as_compiled(tn_eltwise_node_t* nodes, int n_nodes, const tn_tensor_t** inputs, int* n_inputs) {
+    return rewrite_as<ProgLogSquareExp>(nodes, n_nodes, inputs, n_inputs) || rewrite_as<ProgMulAdd>(nodes, n_nodes, inputs, n_inputs) ||
+           rewrite_as<ProgSquaredDiff>(nodes, n_nodes, inputs, n_inputs) || rewrite_as<ProgNormScale>(nodes, n_nodes, inputs, n_inputs);
+}
+
 template <typename T>
 tn_status launch_program(const Plan& plan, const tn_tensor_t* const* inputs, int n_inputs,
                          const tn_eltwise_node_t* nodes, int n_nodes, tn_tensor_t* dst, cudaStream_t s) {
@@ -1327,6 +1410,13 @@ tn_status tn_eltwise_program(const tn_tensor_t* const* inputs, int n_inputs, con
             else if (dt == TN_BFLOAT16) local[k].imm = __bfloat162float(__float2bfloat16_rn(local[k].imm));
         }
     }
+    // an expression that a compiled program computes takes that program's form, whatever order the
+    // caller listed its nodes and inputs in
+    const tn_tensor_t* ordered[TN_PROGRAM_MAX_INPUTS] = {};
+    for (int k = 0; k < n_inputs; ++k) ordered[k] = inputs[k];
+    static const bool no_rewrite = getenv("TN_PROGRAM_NO_REWRITE") != nullptr;
+    if (!no_rewrite) rewrite_as_compiled(local, n_nodes, ordered, &n_inputs);
+    inputs = ordered;
     Plan plan;
     TN_TRY(build_plan(inputs, n_inputs, dst, plan));
     cudaStream_t s = as_cuda(stream);

@@ -539,10 +539,9 @@ struct RowStats {
 // Stages 32 consecutive columns of this lane's row at `dst` (2-byte aligned). Full chunks are
 // written as aligned 32-bit words: a lane whose row starts on an odd element shifts its packed
 // pairs by one element (funnel shift) and writes the first and last element on their own.
-template <typename OutT, bool SCALE, bool STATS>
-__device__ __forceinline__ void stage_packed_chunk(const uint32_t (&v)[32], uint8_t* dst, int ncols, bool has_bias, float bias, uint32_t scale2,
-                                                   RowStats& stats, int chunk) {
-    uint32_t w[16];
+// Accumulators of 32 consecutive columns -> 16 packed pairs of rounded (and scaled) results.
+template <typename OutT, bool SCALE>
+__device__ __forceinline__ void pack_chunk(const uint32_t (&v)[32], uint32_t (&w)[16], bool has_bias, float bias, uint32_t scale2) {
     if (has_bias) {  // warp-uniform
 #pragma unroll
         for (int j = 0; j < 16; ++j)
@@ -551,7 +550,12 @@ __device__ __forceinline__ void stage_packed_chunk(const uint32_t (&v)[32], uint
 #pragma unroll
         for (int j = 0; j < 16; ++j) w[j] = finish_pair<OutT, SCALE>(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]), scale2);
     }
-    if constexpr (STATS) stats.template update<OutT>(w, ncols, chunk);
+}
+
+// Stages the 16 pairs at `dst` (2-byte aligned). Full chunks are written as aligned 32-bit words: a
+// lane whose row starts on an odd element shifts its packed pairs by one element (funnel shift) and
+// writes the first and last element on their own.
+__device__ __forceinline__ void stage_packed_chunk(const uint32_t (&w)[16], uint8_t* dst, int ncols) {
     if (ncols == 32) {  // warp-uniform
         const uint32_t odd = (static_cast<uint32_t>(reinterpret_cast<uintptr_t>(dst)) >> 1) & 1u;
         uint32_t* words = reinterpret_cast<uint32_t*>(dst + 2 * odd);
@@ -594,16 +598,22 @@ __device__ __forceinline__ void drain_packed(uint8_t* stage, uint8_t* gptr, int 
     const bool mine = lane < rows;
     RowStats stats;
     stats.init();
-    uint32_t va[32], vb[32];
-    tmem_load_issue(taddr0, va);
-    for (int c = 0; c < chunks; c += 2) {
-        tmem_load_wait(va);
-        if (c + 1 < chunks) tmem_load_issue(taddr0 + (c + 1) * 32, vb);
-        if (mine) stage_packed_chunk<OutT, SCALE, STATS>(va, my_row + c * 64, min(32, n - c * 32), has_bias, bias, scale2, stats, c);
-        if (c + 1 >= chunks) break;
-        tmem_load_wait(vb);
-        if (c + 2 < chunks) tmem_load_issue(taddr0 + (c + 2) * 32, va);
-        if (mine) stage_packed_chunk<OutT, SCALE, STATS>(vb, my_row + (c + 1) * 64, min(32, n - (c + 1) * 32), has_bias, bias, scale2, stats, c + 1);
+    // One loop body for every chunk (the epilogue warps share the instruction cache with the producer
+    // and the MMA issuer, so the code is kept small): the accumulators are packed into 16 registers,
+    // then the load of the next chunk is issued into the freed ones and runs under the statistics
+    // and the staging stores of this chunk.
+    uint32_t v[32], w[16];
+    tmem_load_issue(taddr0, v);
+#pragma unroll 1
+    for (int c = 0; c < chunks; ++c) {
+        tmem_load_wait(v);
+        pack_chunk<OutT, SCALE>(v, w, has_bias, bias, scale2);
+        if (c + 1 < chunks) tmem_load_issue(taddr0 + (c + 1) * 32, v);
+        const int ncols = min(32, n - c * 32);
+        if (mine) {
+            if constexpr (STATS) stats.template update<OutT>(w, ncols, c);
+            stage_packed_chunk(w, my_row + c * 64, ncols);
+        }
     }
     if constexpr (STATS) {
         if (mine) {

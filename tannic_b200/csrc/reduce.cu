@@ -982,12 +982,6 @@ tn_status tn_reduce_stats(const tn_tensor_t* src, tn_tensor_t* max_out, tn_tenso
 tn_status tn_argsum_fixed_scratch(const tn_tensor_t* src, tn_tensor_t* dst, tn_stream_t stream, uint8_t axis) {
     TN_TRY(check(src, dst, axis, false, false));
     if (axis != src->rank - 1) return fail(TN_ERROR, "argsum_fixed_scratch: axis %d is not the last axis of a rank-%d tensor", (int)axis, (int)src->rank);
-    int64_t expect = 1;
-    for (int d = src->rank - 1; d >= 0; --d) {
-        const int64_t sz = (int64_t)src->shape.sizes[d];
-        if (sz != 1 && src->strides.sizes[d] != expect) return fail(TN_ERROR, "argsum_fixed_scratch: the source must be dense row-major");
-        expect *= sz;
-    }
     const int64_t len = (int64_t)src->shape.sizes[axis];
     if (dst->size == 0) return TN_SUCCESS;
     if (len == 0) {
@@ -995,6 +989,12 @@ tn_status tn_argsum_fixed_scratch(const tn_tensor_t* src, tn_tensor_t* dst, tn_s
         TN_TRY(use_device_of(dst));
         TN_CUDA(cudaMemsetAsync(dst->address, 0, dst->size * (size_t)dtype_bytes(dst->dtype), as_cuda(stream)));
         return TN_SUCCESS;
+    }
+    int64_t expect = 1;
+    for (int d = src->rank - 1; d >= 0; --d) {
+        const int64_t sz = (int64_t)src->shape.sizes[d];
+        if (sz != 1 && src->strides.sizes[d] != expect) return fail(TN_ERROR, "argsum_fixed_scratch: the source must be dense row-major");
+        expect *= sz;
     }
     const int64_t rows = expect / len;
     void* scratch = nullptr;

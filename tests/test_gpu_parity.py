@@ -327,6 +327,32 @@ def test_fused_program_dynamic_and_other_static_shapes():
     assert_close(got, want)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_program_in_any_node_order_takes_the_compiled_form(dtype):
+    """The same expression with its nodes listed in another order, the operands of an add / multiply
+    swapped and the inputs numbered the other way round is rewritten into the compiled program: the
+    result is bit-identical to the canonical listing (and so to the node-by-node chain)."""
+    x, y = gen((300, 512), dtype, 90, 0.1, 4.0), gen((1, 512), dtype, 91, -2.0, 2.0)
+    dx, dy = dev(x), dev(y)
+    canonical = tb.program([dx, dy], CFG2_NODES)
+    # exp first, operands of the add swapped
+    reordered = [(A.OP_EXP, 0, 0), (A.OP_LOG, 0, 0), (A.OP_MUL, 1, 1), (A.OP_ADD, 6, 5), (A.OP_SUB, 7, 4)]
+    assert_same(tb.program([dx, dy], reordered), canonical.cpu())
+    # inputs the other way round: Y is input 0, X input 1
+    renumbered = [(A.OP_MUL, 0, 0), (A.OP_LOG, 1, 1), (A.OP_EXP, 1, 1), (A.OP_ADD, 5, 4), (A.OP_SUB, 7, 6)]
+    assert_same(tb.program([dy, dx], renumbered), canonical.cpu())
+    # x0*x1 + x2 written as x2 + x1*x0
+    a, b, c = dev(gen((64, 256), dtype, 92)), dev(gen((64, 256), dtype, 93)), dev(gen((256,), dtype, 94))
+    want = tb.program([a, b, c], [(A.OP_MUL, 0, 1), (A.OP_ADD, 4, 2)])
+    assert_same(tb.program([c, b, a], [(A.OP_MUL, 1, 2), (A.OP_ADD, 0, 4)]), want.cpu())
+    # a different expression of the same size must not be mistaken for it: log(x) + y*y - exp(y)
+    other = [(A.OP_LOG, 0, 0), (A.OP_MUL, 1, 1), (A.OP_ADD, 4, 5), (A.OP_EXP, 1, 1), (A.OP_SUB, 6, 7)]
+    wide_y = dev(gen((300, 512), dtype, 95, -2.0, 2.0))
+    got = tb.program([dx, wide_y], other)
+    chain = tb.sub(tb.add(tb.log(dx), tb.mul(wide_y, wide_y)), tb.exp(wide_y))
+    assert_close(got, chain.cpu())
+
+
 def test_fused_program_rejects_bad_programs():
     x = dev(gen((8,), torch.float32, 1))
     with pytest.raises(A.TannicError):
