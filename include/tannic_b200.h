@@ -174,10 +174,13 @@ tn_status tn_host_free_pinned(void* address);
 /* Host-memory placement for the transfer path. No reference counterpart (its `Mesh` of devices is a
  * TODO, include/tannic/resources.hpp:194-197, and nothing there knows which host memory node a GPU
  * hangs off). tn_device_numa_node reports the node of the device's PCIe function (-1 where the
- * platform names none); tn_host_allocate_pinned_near pins memory preferably on that node (freed with
+ * platform names none); tn_host_allocate_pinned_near pins memory preferably on that node, or, when the
+ * node is unknown and the host has several, interleaved over all of them (freed with
  * tn_host_free_pinned); tn_bind_thread_near restricts the calling thread to that node's CPUs (within
- * the CPUs the process may use). All three succeed without effect where no node is known. */
+ * the CPUs the process may use). All succeed without effect where the platform gives no information.
+ * tn_host_memory_nodes: memory nodes the kernel reports online (0 when it does not say). */
 tn_status tn_device_numa_node(const tn_device_t* device, int* node);
+int tn_host_memory_nodes(void);
 tn_status tn_host_allocate_pinned_near(const tn_device_t* device, size_t nbytes, void** address);
 tn_status tn_bind_thread_near(const tn_device_t* device, int* node);
 

@@ -111,6 +111,7 @@ PROTOTYPES = {
     "tn_copy": [_TP, _TP, C.c_size_t, StreamT],
     "tn_host_allocate_pinned": [C.c_size_t, C.POINTER(C.c_void_p)],
     "tn_host_free_pinned": [C.c_void_p],
+    "tn_host_memory_nodes": [],
     "tn_device_numa_node": [C.POINTER(DeviceT), C.POINTER(C.c_int)],
     "tn_host_allocate_pinned_near": [C.POINTER(DeviceT), C.c_size_t, C.POINTER(C.c_void_p)],
     "tn_bind_thread_near": [C.POINTER(DeviceT), C.POINTER(C.c_int)],

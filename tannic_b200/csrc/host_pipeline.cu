@@ -115,11 +115,34 @@ int parse_cpulist(const char* text, cpu_set_t* set) {
     return found;
 }
 
-constexpr int kMpolDefault = 0, kMpolPreferred = 1;
-long set_mempolicy_node(int mode, int node) {
+constexpr int kMpolDefault = 0, kMpolPreferred = 1, kMpolInterleave = 3;
+// node >= 0: that node; node < 0 with kMpolInterleave: every node up to `last_node`
+long set_mempolicy_node(int mode, int node, int last_node = -1) {
     unsigned long mask[16] = {0};  // up to 1024 nodes
-    if (node >= 0 && node < 1024) mask[node / (8 * sizeof(unsigned long))] |= 1ul << (node % (8 * sizeof(unsigned long)));
+    const int bits = 8 * (int)sizeof(unsigned long);
+    if (node >= 0 && node < 1024) mask[node / bits] |= 1ul << (node % bits);
+    for (int n = 0; node < 0 && n <= last_node && n < 1024; ++n) mask[n / bits] |= 1ul << (n % bits);
     return syscall(SYS_set_mempolicy, mode, mode == kMpolDefault ? nullptr : mask, mode == kMpolDefault ? 0ul : 1025ul);
+}
+
+// Highest memory node the kernel reports online (0 on a single-node host, -1 when it does not say).
+int last_online_node() {
+    FILE* f = fopen("/sys/devices/system/node/online", "r");
+    if (!f) return -1;
+    char text[256] = {0};
+    const bool got = fgets(text, sizeof(text), f) != nullptr;
+    fclose(f);
+    if (!got) return -1;
+    int last = -1;
+    for (const char* p = text; *p;) {
+        char* end = nullptr;
+        const long v = strtol(p, &end, 10);
+        if (end == p) break;
+        if (v > last) last = (int)v;
+        p = (*end == '-' || *end == ',') ? end + 1 : end;
+        if (*end != '-' && *end != ',') break;
+    }
+    return last;
 }
 
 }  // namespace
@@ -135,6 +158,8 @@ tn_status tn_device_numa_node(const tn_device_t* device, int* node) {
     *node = numa_node_of(device->id);
     return TN_SUCCESS;
 }
+
+int tn_host_memory_nodes(void) { return last_online_node() + 1; }
 
 tn_status tn_bind_thread_near(const tn_device_t* device, int* node) {
     if (!device) return fail(TN_ERROR, "null device");
@@ -168,9 +193,14 @@ tn_status tn_host_allocate_pinned_near(const tn_device_t* device, size_t nbytes,
     TN_TRY(use_device(device->id));
     const int node = numa_node_of(device->id);
     // Pages are placed when they are first touched; cudaHostAlloc touches them while it pins them, so the
-    // preferred node is set around the call and put back afterwards. A kernel or container that refuses
-    // the policy call leaves the default placement, which is what tn_host_allocate_pinned gives.
-    const bool placed = node >= 0 && set_mempolicy_node(kMpolPreferred, node) == 0;
+    // policy is set around the call and put back afterwards: the device's own node where the platform
+    // names it; otherwise, on a host with several memory nodes, the pages are interleaved over all of
+    // them, so that the GPUs of a box do not all stream through the memory controllers of whichever node
+    // the ranks happened to start on. A kernel or container that refuses the policy call leaves the
+    // default placement, which is what tn_host_allocate_pinned gives.
+    bool placed = false;
+    if (node >= 0) placed = set_mempolicy_node(kMpolPreferred, node) == 0;
+    else if (const int last = last_online_node(); last > 0) placed = set_mempolicy_node(kMpolInterleave, -1, last) == 0;
     const cudaError_t err = cudaHostAlloc(address, nbytes ? nbytes : 1, cudaHostAllocDefault);
     if (placed) set_mempolicy_node(kMpolDefault, -1);
     if (err != cudaSuccess) {
