@@ -993,8 +993,10 @@ __device__ __forceinline__ void node_dispatch(int op, const Vec<T> (&a)[U], cons
 // type like the node-by-node chain) lives in shared memory: 16 bytes per thread, vector and value,
 // at word (value * U + u) * blockDim.x + thread. Nothing is shared between threads, so no barrier is
 // needed; shared memory only stands in for a register file that can be indexed at run time.
-// (Keeping the previous node's result in registers, with the host marking which operands and results
-// can skip shared memory, measured slower: 0.214 against 0.172 ms on a six-node expression.)
+// (Two alternatives measured slower on a six-node float16 expression over [8192,8192], 0.172 ms as
+// written here: keeping the previous node's result in registers, with the host marking which operands
+// and results can skip shared memory, 0.214 ms; a postfix program on a four-slot register stack with
+// one switch case per (operation, slot), no shared memory at all, 0.253 ms.)
 template <typename T, int U>
 __device__ __forceinline__ void eval_interpreted(const Vec<T> (&vin)[U][kMaxIn], Vec<T> (&out)[U], const ProgArgs& g) {
     extern __shared__ uint4 program_values[];

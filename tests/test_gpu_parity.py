@@ -353,6 +353,43 @@ def test_program_in_any_node_order_takes_the_compiled_form(dtype):
     assert_close(got, chain.cpu())
 
 
+@pytest.mark.parametrize("dtype", HALVES)
+def test_interpreted_programs_of_many_shapes(dtype):
+    """16-bit expressions outside the compiled set (the in-kernel interpreter): trees of several depths,
+    `x op x`, a subtree used twice, non-commutative operand order, immediates, a column-broadcast input
+    and a five-deep right-leaning chain: all against the oracle's node-by-node chain; the exact
+    operations also bit for bit against the device's own node-by-node chain."""
+    x, w = gen((130, 264), dtype, 100, 0.2, 3.0), gen((130, 264), dtype, 101, -2.0, 2.0)
+    b, col = gen((264,), dtype, 102, -1.0, 1.0), gen((130, 1), dtype, 103, 0.5, 1.5)
+    dx, dw, db, dcol = dev(x), dev(w), dev(b), dev(col)
+    O, B, U = oracle, oracle.binary, oracle.unary
+    # tanh(x*w + b) * 0.5 - rsqrt(x, 1e-3)
+    got = tb.program([dx, dw, db], [(A.OP_MUL, 0, 1), (A.OP_ADD, 4, 2), (A.OP_TANH, 5, 5), (A.OP_SCALE, 6, 6, 0.5), (A.OP_RSQRT, 0, 0, 1e-3), (A.OP_SUB, 7, 8)])
+    want = B("sub", O.scale(U("tanh", B("add", B("mul", x, w), b)), 0.5), U("rsqrt", x, eps=1e-3))
+    assert_close(got, want)
+    # exact operations only: ((x - w) * (x - w) + |w|) * col - x, with (x - w) written once and used twice
+    nodes = [(A.OP_SUB, 0, 1), (A.OP_MUL, 4, 4), (A.OP_ABS, 1, 1), (A.OP_ADD, 5, 6), (A.OP_MUL, 7, 2), (A.OP_SUB, 8, 0)]
+    got = tb.program([dx, dw, dcol], nodes)
+    d_ = tb.sub(dx, dw)
+    chain = tb.sub(tb.mul(tb.add(tb.mul(d_, d_), tb.abs(dw)), dcol), dx)
+    assert_same(got, chain.cpu())
+    diff = B("sub", x, w)
+    assert_same(got, B("sub", B("mul", B("add", B("mul", diff, diff), U("abs", w)), col), x))
+    # operand order of the non-commutative ones: w - (x - b), pow(x, w)
+    got = tb.program([dx, dw, db], [(A.OP_SUB, 0, 2), (A.OP_SUB, 1, 4)])
+    assert_same(got, B("sub", w, B("sub", x, b)))
+    got = tb.program([dx, dw], [(A.OP_POW, 0, 1), (A.OP_NEG, 4, 4), (A.OP_EXP, 5, 5)])
+    assert_close(got, U("exp", U("neg", B("pow", x, w))))
+    # the same value feeding two different nodes (evaluated twice on the stack): (x+w) * (x+w - b)
+    got = tb.program([dx, dw, db], [(A.OP_ADD, 0, 1), (A.OP_SUB, 4, 2), (A.OP_MUL, 4, 5)])
+    sm_ = B("add", x, w)
+    assert_same(got, B("mul", sm_, B("sub", sm_, b)))
+    # a right-leaning chain of subtractions five deep: x - (w - (x - (w - (x - b))))
+    nodes = [(A.OP_SUB, 0, 2), (A.OP_SUB, 1, 4), (A.OP_SUB, 0, 5), (A.OP_SUB, 1, 6), (A.OP_SUB, 0, 7)]
+    got = tb.program([dx, dw, db], nodes)
+    assert_same(got, B("sub", x, B("sub", w, B("sub", x, B("sub", w, B("sub", x, b))))))
+
+
 def test_fused_program_rejects_bad_programs():
     x = dev(gen((8,), torch.float32, 1))
     with pytest.raises(A.TannicError):
