@@ -237,6 +237,148 @@ __global__ void __launch_bounds__(kThreads) reduce_rows_warp(const T* __restrict
     }
 }
 
+
+// ---- one thread per row, rows staged per warp ---------------------------------------------
+// Short rows of a 16-bit float type (up to 400 elements), dense source, last axis. A warp owns a span of
+// 32 consecutive rows, which is one contiguous, 16-byte-aligned byte range: it copies the span into its own
+// block of shared memory with coalesced 16-byte loads, then every lane reduces ONE row from there, so no
+// partial results ever cross lanes. The row is read a word (two elements) at a time; per block of 16
+// words a packed max / min tree gives the best even and the best odd element, compared (strictly, ordered:
+// a NaN never wins, the first of equal values stays) with the row's running pair; only the block where
+// each last improved is remembered and the element's position inside it is found by one scan at the end.
+// Every warp has two blocks and copies its next span (cp.async) while it reduces the current one; up to
+// 16 warps per CTA, one CTA per SM, and nothing but __syncwarp() orders anything.
+constexpr int kLaneRows = 32;            // rows per span: one per lane
+constexpr int kLaneMaxLen = 400;         // 2 blocks x 32 rows x 400 x 2 B = 50 KB per warp -> at least 4 warps per CTA
+constexpr int kLaneSmemBytes = 200 << 10;
+
+template <typename T, bool MIN> __device__ __forceinline__ uint32_t best_pair(uint32_t a, uint32_t b) {
+    using T2 = typename pair_of_half<T>::type;
+    const T2 m = MIN ? __hmin2(*reinterpret_cast<const T2*>(&a), *reinterpret_cast<const T2*>(&b))
+                     : __hmax2(*reinterpret_cast<const T2*>(&a), *reinterpret_cast<const T2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&m);
+}
+
+template <typename T, bool SUM, bool ARG, bool MIN>
+__global__ void __launch_bounds__(512, 1) reduce_rows_lane(const T* __restrict__ src, int64_t rows, int len, uint32_t span_stride,
+                                                           Outputs out) {
+    static_assert(sizeof(T) == 2, "16-bit float types only");
+    extern __shared__ __align__(128) unsigned char lane_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    // two blocks per warp: the copy of the warp's next span runs while the current one is reduced
+    unsigned char* blocks = lane_smem + static_cast<size_t>(warp) * 2 * span_stride;
+    const int64_t spans = (rows + kLaneRows - 1) / kLaneRows;
+    const uint32_t none = pair_bits<T>(cmp_init<float, MIN>());
+    const int64_t step = static_cast<int64_t>(gridDim.x) * warps;
+    auto fetch = [&](int64_t span, unsigned char* stage) {
+        if (span < spans) {
+            const int64_t row0 = span * kLaneRows;
+            const int nrows = static_cast<int>(rows - row0 < kLaneRows ? rows - row0 : kLaneRows);
+            const int elems = nrows * len;
+            const unsigned char* g = reinterpret_cast<const unsigned char*>(src + row0 * len);  // 64 * len bytes per span: 16-byte aligned
+            const int vecs = (elems * 2) >> 4;
+            const uint32_t sbase = static_cast<uint32_t>(__cvta_generic_to_shared(stage));
+            for (int v = lane; v < vecs; v += 32)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sbase + v * 16), "l"(g + static_cast<size_t>(v) * 16) : "memory");
+            for (int e = vecs * 8 + lane; e < elems; e += 32)  // ragged end of the last span
+                reinterpret_cast<uint16_t*>(stage)[e] = reinterpret_cast<const uint16_t*>(g)[e];
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    int which = 0;
+    int64_t span = static_cast<int64_t>(blockIdx.x) * warps + warp;
+    fetch(span, blocks);
+    for (; span < spans; span += step, which ^= 1) {
+        unsigned char* stage = blocks + static_cast<size_t>(which) * span_stride;
+        fetch(span + step, blocks + static_cast<size_t>(which ^ 1) * span_stride);  // the other block was released by the __syncwarp that ended the last pass
+        asm volatile("cp.async.wait_group 1;" ::: "memory");                      // all but the newest group have landed
+        __syncwarp();
+        const int64_t row0 = span * kLaneRows;
+        const int nrows = static_cast<int>(rows - row0 < kLaneRows ? rows - row0 : kLaneRows);
+        if (lane < nrows) {
+            const T* row = reinterpret_cast<const T*>(stage) + lane * len;
+            const int odd = (lane * len) & 1;  // the row starts in the upper half of a word: peel one element
+            const uint32_t* words = reinterpret_cast<const uint32_t*>(row + odd);
+            const int nwords = (len - odd) >> 1;
+            State<T, SUM, ARG, MIN> st;
+            st.init();
+            if (odd) st.feed(row[0], 0);
+            float sum_lo = 0.0f, sum_hi = 0.0f;
+            float best_lo = cmp_init<float, MIN>(), best_hi = cmp_init<float, MIN>();
+            int block_lo = -1, block_hi = -1;
+            for (int b0 = 0; b0 < nwords; b0 += 16) {
+                uint32_t m = none;
+                if (b0 + 16 <= nwords) {
+                    uint32_t w[16];
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) w[k] = words[b0 + k];
+                    if constexpr (ARG) {
+                        uint32_t t8[8];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) t8[k] = best_pair<T, MIN>(w[k], w[k + 8]);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) t8[k] = best_pair<T, MIN>(t8[k], t8[k + 4]);
+                        m = best_pair<T, MIN>(best_pair<T, MIN>(t8[0], t8[2]), best_pair<T, MIN>(t8[1], t8[3]));
+                    }
+                    if constexpr (SUM) {
+#pragma unroll
+                        for (int k = 0; k < 16; ++k) {
+                            sum_lo += half_of_pair<T>(w[k], 0);
+                            sum_hi += half_of_pair<T>(w[k], 1);
+                        }
+                    }
+                } else {
+                    for (int k = b0; k < nwords; ++k) {
+                        const uint32_t w = words[k];
+                        if constexpr (ARG) m = best_pair<T, MIN>(m, w);
+                        if constexpr (SUM) {
+                            sum_lo += half_of_pair<T>(w, 0);
+                            sum_hi += half_of_pair<T>(w, 1);
+                        }
+                    }
+                }
+                if constexpr (ARG) {
+                    const float lo = half_of_pair<T>(m, 0), hi = half_of_pair<T>(m, 1);
+                    if (MIN ? (lo < best_lo) : (lo > best_lo)) {
+                        best_lo = lo;
+                        block_lo = b0;
+                    }
+                    if (MIN ? (hi < best_hi) : (hi > best_hi)) {
+                        best_hi = hi;
+                        block_hi = b0;
+                    }
+                }
+            }
+            if constexpr (SUM) st.sum += sum_lo + sum_hi;
+            if constexpr (ARG) {
+                // position of each half's extreme inside the block where it first appeared
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int b0 = h ? block_hi : block_lo;
+                    const float best = h ? best_hi : best_lo;
+                    if (b0 >= 0) {
+                        int at = 0;
+                        const int top = nwords - b0 < 16 ? nwords - b0 : 16;
+#pragma unroll 4
+                        for (int k = 15; k >= 0; --k)
+                            if (k < top && half_of_pair<T>(words[b0 + k], h) == best) at = k;
+                        const int j = odd + 2 * (b0 + at) + h;
+                        st.merge(0.0f, to_compute<float>(row[j]), j);  // the element itself: the sign of a zero survives
+                    }
+                }
+            }
+            if ((len - odd) & 1) {
+                State<T, SUM, ARG, MIN> tail;
+                tail.init();
+                tail.feed(row[len - 1], len - 1);
+                st.merge(tail);
+            }
+            write_out(st, out, row0 + lane, len, row[0]);
+        }
+        __syncwarp();  // every lane is done with the block before the next span overwrites it
+    }
+}
+
 // ---- staged short rows -------------------------------------------------------------------
 constexpr int kStagedThreads = 512;
 
@@ -742,6 +884,28 @@ tn_status launch(const tn_tensor_t* src, int axis, Outputs out, cudaStream_t s) 
             }
             tn_status fr = scratch_free(scratch, s);
             return st != TN_SUCCESS ? st : fr;
+        }
+        // 16-bit floats, rows of up to 400 elements, many rows: one thread per row on warp-private staged spans
+        if constexpr (is_half16<T>::value) {
+            static const bool no_lane = getenv("TN_REDUCE_NO_LANE") != nullptr;
+            if (!no_lane && len >= 8 && len <= kLaneMaxLen && total >= 4096 && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+                const uint32_t span_stride = (uint32_t)((kLaneRows * len * 2 + 127) & ~int64_t(127));
+                int warps = (int)(kLaneSmemBytes / (2 * span_stride));
+                if (warps > 16) warps = 16;
+                const size_t smem = (size_t)warps * 2 * span_stride;
+                static thread_local int attr_device = -1;
+                int dev = 0;
+                TN_CUDA(cudaGetDevice(&dev));
+                if (attr_device != dev) {
+                    TN_CUDA(cudaFuncSetAttribute(reduce_rows_lane<T, SUM, ARG, MIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kLaneSmemBytes));
+                    attr_device = dev;
+                }
+                const int64_t spans = ceil_div(total, kLaneRows);
+                int64_t grid = ceil_div(spans, warps);
+                if (grid > sm_count()) grid = sm_count();
+                reduce_rows_lane<T, SUM, ARG, MIN><<<(unsigned)grid, warps * 32, smem, s>>>(p, total, (int)len, span_stride, out);
+                return after_launch("reduce_rows_lane");
+            }
         }
         // Rows up to 1 KiB always take the staged kernel; up to 2 KiB they do unless the row is a
         // whole number of 512-byte warp sweeps, where the warp-per-row kernel is balanced and measured

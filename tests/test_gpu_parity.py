@@ -454,6 +454,37 @@ def test_reduce_keepdim_and_stats():
     assert_close(sm, oracle.reduce("sum", x, -1, acc=oracle.ACC_WIDE))
 
 
+@pytest.mark.parametrize("dtype", HALVES)
+@pytest.mark.parametrize("shape", [(4100, 197), (5000, 9), (4113, 400), (6000, 64), (4500, 33), (21, 12, 197, 197), (4097, 8), (4200, 255)])
+def test_reductions_one_thread_per_row(dtype, shape):
+    """Many short 16-bit rows take the kernel in which a warp stages a span of 32 rows and every lane
+    reduces one of them: even and odd row lengths (rows that start in either half of a word), a row count
+    that is not a multiple of 32, coarse values (many ties: the first occurrence must win), rows with NaN,
+    infinities and all -inf; every reduction kind and the fused statistics, against the oracle."""
+    x = gen(shape, dtype, 61, -2.0, 2.0)
+    flat = x.view(-1, shape[-1])
+    flat[1::3] = (flat[1::3] * 4).round() / 4          # ties
+    flat[2, :] = float("-inf")
+    flat[3, :] = float("nan")
+    flat[4, 1::2] = float("nan")
+    flat[5, 3] = float("inf")
+    flat[5, 6] = float("inf")
+    flat[6, :] = 0.0
+    flat[6, 5] = -0.0
+    dx = dev(x)
+    for kind in ("argmax", "argmin", "max"):
+        assert_same(getattr(tb, kind)(dx, -1), oracle.reduce(kind, x, -1))
+    ok_rows = torch.ones(flat.shape[0], dtype=torch.bool)
+    ok_rows[[2, 3, 4, 5]] = False                       # sums of rows with NaN / inf are not compared
+    want_sum = oracle.reduce("sum", x, -1, acc=oracle.ACC_WIDE).reshape(-1)[ok_rows]
+    assert_close(tb.sum(dx, -1).reshape(-1)[dev(ok_rows)], want_sum)
+    assert_close(tb.mean(dx, -1).reshape(-1)[dev(ok_rows)], oracle.reduce("mean", x, -1, acc=oracle.ACC_WIDE).reshape(-1)[ok_rows])
+    mx, sm, am = tb.reduce_stats(dx, -1)
+    assert_same(am, oracle.reduce("argmax", x, -1))
+    assert_same(mx, oracle.reduce("max", x, -1))
+    assert_close(sm.reshape(-1)[dev(ok_rows)], want_sum)
+
+
 @pytest.mark.parametrize("dtype,shape", [(torch.bfloat16, (12, 197, 197)), (torch.float16, (4099, 64)), (torch.float32, (3001, 100)),
                                          (torch.int32, (2500, 33)), (torch.float64, (2100, 8)), (torch.int8, (2048, 1000)),
                                          (torch.bfloat16, (2100, 1000)), (torch.float32, (2300, 300)), (torch.float16, (2200, 999)),
