@@ -256,7 +256,8 @@ tn_status tn_eltwise_program(const tn_tensor_t* const* inputs, int n_inputs,
  * than the result (a broadcast row) are copied whole first. Returns when dst is complete. Device
  * staging memory is kept between calls and only grows. Replaces the reference's sequence of
  * Tensor::to(Device) -> one launch per node -> read-back, each a synchronous cudaMemcpy
- * (src/tensor.cpp:34-136, src/cuda/mem.cu:54-90). Calls are serialised inside the library. */
+ * (src/tensor.cpp:34-136, src/cuda/mem.cu:54-90). Calls on one device are serialised inside the
+ * library; calls on different devices (one host thread each) run side by side. */
 tn_status tn_eltwise_program_host(const tn_device_t* device, const tn_tensor_t* const* inputs, int n_inputs,
                                   const tn_eltwise_node_t* nodes, int n_nodes, tn_tensor_t* dst, int chunks);
 

@@ -92,14 +92,39 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc(const uint16_t* __restrict__
     }
 }
 
+// The weight re-layout as a job that rides along with the activation re-layout (the extra z slices of that
+// launch do it), so that the convolution's staging is one launch, not two.
+struct WeightJob {
+    const uint16_t* w;
+    uint16_t* out;
+    int64_t Cout, Cin, Kh, Kw, ws0, ws1, ws2, ws3;
+};
+// w[co, ci, kh, kw] (any strides) -> out[kh*Kw + kw][co][ci], `part` of `parts` equal shares of thread blocks
+__device__ __forceinline__ void pack_weights_part(const WeightJob& j, int64_t part, int64_t parts) {
+    const int64_t total = j.Kh * j.Kw * j.Cout * j.Cin;
+    for (int64_t i = part * 256 + threadIdx.x; i < total; i += parts * 256) {
+        int64_t rem = i;
+        const int64_t ci = rem % j.Cin; rem /= j.Cin;
+        const int64_t co = rem % j.Cout; rem /= j.Cout;
+        const int64_t kw = rem % j.Kw;
+        const int64_t kh = rem / j.Kw;
+        j.out[i] = j.w[co * j.ws0 + ci * j.ws1 + kh * j.ws2 + kw * j.ws3];
+    }
+}
+
 // Same re-layout for a dense 16-bit NCHW tensor whose image size H*W is a multiple of 8: both
 // global sides move 16 bytes per thread. A 64-channel x 64-pixel tile is held as 64 rows of 32
 // words (a word = two neighbouring pixels of one channel). Row r sits at row index
 // (r % 8) * 8 + r / 8 and its words are XOR-swizzled by 4 * (r / 8), which makes the 16-byte row
 // stores and the per-channel word gathers of the second phase both free of bank conflicts.
 __global__ void __launch_bounds__(256) nchw_to_nhwc_vec(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, int64_t C,
-                                                        int64_t HW) {
+                                                        int64_t HW, int64_t images, WeightJob weights) {
     __shared__ __align__(16) uint32_t tile[64 * 32];
+    if (blockIdx.z >= images) {  // the extra slices repack the weights
+        const int64_t per_slice = (int64_t)gridDim.x * gridDim.y, slices = gridDim.z - images;
+        pack_weights_part(weights, (blockIdx.z - images) * per_slice + (int64_t)blockIdx.y * gridDim.x + blockIdx.x, per_slice * slices);
+        return;
+    }
     const int64_t p0 = (int64_t)blockIdx.x * 64, c0 = (int64_t)blockIdx.y * 64, n = blockIdx.z;
 #pragma unroll
     for (int it = 0; it < 2; ++it) {
@@ -249,16 +274,22 @@ tn_status conv_impl(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_
             uint16_t* wp = reinterpret_cast<uint16_t*>(scratch + x_padded);
             const dim3 tgrid((unsigned)ceil_div(g.H * g.W, 64), (unsigned)ceil_div(g.Cin, 64), (unsigned)g.N);
             tn_status st = TN_SUCCESS;
+            bool weights_packed = false;
             if (x_is_nhwc) {
                 xh = const_cast<uint16_t*>(static_cast<const uint16_t*>(g.x));
             } else {
-                if (dense_nchw(x) && (g.H * g.W) % 8 == 0 && (reinterpret_cast<uintptr_t>(g.x) & 15) == 0)
-                    nchw_to_nhwc_vec<<<tgrid, 256, 0, s>>>(static_cast<const uint16_t*>(g.x), xh, g.Cin, g.H * g.W);
-                else
+                if (dense_nchw(x) && (g.H * g.W) % 8 == 0 && (reinterpret_cast<uintptr_t>(g.x) & 15) == 0) {
+                    // one launch for both re-layouts: the weights ride along in one extra z slice
+                    const WeightJob job{static_cast<const uint16_t*>(g.w), wp, g.Cout, g.Cin, g.Kh, g.Kw, g.ws[0], g.ws[1], g.ws[2], g.ws[3]};
+                    const dim3 both(tgrid.x, tgrid.y, tgrid.z + 1);
+                    nchw_to_nhwc_vec<<<both, 256, 0, s>>>(static_cast<const uint16_t*>(g.x), xh, g.Cin, g.H * g.W, g.N, job);
+                    weights_packed = true;
+                } else {
                     nchw_to_nhwc<<<tgrid, 256, 0, s>>>(static_cast<const uint16_t*>(g.x), xh, g.Cin, g.H, g.W, g.xs[0], g.xs[1], g.xs[2], g.xs[3]);
+                }
                 st = after_launch("nchw_to_nhwc");
             }
-            if (st == TN_SUCCESS) {
+            if (st == TN_SUCCESS && !weights_packed) {
                 int64_t wblocks = ceil_div(g.Kh * g.Kw * g.Cout * g.Cin, 256);
                 if (wblocks > 1184) wblocks = 1184;
                 pack_weights<<<(unsigned)wblocks, 256, 0, s>>>(static_cast<const uint16_t*>(g.w), wp, g.Cout, g.Cin, g.Kh, g.Kw, g.ws[0], g.ws[1], g.ws[2], g.ws[3]);

@@ -23,19 +23,22 @@ namespace {
 
 constexpr int kMaxChunks = 64;
 
+constexpr int kMaxDevices = 64;
+
+// Streams, events and staging memory of one device; created on first use, kept until exit. Calls on
+// one device are serialised by the device's own mutex, calls on different devices run side by side.
 struct Pipeline {
+    std::mutex mutex;
     bool ready = false;
     cudaStream_t in = nullptr, run = nullptr, out = nullptr;
     cudaEvent_t arrived[kMaxChunks] = {}, done[kMaxChunks] = {};
-    cudaEvent_t whole = nullptr;
     void* stage_in[TN_PROGRAM_MAX_INPUTS] = {};
     size_t stage_in_bytes[TN_PROGRAM_MAX_INPUTS] = {};
     void* stage_out = nullptr;
     size_t stage_out_bytes = 0;
 };
 
-std::mutex g_mutex;               // one host-to-host call per process at a time
-std::vector<Pipeline> g_pipelines;  // per device, created on first use, kept until exit
+Pipeline g_pipelines[kMaxDevices];
 
 tn_status prepare(Pipeline& p) {
     if (p.ready) return TN_SUCCESS;
@@ -46,7 +49,6 @@ tn_status prepare(Pipeline& p) {
         TN_CUDA(cudaEventCreateWithFlags(&p.arrived[c], cudaEventDisableTiming));
         TN_CUDA(cudaEventCreateWithFlags(&p.done[c], cudaEventDisableTiming));
     }
-    TN_CUDA(cudaEventCreateWithFlags(&p.whole, cudaEventDisableTiming));
     p.ready = true;
     return TN_SUCCESS;
 }
@@ -224,9 +226,9 @@ tn_status tn_eltwise_program_host(const tn_device_t* device, const tn_tensor_t* 
     }
     if (dst->size == 0) return TN_SUCCESS;
     TN_TRY(use_device(device->id));
-    std::lock_guard<std::mutex> lock(g_mutex);
-    if ((int)g_pipelines.size() <= device->id) g_pipelines.resize(device->id + 1);
+    if (device->id >= kMaxDevices) return fail(TN_ERROR, "device id %d is beyond the %d devices the host pipeline keeps state for", device->id, kMaxDevices);
     Pipeline& p = g_pipelines[device->id];
+    std::lock_guard<std::mutex> lock(p.mutex);
     TN_TRY(prepare(p));
 
     // an input is cut along its rows when it has the result's rank and leading extent; anything smaller

@@ -86,7 +86,9 @@ Runtime& runtime() {
 // (Tensor::assign, src/tensor.cpp:34-44: one cuda::copyFromHost of dsizeof(dtype) bytes per element).
 // tn_assign_from_host gathers such writes while they extend one contiguous device range and sends
 // the range as ONE copy as soon as anything else happens on this thread: every entry point of the
-// library passes through use_device(), which flushes first, so program order is kept.
+// library passes through use_device(), which flushes first, so program order is kept. The pending
+// run belongs to the calling thread: a thread must flush (any entry point, or tn_flush_assignments)
+// before it ends or hands the tensor to another thread.
 namespace {
 struct PendingAssign {
     int device = -1;

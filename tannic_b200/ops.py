@@ -88,7 +88,11 @@ def _compare(name: str, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     for s in shape:
         n *= s
     packed = torch.empty(((n + 7) // 8,), dtype=torch.uint8, device=a.device)
-    dd = A.make_tensor(packed.data_ptr(), shape, torch.empty(shape, device="meta").stride(), A.BOOLEAN,
+    dense, run = [], 1
+    for extent in reversed(shape):
+        dense.insert(0, run)
+        run *= extent
+    dd = A.make_tensor(packed.data_ptr(), shape, dense, A.BOOLEAN,
                        a.device.index if a.device.index is not None else torch.cuda.current_device())
     da, db = desc(a), desc(b)
     A.check(getattr(A.lib(), f"tn_{name}")(C.byref(da), C.byref(db), C.byref(dd), current_stream(a)))

@@ -891,7 +891,8 @@ def test_conv2d_strided_on_tensor_cores(dtype, shape):
     bias = gen((cout,), dtype, 54, -1, 1)
     launches = tb.launch_count()
     got = tb.convolve2D(dev(x), dev(wt), stride, pad)
-    assert tb.launch_count() - launches == 3, "expected staging + weight packing + tensor-core GEMM"
+    # staging (the weight re-layout rides along in the same launch when the activation is dense) + tensor-core GEMM
+    assert tb.launch_count() - launches in (2, 3), "expected staging (+ weight packing) + tensor-core GEMM"
     assert_close(got, oracle.conv2d(x, wt, stride, pad, acc=oracle.ACC_WIDE))
     assert_close(tb.convolve2D(dev(x), dev(wt), stride, pad, bias=dev(bias)), oracle.conv2d(x, wt, stride, pad, bias=bias, acc=oracle.ACC_WIDE))
     assert tb.device_errors() == 0
