@@ -14,6 +14,7 @@
 //   MODE_K  B is K-major ([N, K]: `matmul(X, W.transpose(-1,-2))`), one 64x256 TMA box per stage;
 //   MODE_N  B is N-major ([K, N]: plain matmul, the [Cin, H*W] matrix of a 1x1 convolution),
 //           four 64-column boxes per stage and MN-major shared-memory descriptors;
+//           (with K <= 256 and one A for all batches: the stationary-A kernel further down);
 //   MODE_CONV  implicit-GEMM convolution: A = weights repacked to [tap][Cout][Cin], B = the
 //           activation in NHWC, fetched per (tap, channel block) as a 4-D box
 //           {64 channels, Wout, Hbox, 1} whose W/H coordinates are shifted by the tap and may
@@ -174,6 +175,32 @@ __device__ __forceinline__ void tmem_load_wait(uint32_t (&v)[32]) {
         : "memory");
 }
 
+// Registers -> tensor memory, the mirror image of the load above: lane i of the warp writes 32
+// consecutive 32-bit columns of TMEM lane (32 * (warp % 4) + i).
+__device__ __forceinline__ void tmem_store(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0],"
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16,"
+        " %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]),
+          "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]),
+          "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]),
+          "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// The same MMA with the A operand in tensor memory: row i of the 128 x 16 block in lane i, two
+// consecutive K elements per 32-bit column (so one instruction reads 8 columns).
+__device__ __forceinline__ void umma_f16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // Shared-memory matrix descriptor of a 128-byte-swizzled tile (sm_100 format: start address,
 // leading / stride byte offsets in 16-byte units, version 1 at bit 46, layout type 2 =
 // SWIZZLE_128B at bits 61-63).
@@ -211,6 +238,12 @@ struct KernelArgs {
     int cblocks, kw, pad_h, pad_w, hbox, str_h;
     int epi_warps;             // 4 or 8 epilogue warps take part (the others exit at once)
     uint32_t pack_stage_bytes; // packed epilogue: bytes of one warp's staging block (multiple of 128)
+    // stationary-A variant
+    const void* a;             // first operand [M, K], K contiguous
+    int64_t lda;
+    int k_total;               // K (a multiple of 8, at most 256)
+    int groups;                // CTA groups; each holds every row tile once and takes a share of the column tiles
+    uint32_t col_tiles;        // column tiles over all batches
     void* stat_max;            // fused row statistics (packed epilogue only); each may be null
     void* stat_sum;
     int64_t* stat_argmax;
@@ -890,6 +923,220 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0 && *abort_flag) atomicAdd(&g_tc_aborts, 1u);
 }
 
+// ---- stationary A for short K ---------------------------------------------------------------
+// With K <= 256 a tile is one pass of at most four K-blocks, so the ring above holds exactly one
+// tile's operands: a stage is refilled only after its MMAs have run, the next tile's first block
+// lands one load latency later, and the time per tile is that round trip however little of
+// HBM, L2 or the tensor pipe is in use. (Keeping A resident in SHARED memory changes nothing:
+// the ring that is left still holds one tile of B. Measured both ways.) This variant takes A
+// out of shared memory altogether. A CTA owns ONE 128-row tile of A for its whole life and
+// holds it in tensor memory (128 lanes x 128 columns of packed 16-bit pairs, next to two
+// 192-column accumulators: 2 * 192 + 128 = 512 columns), the MMAs take A from there
+// (tcgen05.mma with a tensor-memory A operand), and all of the ring carries B: eight stages of
+// 64 k-rows x 192 columns, i.e. two tiles in flight, with two thirds of the bytes per result
+// column. CTAs come in groups that contain every row tile once; the groups split the column
+// tiles (over all batches) evenly and the CTAs of a group walk the same columns at about the
+// same time, so B is read from HBM once and from L2 by the others. B is N-major ([K, N]: plain
+// matmul, the 1x1 convolution on NCHW). Narrower tiles do not pay: an MMA of N = 128 takes
+// nearly as long as one of N = 192 when it accumulates into the same columns as the one before
+// it (measured: 88 ns against 98 ns), so a variant with two row tiles per CTA and 128-column
+// accumulators lost more in the tensor pipe than it saved in L2 traffic.
+constexpr int SN = 192;                              // result columns per tile
+constexpr int S_STAGES = 8;
+constexpr uint32_t S_STAGE_BYTES = SN * BK * 2;      // 24 KiB
+constexpr int S_KMAX = 256;
+constexpr uint32_t S_A_COL = 2 * SN;                 // first tensor-memory column of A
+static_assert(S_STAGES * S_STAGE_BYTES == STAGES * STAGE_BYTES, "the stationary variant reuses the ring's memory");
+static_assert(S_A_COL + S_KMAX / 2 <= TMEM_COLS, "two accumulators and A must fit tensor memory");
+
+template <int OUT, bool SCALE>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_gemm_stationary_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_d, const KernelArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw);
+    const uint32_t staging = base + S_STAGES * S_STAGE_BYTES;
+    uint8_t* staging_ptr = base_ptr + S_STAGES * S_STAGE_BYTES;
+    const uint32_t bars = staging + STAGING_BYTES;
+    // barrier layout (8 bytes each): full[S_STAGES], empty[S_STAGES], acc_full[2], acc_empty[2]
+    const uint32_t full0 = bars, empty0 = bars + 8 * S_STAGES, accf0 = bars + 16 * S_STAGES, acce0 = accf0 + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + S_STAGES * S_STAGE_BYTES + STAGING_BYTES + 16 * S_STAGES + 32);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_blocks = g.k_blocks;
+    const int mt = static_cast<int>(blockIdx.x) % g.m_tiles, group = static_cast<int>(blockIdx.x) / g.m_tiles;
+    // this group's share of the column tiles
+    const uint32_t j0 = static_cast<uint32_t>(static_cast<uint64_t>(group) * g.col_tiles / g.groups);
+    const uint32_t j1 = static_cast<uint32_t>(static_cast<uint64_t>(group + 1) * g.col_tiles / g.groups);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S_STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(accf0 + 8 * b, 1);
+            mbar_init(acce0 + 8 * b, g.epi_warps);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp >= 2) {
+        // A -> tensor memory: the lane's row, 128 of its K elements per warp (warps 2-5 the first
+        // 128, warps 6-9 the rest), zero beyond M and K so that nothing undefined meets the
+        // zero-filled rows of B. Rows are read with 16-byte loads straight from global memory: 64 KiB
+        // per CTA, once.
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        const int64_t row = static_cast<int64_t>(mt) * BM + quarter * 32 + lane;
+        const uint16_t* arow = static_cast<const uint16_t*>(g.a) + row * g.lda;
+#pragma unroll 1
+        for (int q = 0; q < 2; ++q) {
+            const int col0 = half * 64 + q * 32;  // packed columns [col0, col0 + 32) = K elements [2 col0, 2 col0 + 64)
+            uint32_t v[32];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int k = 2 * col0 + 8 * u;
+                uint4 w = make_uint4(0u, 0u, 0u, 0u);
+                if (row < g.M && k < g.k_total) w = __ldg(reinterpret_cast<const uint4*>(arow + k));
+                v[4 * u] = w.x; v[4 * u + 1] = w.y; v[4 * u + 2] = w.z; v[4 * u + 3] = w.w;
+                if (k + 8 > g.k_total) {  // the row's pitch covers the 16 bytes, K does not: drop what lies past K
+#pragma unroll
+                    for (int e2 = 0; e2 < 4; ++e2) {
+                        const int first = k + 2 * e2;
+                        if (first >= g.k_total) v[4 * u + e2] = 0u;
+                        else if (first + 1 >= g.k_total) v[4 * u + e2] &= 0xFFFFu;
+                    }
+                }
+            }
+            tmem_store(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + S_A_COL + col0, v);
+        }
+        tmem_store_wait();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer ----
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t j = j0; ok && j < j1; ++j) {
+                const int batch = static_cast<int>(j / static_cast<uint32_t>(g.n_tiles));
+                const int nt = static_cast<int>(j - static_cast<uint32_t>(batch) * static_cast<uint32_t>(g.n_tiles));
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % S_STAGES;
+                    const uint32_t parity = ((it / S_STAGES) & 1) ^ 1;
+                    if (!mbar_wait(empty0 + 8 * s, parity, abort_flag)) { ok = false; break; }
+                    const uint32_t sb = base + s * S_STAGE_BYTES;
+                    mbar_expect_tx(full0 + 8 * s, S_STAGE_BYTES);
+                    // three boxes of 64 columns x BK rows, 8 KiB each; a box past the last column is zero fill
+#pragma unroll
+                    for (int c = 0; c < SN / 64; ++c)
+                        tma_load_3d(sb + c * (64 * BK * 2), &map_b, full0 + 8 * s, nt * SN + c * 64, kb * BK, g.b_batched ? batch : 0);
+                }
+            }
+            if (!ok) {
+                for (int spin = 0; spin < 4096; ++spin) __nanosleep(64);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer ------
+        if (lane == 0) {
+            const uint32_t fmt = g.is_bf16 ? 1u : 0u;
+            const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | (static_cast<uint32_t>(SN >> 3) << 17) |
+                                   (static_cast<uint32_t>(BM >> 4) << 24);
+            uint32_t it = 0, local_tile = 0;
+            bool ok = true;
+            for (uint32_t j = j0; ok && j < j1; ++j, ++local_tile) {
+                const int buf = local_tile & 1;
+                const uint32_t acc_parity = ((local_tile >> 1) & 1) ^ 1;
+                if (!mbar_wait(acce0 + 8 * buf, acc_parity, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t tmem_acc = tmem_base + buf * SN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % S_STAGES;
+                    const uint32_t parity = (it / S_STAGES) & 1;
+                    if (!mbar_wait(full0 + 8 * s, parity, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sb = base + s * S_STAGE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t db = smem_desc(sb + k * UMMA_K * 128, 64 * BK * 2, 1024);
+                        umma_f16_a_tmem(tmem_acc, tmem_base + S_A_COL + kb * (BK / 2) + k * (UMMA_K / 2), db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty0 + 8 * s);
+                }
+                if (ok) umma_commit(accf0 + 8 * buf);
+            }
+        }
+    } else if (warp - 2 < g.epi_warps) {
+        // ------------------------------------------------------------ epilogue --------
+        const int ew = warp - 2;
+        const int quarter = warp & 3;
+        uint8_t* stage = staging_ptr + ew * STAGING_WARP_BYTES;
+        uint32_t local_tile = 0;
+        int flip = 0;
+        bool ok = true;
+        const int64_t row0 = static_cast<int64_t>(mt) * BM + quarter * 32;
+        float bias = 0.0f;
+        if (g.bias != nullptr && row0 + lane < g.M) {
+            bias = g.is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(g.bias)[row0 + lane])
+                             : __half2float(static_cast<const __half*>(g.bias)[row0 + lane]);
+        }
+        for (uint32_t j = j0; ok && j < j1; ++j, ++local_tile) {
+            const int batch = static_cast<int>(j / static_cast<uint32_t>(g.n_tiles));
+            const int nt = static_cast<int>(j - static_cast<uint32_t>(batch) * static_cast<uint32_t>(g.n_tiles));
+            const int buf = local_tile & 1;
+            const uint32_t parity = (local_tile >> 1) & 1;
+            if (!mbar_wait(accf0 + 8 * buf, parity, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            EpilogueTile e;
+            e.dbase = static_cast<uint8_t*>(g.d) + static_cast<size_t>(batch) * g.d_batch * (OUT == OUT_F32 ? 4 : 2);
+            e.ldd = g.ldd;
+            e.row0 = row0;
+            e.rows = static_cast<int>(min(static_cast<int64_t>(32), g.M - row0));
+            e.col_base = static_cast<int64_t>(nt) * SN;
+            e.col_end = min(g.N, e.col_base + SN);
+            e.taddr0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * SN;
+            e.chunk0 = ew >> 2;
+            e.chunk_step = g.epi_warps >> 2;
+            e.bias = bias;
+            e.scale = g.scale;
+            e.vec_store = g.vec_store;
+            e.has_bias = g.bias != nullptr;
+            e.tma_store = g.tma_store;
+            e.batch = batch;
+            e.n_total = g.N;
+            e.map_d = &map_d;
+            drain_tile<typename out_type<OUT>::type, SCALE>(e, stage, lane, flip);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce0 + 8 * buf);
+        }
+        if (g.tma_store && lane == 0) bulk_wait_all();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && *abort_flag) atomicAdd(&g_tc_aborts, 1u);
+}
+
 // ------------------------------------------------------------------ host --------------
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -1026,6 +1273,31 @@ tn_status launch(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUten
                      : launch_scaled<MODE, OUT_F16, PACK_NONE>(map_a, map_b, map_d, g, stream);
 }
 
+template <int OUT, bool SCALE>
+tn_status launch_stationary_one(const CUtensorMap& map_b, const CUtensorMap& map_d, const KernelArgs& g, cudaStream_t stream) {
+    static thread_local int attr_device = -1;
+    int dev = 0;
+    TN_CUDA(cudaGetDevice(&dev));
+    if (attr_device != dev) {
+        TN_CUDA(cudaFuncSetAttribute(tc_gemm_stationary_kernel<OUT, SCALE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_device = dev;
+    }
+    KernelArgs args = g;
+    args.epi_warps = env_epilogue_warps() ? env_epilogue_warps() : 8;
+    tc_gemm_stationary_kernel<OUT, SCALE><<<g.groups * g.m_tiles, kThreads, SMEM_BYTES, stream>>>(map_b, map_d, args);
+    return after_launch("tc_gemm_stationary_kernel");
+}
+
+template <int OUT>
+tn_status launch_stationary_scaled(const CUtensorMap& map_b, const CUtensorMap& map_d, const KernelArgs& g, cudaStream_t stream) {
+    return g.has_scale ? launch_stationary_one<OUT, true>(map_b, map_d, g, stream) : launch_stationary_one<OUT, false>(map_b, map_d, g, stream);
+}
+
+tn_status launch_stationary(const CUtensorMap& map_b, const CUtensorMap& map_d, const KernelArgs& g, cudaStream_t stream) {
+    if (g.d_is_f32) return launch_stationary_scaled<OUT_F32>(map_b, map_d, g, stream);
+    return g.is_bf16 ? launch_stationary_scaled<OUT_BF16>(map_b, map_d, g, stream) : launch_stationary_scaled<OUT_F16>(map_b, map_d, g, stream);
+}
+
 }  // namespace
 
 bool tc_gemm_eligible(const TcGemm& p) {
@@ -1094,6 +1366,25 @@ tn_status tc_gemm(const TcGemm& p, cudaStream_t stream) {
         g.stat_max = p.stat_max;
         g.stat_sum = p.stat_sum;
         g.stat_argmax = p.stat_argmax;
+    }
+    // Short K with B as [K, N] and one A for all batches: A stays in tensor memory (see the stationary kernel).
+    static const bool no_stationary = getenv("TN_TC_NO_STATIONARY") != nullptr;
+    if (p.b_n_major && p.K <= S_KMAX && (p.a_batch == 0 || p.batches == 1) && g.pack_stage_bytes == 0 && !no_stationary) {
+        const int64_t sms = sm_count();
+        const int64_t n_tiles = ceil_div(p.N, SN), col_tiles = n_tiles * p.batches;
+        const int64_t groups = g.m_tiles <= sms ? sms / g.m_tiles : 0;
+        // enough column tiles per group to pay for loading A, and nearly all SMs in use
+        if (groups > 0 && col_tiles >= 8 * groups && groups * g.m_tiles * 10 >= sms * 9 && col_tiles < (int64_t(1) << 31)) {
+            g.a = p.a;
+            g.lda = p.lda;
+            g.k_total = (int)p.K;
+            g.groups = (int)groups;
+            g.col_tiles = (uint32_t)col_tiles;
+            g.n_tiles = (int)n_tiles;
+            g.tile_n = SN;
+            g.umma_n = SN;
+            return launch_stationary(map_b, map_d, g, stream);
+        }
     }
     return p.b_n_major ? launch<MODE_N>(map_a, map_b, map_d, g, stream) : launch<MODE_K>(map_a, map_b, map_d, g, stream);
 }
