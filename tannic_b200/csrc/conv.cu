@@ -31,29 +31,34 @@ struct ConvArgs {
     int64_t total;
 };
 
-// One thread per output element; threads of a warp share (n, co) almost always, so the
-// weight loads are broadcasts and the x loads are contiguous along the output row.
+// Fallback for everything the tensor-core paths do not take (fp32, fp64, integers, odd layouts).
+// One thread per output element; threads of a warp share (n, co) almost always, so the weight
+// loads are broadcasts and the x loads run along the output row. The taps that fall inside the
+// image form a rectangle [kh0, kh1) x [kw0, kw1) that depends only on the output position: it is
+// clipped once, and the loops below run over exactly the valid taps with running element offsets
+// instead of testing every tap. Terms are added channel by channel, tap row by tap row: the order
+// of the CPU reference, so floating-point results differ from it only by fused multiply-adds.
 template <typename C>
 __global__ void __launch_bounds__(kThreads) conv2d_direct(const __grid_constant__ ConvArgs g) {
     const int64_t step = (int64_t)gridDim.x * kThreads;
     for (int64_t o = (int64_t)blockIdx.x * kThreads + threadIdx.x; o < g.total; o += step) {
-        int64_t rem = o;
-        const int64_t ow = rem % g.Wo; rem /= g.Wo;
-        const int64_t oh = rem % g.Ho; rem /= g.Ho;
-        const int64_t co = rem % g.Cout;
-        const int64_t n = rem / g.Cout;
+        const int64_t row = o / g.Wo, ow = o - row * g.Wo;
+        const int64_t plane = row / g.Ho, oh = row - plane * g.Ho;
+        const int64_t n = plane / g.Cout, co = plane - n * g.Cout;
+        const int64_t top = oh * g.str_h - g.pad_h, left = ow * g.str_w - g.pad_w;  // input position of tap (0, 0)
+        const int64_t kh0 = top < 0 ? -top : 0, kh1 = min(g.Kh, g.H - top);
+        const int64_t kw0 = left < 0 ? -left : 0, kw1 = min(g.Kw, g.W - left);
         // the bias seeds the accumulator (src/cpu/conv2d.cpp:66-113)
         C acc = g.bias ? load_as<C>(g.bias, g.dt, co * g.bias_stride) : C(0);
-        const int64_t base_h = oh * g.str_h - g.pad_h, base_w = ow * g.str_w - g.pad_w;
-        for (int64_t ci = 0; ci < g.Cin; ++ci) {
-            for (int64_t kh = 0; kh < g.Kh; ++kh) {
-                const int64_t ih = base_h + kh;
-                if (ih < 0 || ih >= g.H) continue;
-                for (int64_t kw = 0; kw < g.Kw; ++kw) {
-                    const int64_t iw = base_w + kw;
-                    if (iw < 0 || iw >= g.W) continue;
-                    const C xv = load_as<C>(g.x, g.dt, n * g.xs[0] + ci * g.xs[1] + ih * g.xs[2] + iw * g.xs[3]);
-                    const C wv = load_as<C>(g.w, g.dt, co * g.ws[0] + ci * g.ws[1] + kh * g.ws[2] + kw * g.ws[3]);
+        int64_t x_plane = n * g.xs[0] + (top + kh0) * g.xs[2] + (left + kw0) * g.xs[3];
+        int64_t w_plane = co * g.ws[0] + kh0 * g.ws[2] + kw0 * g.ws[3];
+        for (int64_t ci = 0; ci < g.Cin; ++ci, x_plane += g.xs[1], w_plane += g.ws[1]) {
+            int64_t x_row = x_plane, w_row = w_plane;
+            for (int64_t kh = kh0; kh < kh1; ++kh, x_row += g.xs[2], w_row += g.ws[2]) {
+                int64_t xi = x_row, wi = w_row;
+                for (int64_t kw = kw0; kw < kw1; ++kw, xi += g.xs[3], wi += g.ws[3]) {
+                    const C xv = load_as<C>(g.x, g.dt, xi);
+                    const C wv = load_as<C>(g.w, g.dt, wi);
                     if constexpr (std::is_same<C, int64_t>::value) acc = (int64_t)((uint64_t)acc + (uint64_t)xv * (uint64_t)wv);
                     else acc += xv * wv;
                 }
@@ -169,6 +174,7 @@ __global__ void __launch_bounds__(256) pack_weights(const uint16_t* __restrict__
     }
 }
 
+
 bool dense_nchw(const tn_tensor_t* t) {
     int64_t expect = 1;
     for (int d = 3; d >= 0; --d) {
@@ -275,12 +281,13 @@ tn_status conv_impl(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_
             const dim3 tgrid((unsigned)ceil_div(g.H * g.W, 64), (unsigned)ceil_div(g.Cin, 64), (unsigned)g.N);
             tn_status st = TN_SUCCESS;
             bool weights_packed = false;
+            const bool vec_staging = !x_is_nhwc && dense_nchw(x) && (g.H * g.W) % 8 == 0 && (reinterpret_cast<uintptr_t>(g.x) & 15) == 0;
+            const WeightJob job{static_cast<const uint16_t*>(g.w), wp, g.Cout, g.Cin, g.Kh, g.Kw, g.ws[0], g.ws[1], g.ws[2], g.ws[3]};
             if (x_is_nhwc) {
                 xh = const_cast<uint16_t*>(static_cast<const uint16_t*>(g.x));
             } else {
-                if (dense_nchw(x) && (g.H * g.W) % 8 == 0 && (reinterpret_cast<uintptr_t>(g.x) & 15) == 0) {
+                if (vec_staging) {
                     // one launch for both re-layouts: the weights ride along in one extra z slice
-                    const WeightJob job{static_cast<const uint16_t*>(g.w), wp, g.Cout, g.Cin, g.Kh, g.Kw, g.ws[0], g.ws[1], g.ws[2], g.ws[3]};
                     const dim3 both(tgrid.x, tgrid.y, tgrid.z + 1);
                     nchw_to_nhwc_vec<<<both, 256, 0, s>>>(static_cast<const uint16_t*>(g.x), xh, g.Cin, g.H * g.W, g.N, job);
                     weights_packed = true;
