@@ -283,19 +283,20 @@ tn_status gemm_impl(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst
 
     // collapse the batch dims of an operand into one stride; possible when walking them in row-major
     // order advances by a constant stride, or the operand is shared by every batch
-    auto collapse_batches = [&](const int64_t* bs, int64_t* stride) {
+    auto collapse_in = [](const SimtArgs& q, const int64_t* bs, int64_t* stride) {
         bool any = false, all = true;
         int64_t expect = 0;
-        for (int dim = g.nbatch - 1; dim >= 0; --dim) {
-            if (g.bsize[dim] == 1) continue;
+        for (int dim = q.nbatch - 1; dim >= 0; --dim) {
+            if (q.bsize[dim] == 1) continue;
             if (bs[dim] == 0) { all = false; continue; }
             if (!any) { expect = bs[dim]; *stride = bs[dim]; any = true; }
             if (bs[dim] != expect) return false;
-            expect = bs[dim] * g.bsize[dim];
+            expect = bs[dim] * q.bsize[dim];
         }
         if (!any) { *stride = 0; return true; }
         return all;
     };
+    auto collapse_batches = [&](const int64_t* bs, int64_t* stride) { return collapse_in(g, bs, stride); };
 
     // ---- float32 on the tensor cores (three-way bfloat16 split), for products big enough to pay for
     //      the split passes: dense rows in the result, batch dims that collapse
@@ -376,45 +377,86 @@ tn_status gemm_impl(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst
 
     // ---- tensor-core path: 16-bit operands of one type, result of that type or fp32,
     //      row-major result, batch dims that collapse to one stride per operand.
+    // Returns TN_SUCCESS with *launched = false when the problem `q` is not one the kernel addresses.
+    auto half_on_tensor_cores = [&](const SimtArgs& q, bool with_stats, bool* launched) -> tn_status {
+        *launched = false;
+        int64_t sa = 0, sb = 0, sd = 0;
+        if (!(collapse_in(q, q.a_bs, &sa) && collapse_in(q, q.b_bs, &sb) && collapse_in(q, q.d_bs, &sd) && (sd != 0 || q.batches == 1)))
+            return TN_SUCCESS;
+        TcGemm p;
+        p.a = q.a;
+        p.b = q.b;
+        p.d = q.d;
+        p.ab_dtype = a->dtype;
+        p.d_dtype = dst->dtype;
+        p.M = q.M;
+        p.N = q.N;
+        p.K = q.K;
+        p.lda = q.a_sm;
+        p.b_n_major = q.b_sk != 1;  // then b_sn == 1: rows of B are N-contiguous
+        p.ldb = p.b_n_major ? q.b_sk : q.b_sn;
+        p.ldd = q.d_sm;
+        p.batches = q.batches;
+        p.a_batch = sa;
+        p.b_batch = sb;
+        p.d_batch = sd;
+        // [B, M, K] x shared [K, N] with dense A and D folds into one tall GEMM
+        if (q.batches > 1 && sb == 0 && sa == q.M * q.a_sm && sd == q.M * q.d_sm) {
+            p.M = q.M * q.batches;
+            p.batches = 1;
+            p.a_batch = p.d_batch = 0;
+        }
+        p.has_scale = q.has_scale != 0;
+        p.scale = (float)q.scale_f;
+        if (with_stats && stats && stats->any() && tc_gemm_can_fuse_stats(p)) {
+            // the epilogue keeps each row's maximum, sum and argmax while it drains the row
+            p.stat_max = stats->max ? stats->max->address : nullptr;
+            p.stat_sum = stats->sum ? stats->sum->address : nullptr;
+            p.stat_argmax = stats->argmax ? static_cast<int64_t*>(stats->argmax->address) : nullptr;
+            if (stats_done) *stats_done = true;
+        }
+        if (tc_gemm_eligible(p)) {
+            *launched = true;
+            return tc_gemm(p, s);
+        }
+        if (with_stats && stats_done) *stats_done = false;
+        return TN_SUCCESS;
+    };
     if (a->dtype == b->dtype && is_half(a->dtype) && (dst->dtype == a->dtype || dst->dtype == TN_FLOAT32) &&
         g.a_sk == 1 && g.d_sn == 1 && (g.b_sk == 1 || g.b_sn == 1) && g.K > 0) {
-        auto& collapse = collapse_batches;
-        int64_t sa = 0, sb = 0, sd = 0;
-        if (collapse(g.a_bs, &sa) && collapse(g.b_bs, &sb) && collapse(g.d_bs, &sd) && (sd != 0 || g.batches == 1)) {
-            TcGemm p;
-            p.a = g.a;
-            p.b = g.b;
-            p.d = g.d;
-            p.ab_dtype = a->dtype;
-            p.d_dtype = dst->dtype;
-            p.M = g.M;
-            p.N = g.N;
-            p.K = g.K;
-            p.lda = g.a_sm;
-            p.b_n_major = g.b_sk != 1;  // then b_sn == 1: rows of B are N-contiguous
-            p.ldb = p.b_n_major ? g.b_sk : g.b_sn;
-            p.ldd = g.d_sm;
-            p.batches = g.batches;
-            p.a_batch = sa;
-            p.b_batch = sb;
-            p.d_batch = sd;
-            // [B, M, K] x shared [K, N] with dense A and D folds into one tall GEMM
-            if (g.batches > 1 && sb == 0 && sa == g.M * g.a_sm && sd == g.M * g.d_sm) {
-                p.M = g.M * g.batches;
-                p.batches = 1;
-                p.a_batch = p.d_batch = 0;
+        bool launched = false;
+        TN_TRY(half_on_tensor_cores(g, true, &launched));
+        if (launched) return TN_SUCCESS;
+        // Batch dims that do not collapse as a whole (an operand that broadcasts over SOME of them:
+        // [2,1,M,K] x [2,3,K,N]) usually do once the outermost one is peeled off: one launch per
+        // index of that dim, each a batched problem over the remaining dims.
+        int outer = 0;
+        while (outer < g.nbatch && g.bsize[outer] == 1) ++outer;
+        if (outer < g.nbatch && g.bsize[outer] <= 64 && g.batches > g.bsize[outer]) {
+            const int64_t es = 2, ds = dst->dtype == TN_FLOAT32 ? 4 : 2;
+            auto slice = [&](int64_t i) {
+                SimtArgs q = g;
+                q.a = static_cast<const uint8_t*>(g.a) + i * g.a_bs[outer] * es;
+                q.b = static_cast<const uint8_t*>(g.b) + i * g.b_bs[outer] * es;
+                q.d = static_cast<uint8_t*>(g.d) + i * g.d_bs[outer] * ds;
+                q.batches = g.batches / g.bsize[outer];
+                q.bsize[outer] = 1;
+                return q;
+            };
+            // every slice has the same shape and strides; they differ in their base addresses only, and
+            // those stay 16-byte aligned when the peeled strides are multiples of 8 elements
+            const bool aligned = g.a_bs[outer] % 8 == 0 && g.b_bs[outer] % 8 == 0 && g.d_bs[outer] % 8 == 0;
+            if (aligned) {
+                TN_TRY(half_on_tensor_cores(slice(0), false, &launched));
+                if (launched) {
+                    for (int64_t i = 1; i < g.bsize[outer]; ++i) {
+                        bool again = false;
+                        TN_TRY(half_on_tensor_cores(slice(i), false, &again));
+                        if (!again) return fail(TN_ERROR, "gemm: slice %lld of a peeled batch dim was refused by the tensor-core path", (long long)i);
+                    }
+                    return TN_SUCCESS;
+                }
             }
-            p.has_scale = g.has_scale != 0;
-            p.scale = (float)g.scale_f;
-            if (stats && stats->any() && tc_gemm_can_fuse_stats(p)) {
-                // the epilogue keeps each row's maximum, sum and argmax while it drains the row
-                p.stat_max = stats->max ? stats->max->address : nullptr;
-                p.stat_sum = stats->sum ? stats->sum->address : nullptr;
-                p.stat_argmax = stats->argmax ? static_cast<int64_t*>(stats->argmax->address) : nullptr;
-                if (stats_done) *stats_done = true;
-            }
-            if (tc_gemm_eligible(p)) return tc_gemm(p, s);
-            if (stats_done) *stats_done = false;
         }
     }
 

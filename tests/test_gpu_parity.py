@@ -610,9 +610,32 @@ def test_matmul_batched_broadcast_and_more_than_256_batches():
     # rank-4 x rank-2 broadcast (tests/cpu/test-matmul.cpp: Rank4Rank2StridedTransposed)
     x, w = gen((2, 3, 40, 64), torch.float16, 34, -1, 1), gen((48, 64), torch.float16, 35, -1, 1)
     assert_close(tb.matmul(dev(x), dev(w).t()), oracle.matmul(x, w.t(), acc=oracle.ACC_WIDE))
-    # batch-broadcast first operand: falls back to the SIMT path
+    # batch-broadcast first operand: one A for every batch of B
     a, b = gen((1, 40, 64), torch.float16, 36, -1, 1), gen((5, 64, 24), torch.float16, 37, -1, 1)
     assert_close(tb.matmul(dev(a), dev(b)), oracle.matmul(a, b, acc=oracle.ACC_WIDE))
+    assert tb.device_errors() == 0
+
+
+@pytest.mark.parametrize("dtype", HALVES)
+def test_matmul_operand_broadcast_over_some_batch_dims(dtype):
+    """[2,1,M,K] x [2,3,K,N]: the first operand's batch dims do not collapse into one stride over the six
+    batches. The outermost batch dim is peeled off: one tensor-core launch per index, each over three batches."""
+    a, b = gen((2, 1, 72, 64), dtype, 38, -1, 1), gen((2, 3, 64, 48), dtype, 39, -1, 1)
+    launches = tb.launch_count()
+    got = tb.matmul(dev(a), dev(b))
+    assert tb.launch_count() - launches == 2
+    assert got.shape == (2, 3, 72, 48)
+    for i in range(2):
+        for j in range(3):
+            assert_close(got[i, j], oracle.matmul(a[i, 0], b[i, j], acc=oracle.ACC_WIDE))
+    # the second operand broadcast instead, transposed (K-major) layout
+    x, w = gen((3, 2, 40, 64), dtype, 40, -1, 1), gen((3, 1, 56, 64), dtype, 41, -1, 1)
+    launches = tb.launch_count()
+    got = tb.matmul(dev(x), dev(w).transpose(-1, -2))
+    assert tb.launch_count() - launches == 3
+    for i in range(3):
+        for j in range(2):
+            assert_close(got[i, j], oracle.matmul(x[i, j], w[i, 0].t(), acc=oracle.ACC_WIDE))
     assert tb.device_errors() == 0
 
 
