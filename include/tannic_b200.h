@@ -261,6 +261,24 @@ tn_status tn_eltwise_program(const tn_tensor_t* const* inputs, int n_inputs,
 tn_status tn_eltwise_program_host(const tn_device_t* device, const tn_tensor_t* const* inputs, int n_inputs,
                                   const tn_eltwise_node_t* nodes, int n_nodes, tn_tensor_t* dst, int chunks);
 
+/* Programs that none of the ahead-of-time compiled node lists covers are instantiated at run time:
+ * the library hands the text of its own kernel template plus the caller's node list to NVRTC
+ * (looked up with dlopen, CUDA headers under CUDA_HOME / CUDA_PATH / /usr/local/cuda), loads the
+ * sm_100a image and keeps it for the life of the process, keyed by device, element type, node list
+ * and operand kinds; immediates stay arguments. A compilation takes about a second, so by default
+ * only results of 2^20 elements and more trigger one. Without NVRTC, or when a compilation fails,
+ * the in-kernel interpreter runs the program instead: same results bit for bit, about a third of
+ * the speed. The reference has no counterpart (one kernel launch per node, include/tannic/tensor.hpp:351-371).
+ * mode: 0 = never compile, 1 = compile for large results (default; TN_PROGRAM_JIT=0 in the
+ * environment selects 0), 2 = always compile. */
+tn_status tn_program_jit_enable(int mode);
+/* Counters since the process started: programs compiled, compilations that failed (those programs are
+ * interpreted from then on), and whether NVRTC and its headers were found (0 before the first attempt
+ * finds them missing, too). Any pointer may be null. */
+tn_status tn_program_jit_stats(unsigned int* compiled, unsigned int* failed, unsigned int* available);
+/* Compiler output of the last failed compilation (empty when none failed); for diagnostics. */
+const char* tn_program_jit_log(void);
+
 /* ------------------------------------------------------------------ contractions ----- */
 
 /* reference: cuda::gemm, src/cuda/matmul.cu:189-191 (CPU twin src/cpu/matmul.cpp:254-256).

@@ -115,6 +115,8 @@ PROTOTYPES = {
     "tn_device_numa_node": [C.POINTER(DeviceT), C.POINTER(C.c_int)],
     "tn_host_allocate_pinned_near": [C.POINTER(DeviceT), C.c_size_t, C.POINTER(C.c_void_p)],
     "tn_bind_thread_near": [C.POINTER(DeviceT), C.POINTER(C.c_int)],
+    "tn_program_jit_enable": [C.c_int],
+    "tn_program_jit_stats": [C.POINTER(C.c_uint), C.POINTER(C.c_uint), C.POINTER(C.c_uint)],
     "tn_eltwise_program_host": [C.POINTER(DeviceT), C.POINTER(_TP), C.c_int, C.POINTER(EltwiseNode), C.c_int, _TP, C.c_int],
     "tn_gemm_scaled_stats": [_TP, _TP, C.POINTER(ScalarT), _TP, _TP, _TP, _TP, StreamT],
     "tn_rsqrt": [_TP, _TP, StreamT, C.c_float],
@@ -139,6 +141,7 @@ PROTOTYPES = {
     "tn_device_errors": [C.POINTER(C.c_uint)],
     "tn_selftest_bounded_wait": [C.POINTER(DeviceT), StreamT, C.c_uint],
     "tn_launch_count": [],
+    "tn_program_jit_log": [],
 }
 for _n in _UNARY:
     PROTOTYPES[f"tn_{_n}"] = [_TP, _TP, StreamT]
@@ -147,7 +150,7 @@ for _n in _BINARY:
 for _n in _REDUCE:
     PROTOTYPES[f"tn_{_n}"] = [_TP, _TP, StreamT, C.c_uint8]
 
-_RESTYPES = {"tn_dtype_size": C.c_size_t, "tn_last_error": C.c_char_p, "tn_launch_count": C.c_uint64, "tn_h2d_copy_count": C.c_uint64}
+_RESTYPES = {"tn_dtype_size": C.c_size_t, "tn_last_error": C.c_char_p, "tn_program_jit_log": C.c_char_p, "tn_launch_count": C.c_uint64, "tn_h2d_copy_count": C.c_uint64}
 
 
 def bind(cdll: C.CDLL, names=None) -> C.CDLL:

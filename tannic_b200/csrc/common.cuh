@@ -12,6 +12,7 @@
 #include <cstdio>
 
 #include "tannic_b200.h"
+#include "numeric.cuh"
 
 namespace tnb {
 
@@ -73,27 +74,6 @@ template <> struct dtype_of<__half> { static constexpr int value = TN_FLOAT16; }
 template <> struct dtype_of<__nv_bfloat16> { static constexpr int value = TN_BFLOAT16; };
 template <> struct dtype_of<float> { static constexpr int value = TN_FLOAT32; };
 template <> struct dtype_of<double> { static constexpr int value = TN_FLOAT64; };
-
-// Arithmetic type a storage type computes in: half types in float32 (rounded once on store,
-// as src/cuda/ops-unary.cu:116-136 does), integers in their own width (wrapping).
-template <typename T> struct compute_of { using type = T; };
-template <> struct compute_of<__half> { using type = float; };
-template <> struct compute_of<__nv_bfloat16> { using type = float; };
-
-template <typename C, typename T> __device__ __forceinline__ C to_compute(T v) { return static_cast<C>(v); }
-template <> __device__ __forceinline__ float to_compute<float, __half>(__half v) { return __half2float(v); }
-template <> __device__ __forceinline__ float to_compute<float, __nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
-template <> __device__ __forceinline__ double to_compute<double, __half>(__half v) { return (double)__half2float(v); }
-template <> __device__ __forceinline__ double to_compute<double, __nv_bfloat16>(__nv_bfloat16 v) { return (double)__bfloat162float(v); }
-
-template <typename T, typename C> __device__ __forceinline__ T from_compute(C v) { return static_cast<T>(v); }
-template <> __device__ __forceinline__ __half from_compute<__half, float>(float v) { return __float2half_rn(v); }
-template <> __device__ __forceinline__ __nv_bfloat16 from_compute<__nv_bfloat16, float>(float v) { return __float2bfloat16_rn(v); }
-template <> __device__ __forceinline__ __half from_compute<__half, double>(double v) { return __double2half(v); }
-template <> __device__ __forceinline__ __nv_bfloat16 from_compute<__nv_bfloat16, double>(double v) { return __double2bfloat16(v); }
-
-template <> __device__ __forceinline__ __half from_compute<__half, int64_t>(int64_t v) { return __float2half_rn((float)v); }
-template <> __device__ __forceinline__ __nv_bfloat16 from_compute<__nv_bfloat16, int64_t>(int64_t v) { return __float2bfloat16_rn((float)v); }
 
 // Runtime-typed element access for the generic (any dtype pair, any strides) kernels.
 // C is float, double or int64_t. Integer sources feeding a float32 class convert int -> float

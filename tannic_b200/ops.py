@@ -457,5 +457,17 @@ def device_errors() -> int:
     return n.value
 
 
+def program_jit(mode: int) -> None:
+    """0: never compile programs at run time, 1: for results of 2^20 elements and more, 2: always."""
+    A.check(A.lib().tn_program_jit_enable(int(mode)))
+
+
+def program_jit_stats() -> dict:
+    """Run-time compiled programs so far, failed compilations, and whether NVRTC is usable."""
+    c, f, a = C.c_uint(0), C.c_uint(0), C.c_uint(0)
+    A.check(A.lib().tn_program_jit_stats(C.byref(c), C.byref(f), C.byref(a)))
+    return {"compiled": c.value, "failed": f.value, "available": bool(a.value), "log": (A.lib().tn_program_jit_log() or b"").decode(errors="replace")}
+
+
 def launch_count() -> int:
     return int(A.lib().tn_launch_count())

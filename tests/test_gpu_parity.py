@@ -809,6 +809,18 @@ def test_matmul_half_to_float32_result():
     assert_close(got, want, tol=(1e-4, 1e-4))
 
 
+def test_matmul_short_k_shared_first_operand_float32_result():
+    """The kernel that keeps A in tensor memory, writing float32 (16 elements per store box instead of 32)."""
+    a, b = gen((136, 128), torch.bfloat16, 75, -1, 1), gen((260, 128, 1000), torch.bfloat16, 76, -1, 1)
+    got = tb.matmul(dev(a), dev(b), out_dtype=A.FLOAT32)
+    assert got.dtype == torch.float32 and got.shape == (260, 136, 1000)
+    for i in (0, 131, 259):
+        assert_close(got[i], oracle.matmul(a, b[i], acc=oracle.ACC_WIDE, out_dtype=A.FLOAT32), tol=(1e-4, 1e-4))
+    ref = torch.matmul(dev(a).float(), dev(b).float())
+    assert torch.allclose(got, ref, rtol=1e-3, atol=1e-3)
+    assert tb.device_errors() == 0
+
+
 def test_matmul_errors():
     a, b = dev(gen((4, 5), torch.float16, 1)), dev(gen((5, 3), torch.bfloat16, 2))
     with pytest.raises(A.TannicError) as e:
