@@ -405,6 +405,11 @@ tn_status tn_le(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn
  * healthy run); synchronises the device. The reference has no device-side waits to bound. */
 tn_status tn_device_errors(unsigned int* count);
 
+/* Diagnostics, no reference counterpart: launches of the tensor-core GEMM since load, by variant:
+ * [0] general kernel, [1] packed-row epilogue, [2] packed rows + fused row statistics, [3] stationary A
+ * (short K, A held in tensor memory). Convolutions through the implicit GEMM count under [0]. */
+tn_status tn_gemm_path_launches(uint64_t counts[4]);
+
 /* Failure-detection self-test, no reference counterpart: launches one warp that waits, with the same
  * bounded wait the tensor-core kernels use, on a barrier nothing ever completes. The wait runs out
  * after `polls` polls (about 64 ns each, capped at the kernels' own limit), the kernel returns

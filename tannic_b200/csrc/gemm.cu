@@ -7,6 +7,7 @@ namespace tnb {
 
 bool read_host_scalar(const tn_scalar_t* sc, double* f, int64_t* i);
 tn_status tc_abort_count(unsigned int* count);
+void tc_path_launches(uint64_t (&out)[4]);
 tn_status reduce_abort_count(unsigned int* count);
 tn_status tc_wait_probe(cudaStream_t stream, unsigned int polls);
 
@@ -580,6 +581,14 @@ tn_status tn_device_errors(unsigned int* count) {
     TN_TRY(tc_abort_count(&tc));
     TN_TRY(reduce_abort_count(&red));
     *count = tc + red;
+    return TN_SUCCESS;
+}
+
+tn_status tn_gemm_path_launches(uint64_t counts[4]) {
+    if (!counts) return fail(TN_ERROR, "null counts");
+    uint64_t c[4];
+    tc_path_launches(c);
+    for (int i = 0; i < 4; ++i) counts[i] = c[i];
     return TN_SUCCESS;
 }
 

@@ -64,6 +64,7 @@ constexpr uint32_t kSpinFast = 2048;      // polls without sleeping
 constexpr uint32_t kSpinLimit = 1u << 20; // then ~64 ns sleeps: gives up after roughly 0.1 s
 
 __device__ unsigned int g_tc_aborts = 0;
+std::atomic<uint64_t> g_path_launches[4];  // general, packed rows, packed rows + statistics, stationary A
 
 // ------------------------------------------------------------------ PTX wrappers ------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -1248,6 +1249,7 @@ tn_status launch_one(const CUtensorMap& map_a, const CUtensorMap& map_b, const C
         smem = 1024 + PACKED_STAGES * STAGE_BYTES + kEpilogueWarps * g.pack_stage_bytes + 256;
     }
     tc_gemm_kernel<MODE, OUT, SCALE, PACK><<<grid, kThreads, smem, stream>>>(map_a, map_b, map_d, args);
+    g_path_launches[PACK == PACK_NONE ? 0 : PACK == PACK_ROWS ? 1 : 2].fetch_add(1, std::memory_order_relaxed);
     return after_launch("tc_gemm_kernel");
 }
 
@@ -1285,6 +1287,7 @@ tn_status launch_stationary_one(const CUtensorMap& map_b, const CUtensorMap& map
     KernelArgs args = g;
     args.epi_warps = env_epilogue_warps() ? env_epilogue_warps() : 8;
     tc_gemm_stationary_kernel<OUT, SCALE><<<g.groups * g.m_tiles, kThreads, SMEM_BYTES, stream>>>(map_b, map_d, args);
+    g_path_launches[3].fetch_add(1, std::memory_order_relaxed);
     return after_launch("tc_gemm_stationary_kernel");
 }
 
@@ -1373,8 +1376,9 @@ tn_status tc_gemm(const TcGemm& p, cudaStream_t stream) {
         const int64_t sms = sm_count();
         const int64_t n_tiles = ceil_div(p.N, SN), col_tiles = n_tiles * p.batches;
         const int64_t groups = g.m_tiles <= sms ? sms / g.m_tiles : 0;
-        // enough column tiles per group to pay for loading A, and nearly all SMs in use
-        if (groups > 0 && col_tiles >= 8 * groups && groups * g.m_tiles * 10 >= sms * 9 && col_tiles < (int64_t(1) << 31)) {
+        // enough column tiles per CTA to pay for loading A (below about forty the general kernel is as
+        // fast or faster: measured on the 1x1 convolution with 16, 32 and 64 images), and nearly all SMs in use
+        if (groups > 0 && col_tiles >= 40 * groups && groups * g.m_tiles * 10 >= sms * 9 && col_tiles < (int64_t(1) << 31)) {
             g.a = p.a;
             g.lda = p.lda;
             g.k_total = (int)p.K;
@@ -1476,6 +1480,10 @@ tn_status tc_wait_probe(cudaStream_t stream, unsigned int polls) {
     if (polls > kSpinLimit) polls = kSpinLimit;
     wait_probe_kernel<<<1, 32, 0, stream>>>(polls);
     return after_launch("wait_probe_kernel");
+}
+
+void tc_path_launches(uint64_t (&out)[4]) {
+    for (int i = 0; i < 4; ++i) out[i] = g_path_launches[i].load(std::memory_order_relaxed);
 }
 
 tn_status tc_abort_count(unsigned int* count) {

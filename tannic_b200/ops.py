@@ -469,5 +469,12 @@ def program_jit_stats() -> dict:
     return {"compiled": c.value, "failed": f.value, "available": bool(a.value), "log": (A.lib().tn_program_jit_log() or b"").decode(errors="replace")}
 
 
+def gemm_path_launches() -> dict:
+    """Tensor-core GEMM launches since load, by kernel variant."""
+    c = (C.c_uint64 * 4)()
+    A.check(A.lib().tn_gemm_path_launches(c))
+    return {"general": c[0], "packed": c[1], "packed_stats": c[2], "stationary": c[3]}
+
+
 def launch_count() -> int:
     return int(A.lib().tn_launch_count())

@@ -686,11 +686,11 @@ def test_matmul_short_k_many_row_tiles(batches, m, n, k, n_major):
 
 
 @pytest.mark.parametrize("dtype,m,k,n,batches,lda,scale", [
-    (torch.float16, 200, 256, 818, 160, None, None),    # two row tiles (the second ragged), ragged last column tile
-    (torch.bfloat16, 128, 64, 1000, 300, None, 0.5),    # one K block, one row tile: 148 groups
-    (torch.float16, 200, 75, 816, 160, 80, None),       # K not a multiple of 8 inside a wider pitch: the tail of A must read as zero
-    (torch.float16, 1024, 256, 3136, 16, None, None),   # the 1x1-convolution geometry: eight row tiles, 18 groups
-    (torch.bfloat16, 300, 136, 200, 500, None, None),   # three row tiles, two column tiles per batch
+    (torch.float16, 200, 256, 824, 600, None, None),    # two row tiles (the second ragged), last column tile 56 wide
+    (torch.bfloat16, 128, 64, 1000, 1000, None, 0.5),   # one K block, one row tile: 148 groups
+    (torch.float16, 200, 75, 816, 600, 80, None),       # K not a multiple of 8 inside a wider pitch: the tail of A must read as zero
+    (torch.float16, 1024, 256, 3136, 48, None, None),   # the 1x1-convolution geometry: eight row tiles, 18 groups
+    (torch.bfloat16, 300, 136, 200, 1000, None, None),  # three row tiles, two column tiles per batch
 ])
 def test_matmul_short_k_shared_first_operand(dtype, m, k, n, batches, lda, scale):
     """One A[M, K <= 256] against many B[K, N] (N contiguous) with enough column tiles: the kernel
@@ -700,25 +700,30 @@ def test_matmul_short_k_shared_first_operand(dtype, m, k, n, batches, lda, scale
     a = a_full[:, :k]
     b = gen((batches, k, n), dtype, 71, -1, 1)
     da = dev(a_full)[:, :k]
+    before = tb.gemm_path_launches()["stationary"]
     got = tb.matmul(da, dev(b)) if scale is None else tb.matmul(da, dev(b), scale_by=scale)
+    assert tb.gemm_path_launches()["stationary"] == before + 1, "this shape is meant for the stationary-A kernel"
     assert got.shape == (batches, m, n)
     rows = slice(m - 72, m)
     for i in sorted({0, batches // 2, batches - 1}):
         want = oracle.matmul(a[rows].contiguous(), b[i], acc=oracle.ACC_WIDE)
         assert_close(got[i][rows], want if scale is None else oracle.scale(want, scale))
-    ref = torch.matmul(da.float(), dev(b).float()) * (scale or 1.0)
-    assert torch.allclose(got.float(), ref, rtol=2e-2, atol=2e-2 * (4 if dtype == torch.bfloat16 else 1))
+    for lo in range(0, batches, 100):  # every batch against a float32 product on the device, a slab at a time
+        ref = torch.matmul(da.float(), dev(b[lo:lo + 100]).float()) * (scale or 1.0)
+        assert torch.allclose(got[lo:lo + 100].float(), ref, rtol=2e-2, atol=2e-2 * (4 if dtype == torch.bfloat16 else 1))
     assert tb.device_errors() == 0
 
 
 @pytest.mark.parametrize("dtype", HALVES)
 def test_conv2d_1x1_many_images_with_bias(dtype):
     """1x1 convolution on NCHW with enough images for the stationary-weights kernel; bias per output channel."""
-    x = gen((72, 72, 40, 40), dtype, 72, -1, 1)
+    x = gen((336, 72, 40, 40), dtype, 72, -1, 1)
     wt = gen((200, 72, 1, 1), dtype, 73, -0.2, 0.2)
     bias = gen((200,), dtype, 74, -1, 1)
+    before = tb.gemm_path_launches()["stationary"]
     got = tb.convolve2D(dev(x), dev(wt), 1, 0, bias=dev(bias))
-    for i in (0, 35, 71):
+    assert tb.gemm_path_launches()["stationary"] == before + 1
+    for i in (0, 170, 335):
         assert_close(got[i:i + 1], oracle.conv2d(x[i:i + 1], wt, 1, 0, bias=bias, acc=oracle.ACC_WIDE))
     ref = torch.nn.functional.conv2d(dev(x).float(), dev(wt).float(), dev(bias).float())
     assert torch.allclose(got.float(), ref, rtol=2e-2, atol=3e-2)
@@ -811,10 +816,12 @@ def test_matmul_half_to_float32_result():
 
 def test_matmul_short_k_shared_first_operand_float32_result():
     """The kernel that keeps A in tensor memory, writing float32 (16 elements per store box instead of 32)."""
-    a, b = gen((136, 128), torch.bfloat16, 75, -1, 1), gen((260, 128, 1000), torch.bfloat16, 76, -1, 1)
+    a, b = gen((136, 128), torch.bfloat16, 75, -1, 1), gen((500, 128, 1000), torch.bfloat16, 76, -1, 1)
+    before = tb.gemm_path_launches()["stationary"]
     got = tb.matmul(dev(a), dev(b), out_dtype=A.FLOAT32)
-    assert got.dtype == torch.float32 and got.shape == (260, 136, 1000)
-    for i in (0, 131, 259):
+    assert tb.gemm_path_launches()["stationary"] == before + 1
+    assert got.dtype == torch.float32 and got.shape == (500, 136, 1000)
+    for i in (0, 131, 499):
         assert_close(got[i], oracle.matmul(a, b[i], acc=oracle.ACC_WIDE, out_dtype=A.FLOAT32), tol=(1e-4, 1e-4))
     ref = torch.matmul(dev(a).float(), dev(b).float())
     assert torch.allclose(got, ref, rtol=1e-3, atol=1e-3)
