@@ -4,7 +4,7 @@
 // Paths:
 //   1x1, stride 1, no padding, dense fp16/bf16 tensors -> batched tensor-core GEMM
 //        y[n] = W[Cout, Cin] . x[n][Cin, H*W]   (x[n] is an N-major B operand);
-//   other fp16/bf16 convolutions (stride 1..8) with Cin % 8 == 0 and Wout * stride <= 256 -> implicit GEMM on
+//   other fp16/bf16 convolutions (stride 1..8) with Wout * stride <= 256 -> implicit GEMM on
 //        the tcgen05 main loop: the activation is first re-laid as NHWC and the weights as
 //        [tap][Cout][Cin] in scratch memory (TMA needs the channel axis innermost: a tap shift
 //        of one pixel along W would otherwise break its 16-byte start alignment), then every
@@ -68,9 +68,10 @@ __global__ void __launch_bounds__(kThreads) conv2d_direct(const __grid_constant_
     }
 }
 
-// x[n, c, h, w] (any strides) -> out[n, h, w, c]; 64 channels x 64 pixels per CTA through a
+// x[n, c, h, w] (any strides) -> out[n, h, w, c] with the channel pitch padded to Cp (a multiple of 8,
+// the padding zero-filled, so that a pixel is a whole number of 16-byte units for TMA); 64 channels x 64 pixels per CTA through a
 // padded shared-memory tile so that both sides are contiguous 128-byte runs per 64 threads.
-__global__ void __launch_bounds__(256) nchw_to_nhwc(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, int64_t C,
+__global__ void __launch_bounds__(256) nchw_to_nhwc(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, int64_t C, int64_t Cp,
                                                     int64_t H, int64_t W, int64_t xs0, int64_t xs1, int64_t xs2, int64_t xs3) {
     __shared__ uint16_t tile[64][66];
     const int64_t HW = H * W;
@@ -92,7 +93,7 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc(const uint16_t* __restrict__
 #pragma unroll 4
         for (int i = 0; i < 16; ++i) {
             const int64_t p = p0 + pl + 4 * i;
-            if (p < HW && c < C) out[(n * HW + p) * C + c] = tile[cl][pl + 4 * i];
+            if (p < HW && c < Cp) out[(n * HW + p) * Cp + c] = tile[cl][pl + 4 * i];  // channels C..Cp-1 were staged as zeros
         }
     }
 }
@@ -102,18 +103,18 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc(const uint16_t* __restrict__
 struct WeightJob {
     const uint16_t* w;
     uint16_t* out;
-    int64_t Cout, Cin, Kh, Kw, ws0, ws1, ws2, ws3;
+    int64_t Cout, Cin, Cp, Kh, Kw, ws0, ws1, ws2, ws3;  // Cp: channel pitch of the packed weights (Cin rounded up to 8, zero-filled)
 };
 // w[co, ci, kh, kw] (any strides) -> out[kh*Kw + kw][co][ci], `part` of `parts` equal shares of thread blocks
 __device__ __forceinline__ void pack_weights_part(const WeightJob& j, int64_t part, int64_t parts) {
-    const int64_t total = j.Kh * j.Kw * j.Cout * j.Cin;
+    const int64_t total = j.Kh * j.Kw * j.Cout * j.Cp;
     for (int64_t i = part * 256 + threadIdx.x; i < total; i += parts * 256) {
         int64_t rem = i;
-        const int64_t ci = rem % j.Cin; rem /= j.Cin;
+        const int64_t ci = rem % j.Cp; rem /= j.Cp;
         const int64_t co = rem % j.Cout; rem /= j.Cout;
         const int64_t kw = rem % j.Kw;
         const int64_t kh = rem / j.Kw;
-        j.out[i] = j.w[co * j.ws0 + ci * j.ws1 + kh * j.ws2 + kw * j.ws3];
+        j.out[i] = ci < j.Cin ? j.w[co * j.ws0 + ci * j.ws1 + kh * j.ws2 + kw * j.ws3] : (uint16_t)0;
     }
 }
 
@@ -159,21 +160,8 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_vec(const uint16_t* __restri
     }
 }
 
-// w[co, ci, kh, kw] (any strides) -> out[kh*Kw + kw][co][ci]
-__global__ void __launch_bounds__(256) pack_weights(const uint16_t* __restrict__ w, uint16_t* __restrict__ out, int64_t Cout,
-                                                    int64_t Cin, int64_t Kh, int64_t Kw, int64_t ws0, int64_t ws1, int64_t ws2,
-                                                    int64_t ws3) {
-    const int64_t total = Kh * Kw * Cout * Cin;
-    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
-        int64_t rem = i;
-        const int64_t ci = rem % Cin; rem /= Cin;
-        const int64_t co = rem % Cout; rem /= Cout;
-        const int64_t kw = rem % Kw;
-        const int64_t kh = rem / Kw;
-        out[i] = w[co * ws0 + ci * ws1 + kh * ws2 + kw * ws3];
-    }
-}
-
+// The same re-layout as a launch of its own (activations that need no re-layout, or the element-wise one).
+__global__ void __launch_bounds__(256) pack_weights(WeightJob job) { pack_weights_part(job, blockIdx.x, gridDim.x); }
 
 bool dense_nchw(const tn_tensor_t* t) {
     int64_t expect = 1;
@@ -258,10 +246,13 @@ tn_status conv_impl(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_
 
     if (is_half(g.dt) && g.str_h <= 8 && g.str_w <= 8 && dense_nchw(y) && (!bias || g.bias_stride == 1) && g.N <= 65535) {
         TcConv p;
+        // a pixel of the NHWC copy must be a whole number of 16-byte units: channel counts that are not a
+        // multiple of 8 (a 3-channel stem) are padded with zero channels in the copy and in the packed weights
+        const int64_t Cp = (g.Cin + 7) & ~int64_t(7);
         p.bias = g.bias;
         p.y = g.y;
         p.dtype = g.dt;
-        p.N = g.N; p.C = g.Cin; p.H = g.H; p.W = g.W; p.Cout = g.Cout; p.Kh = g.Kh; p.Kw = g.Kw;
+        p.N = g.N; p.C = Cp; p.H = g.H; p.W = g.W; p.Cout = g.Cout; p.Kh = g.Kh; p.Kw = g.Kw;
         p.Ho = g.Ho; p.Wo = g.Wo; p.pad_h = g.pad_h; p.pad_w = g.pad_w;
         p.stride_h = g.str_h; p.stride_w = g.str_w;
         // placeholders so that the eligibility test sees aligned pointers; the real ones follow
@@ -270,9 +261,9 @@ tn_status conv_impl(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_
         if (tc_conv_eligible(p)) {
             // an activation that already lies as [N][H][W][C] in memory (an NCHW view of channels-last
             // storage) is read in place; only the weights are repacked then
-            const bool x_is_nhwc = g.xs[1] == 1 && g.xs[3] == g.Cin && g.xs[2] == g.W * g.Cin && g.xs[0] == g.H * g.W * g.Cin &&
+            const bool x_is_nhwc = Cp == g.Cin && g.xs[1] == 1 && g.xs[3] == g.Cin && g.xs[2] == g.W * g.Cin && g.xs[0] == g.H * g.W * g.Cin &&
                                    (reinterpret_cast<uintptr_t>(g.x) & 15) == 0;
-            const size_t x_bytes = x_is_nhwc ? 0 : (size_t)(g.N * g.H * g.W * g.Cin) * 2, w_bytes = (size_t)(g.Kh * g.Kw * g.Cout * g.Cin) * 2;
+            const size_t x_bytes = x_is_nhwc ? 0 : (size_t)(g.N * g.H * g.W * Cp) * 2, w_bytes = (size_t)(g.Kh * g.Kw * g.Cout * Cp) * 2;
             const size_t x_padded = (x_bytes + 255) & ~size_t(255);
             uint8_t* scratch = nullptr;
             TN_TRY(scratch_alloc(reinterpret_cast<void**>(&scratch), x_padded + w_bytes, s));
@@ -281,8 +272,8 @@ tn_status conv_impl(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_
             const dim3 tgrid((unsigned)ceil_div(g.H * g.W, 64), (unsigned)ceil_div(g.Cin, 64), (unsigned)g.N);
             tn_status st = TN_SUCCESS;
             bool weights_packed = false;
-            const bool vec_staging = !x_is_nhwc && dense_nchw(x) && (g.H * g.W) % 8 == 0 && (reinterpret_cast<uintptr_t>(g.x) & 15) == 0;
-            const WeightJob job{static_cast<const uint16_t*>(g.w), wp, g.Cout, g.Cin, g.Kh, g.Kw, g.ws[0], g.ws[1], g.ws[2], g.ws[3]};
+            const bool vec_staging = !x_is_nhwc && Cp == g.Cin && dense_nchw(x) && (g.H * g.W) % 8 == 0 && (reinterpret_cast<uintptr_t>(g.x) & 15) == 0;
+            const WeightJob job{static_cast<const uint16_t*>(g.w), wp, g.Cout, g.Cin, Cp, g.Kh, g.Kw, g.ws[0], g.ws[1], g.ws[2], g.ws[3]};
             if (x_is_nhwc) {
                 xh = const_cast<uint16_t*>(static_cast<const uint16_t*>(g.x));
             } else {
@@ -292,14 +283,14 @@ tn_status conv_impl(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_
                     nchw_to_nhwc_vec<<<both, 256, 0, s>>>(static_cast<const uint16_t*>(g.x), xh, g.Cin, g.H * g.W, g.N, job);
                     weights_packed = true;
                 } else {
-                    nchw_to_nhwc<<<tgrid, 256, 0, s>>>(static_cast<const uint16_t*>(g.x), xh, g.Cin, g.H, g.W, g.xs[0], g.xs[1], g.xs[2], g.xs[3]);
+                    nchw_to_nhwc<<<tgrid, 256, 0, s>>>(static_cast<const uint16_t*>(g.x), xh, g.Cin, Cp, g.H, g.W, g.xs[0], g.xs[1], g.xs[2], g.xs[3]);
                 }
                 st = after_launch("nchw_to_nhwc");
             }
             if (st == TN_SUCCESS && !weights_packed) {
-                int64_t wblocks = ceil_div(g.Kh * g.Kw * g.Cout * g.Cin, 256);
+                int64_t wblocks = ceil_div(g.Kh * g.Kw * g.Cout * Cp, 256);
                 if (wblocks > 1184) wblocks = 1184;
-                pack_weights<<<(unsigned)wblocks, 256, 0, s>>>(static_cast<const uint16_t*>(g.w), wp, g.Cout, g.Cin, g.Kh, g.Kw, g.ws[0], g.ws[1], g.ws[2], g.ws[3]);
+                pack_weights<<<(unsigned)wblocks, 256, 0, s>>>(job);
                 st = after_launch("pack_weights");
             }
             if (st == TN_SUCCESS) {

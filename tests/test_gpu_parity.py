@@ -715,6 +715,27 @@ def test_matmul_short_k_shared_first_operand(dtype, m, k, n, batches, lda, scale
 
 
 @pytest.mark.parametrize("dtype", HALVES)
+@pytest.mark.parametrize("shape", [
+    # (N, Cin, H, W, Cout, Kh, Kw, stride, pad)
+    (2, 3, 64, 64, 16, 7, 7, 2, 3),      # a ResNet-stem geometry: three input channels
+    (3, 20, 18, 24, 40, 3, 3, 1, 1),     # 20 channels: padded to 24
+    (1, 67, 12, 16, 8, 3, 3, 1, 0),      # two channel blocks, the second holds 3 real + 5 zero channels
+])
+def test_conv2d_channel_counts_that_are_not_multiples_of_8(dtype, shape):
+    """The NHWC copy and the packed weights pad the channel pitch to a multiple of 8 with zeros, so these
+    convolutions run on the tensor cores too (they used to fall to the one-thread-per-output kernel)."""
+    n, cin, h, w, cout, kh, kw, stride, pad = shape
+    x = gen((n, cin, h, w), dtype, 55, -1, 1)
+    wt = gen((cout, cin, kh, kw), dtype, 56, -0.2, 0.2)
+    bias = gen((cout,), dtype, 57, -1, 1)
+    before = tb.gemm_path_launches()["general"]
+    got = tb.convolve2D(dev(x), dev(wt), stride, pad, bias=dev(bias))
+    assert tb.gemm_path_launches()["general"] == before + 1, "expected the implicit GEMM"
+    assert_close(got, oracle.conv2d(x, wt, stride, pad, bias=bias, acc=oracle.ACC_WIDE))
+    assert tb.device_errors() == 0
+
+
+@pytest.mark.parametrize("dtype", HALVES)
 def test_conv2d_1x1_many_images_with_bias(dtype):
     """1x1 convolution on NCHW with enough images for the stationary-weights kernel; bias per output channel."""
     x = gen((336, 72, 40, 40), dtype, 72, -1, 1)
