@@ -719,20 +719,19 @@ __global__ void __launch_bounds__(256) reduce_cols_tiled(const T* __restrict__ s
     if (in_range) {
         const T* base = src + ou * len * inner + col0;
         int64_t l = l0 + ty;
-        // two rows in flight per thread
-        for (; l + 8 < l1; l += 16) {
-            alignas(16) T e0[VEC], e1[VEC];
-            if constexpr (VEC > 1) {
-                *reinterpret_cast<uint4*>(e0) = __ldg(reinterpret_cast<const uint4*>(base + l * inner));
-                *reinterpret_cast<uint4*>(e1) = __ldg(reinterpret_cast<const uint4*>(base + (l + 8) * inner));
-            } else {
-                e0[0] = __ldg(base + l * inner);
-                e1[0] = __ldg(base + (l + 8) * inner);
+        // four rows in flight per thread (64 bytes): with six CTAs resident per SM that is about 96 KiB
+        // of loads in flight per SM, enough to cover the HBM latency
+        for (; l + 24 < l1; l += 32) {
+            alignas(16) T e[4][VEC];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                if constexpr (VEC > 1) *reinterpret_cast<uint4*>(e[r]) = __ldg(reinterpret_cast<const uint4*>(base + (l + 8 * r) * inner));
+                else e[r][0] = __ldg(base + (l + 8 * r) * inner);
             }
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) st[k].feed(e0[k], l);
+            for (int r = 0; r < 4; ++r)
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) st[k].feed(e1[k], l + 8);
+                for (int k = 0; k < VEC; ++k) st[k].feed(e[r][k], l + 8 * r);
         }
         for (; l < l1; l += 8) {
             alignas(16) T e0[VEC];
@@ -937,8 +936,8 @@ tn_status launch(const tn_tensor_t* src, int axis, Outputs out, cudaStream_t s) 
         const bool vec = V > 1 && inner % V == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0;
         const int64_t per_thread = vec ? V : 1;
         const int64_t gx = ceil_div(inner, 32 * per_thread);
-        // split the reduced axis across CTAs until about two waves of CTAs exist
-        int64_t splits = ceil_div((int64_t)sm_count() * 2, gx * outer);
+        // split the reduced axis across CTAs until about six CTAs per SM exist
+        int64_t splits = ceil_div((int64_t)sm_count() * env_knob("TN_REDUCE_COLS_CTAS_PER_SM", 6), gx * outer);
         if (splits > len / 64) splits = len / 64;
         if (splits < 1) splits = 1;
         if (splits > 1024) splits = 1024;
