@@ -75,6 +75,42 @@ def gather_shards(local: torch.Tensor, total_rows: int, out: torch.Tensor | None
     return torch.cat([p[: b - a] for p, (a, b) in zip(parts, sizes)], dim=0)
 
 
+def produce_and_gather(out: torch.Tensor, rows_per_rank: int, produce, pieces: int = 4) -> torch.Tensor:
+    """Compute this rank's `rows_per_rank` leading rows of `out` piece by piece and ship every finished
+    piece to all other ranks while the next one is being computed.
+
+    `out` is the WHOLE result on every rank ([world * rows_per_rank, ...], dense); rank r owns rows
+    [r * rows_per_rank, (r + 1) * rows_per_rank). `produce(lo, hi, dst)` must enqueue, on the current
+    stream, the work that writes local rows [lo, hi) into `dst` (a view of this rank's own rows of `out`:
+    nothing is staged or copied on the owner). After each piece the N - 1 sends of it and the N - 1
+    receives of the peers' matching pieces go out as one grouped point-to-point call; the communication
+    library orders them after the work already on the current stream and runs them on its own stream, so
+    they overlap the next piece's kernel. Returns `out` once every piece of every rank has arrived.
+    With one rank it just runs `produce` over all rows."""
+    w, r = world()
+    mine = out[r * rows_per_rank:(r + 1) * rows_per_rank]
+    if w == 1:
+        produce(0, rows_per_rank, mine)
+        return out
+    pieces = max(1, min(int(pieces), rows_per_rank))
+    pending = []
+    for c in range(pieces):
+        lo, hi = c * rows_per_rank // pieces, (c + 1) * rows_per_rank // pieces
+        if hi <= lo:
+            continue
+        produce(lo, hi, mine[lo:hi])
+        ops = []
+        for peer in range(w):
+            if peer == r:
+                continue
+            ops.append(dist.P2POp(dist.isend, mine[lo:hi], peer))
+            ops.append(dist.P2POp(dist.irecv, out[peer * rows_per_rank + lo:peer * rows_per_rank + hi], peer))
+        pending.extend(dist.batch_isend_irecv(ops))
+    for req in pending:
+        req.wait()
+    return out
+
+
 def combine_sum(partial: torch.Tensor) -> torch.Tensor:
     """Sum over ranks of per-rank partial sums, accumulated as wide as the one-GPU reduction does
     (float32 for 16-bit floats, float64 for float32 / float64, int64 for integers)."""

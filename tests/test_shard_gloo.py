@@ -76,6 +76,18 @@ def _worker(rank, world, port, results):
             ok = False  # the whole tensor is not this rank's shard
         except ValueError:
             pass
+        # a product computed piece by piece, every finished piece shipped while the next is computed:
+        # rank r owns rows [r * 7, r * 7 + 7) of the whole result (7 rows do not split evenly into 3 pieces)
+        a_full, w_mat = torch.randn(world * 7, 6), torch.randn(6, 4)
+        whole = torch.full((world * 7, 4), float("nan"))
+        calls = []
+
+        def produce(lo, hi, dst):
+            calls.append((lo, hi))
+            dst.copy_(a_full[rank * 7 + lo:rank * 7 + hi] @ w_mat)
+
+        shard.produce_and_gather(whole, 7, produce, pieces=3)
+        ok = ok and torch.allclose(whole, a_full @ w_mat) and calls == [(0, 2), (2, 4), (4, 7)]
         results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
