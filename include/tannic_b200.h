@@ -405,6 +405,13 @@ tn_status tn_le(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn
  * healthy run); synchronises the device. The reference has no device-side waits to bound. */
 tn_status tn_device_errors(unsigned int* count);
 
+/* The tensor-core GEMM and convolution kernels are persistent, one thread block per SM, and a block fills
+ * its SM's shared memory: while one runs, no kernel of another stream gets an SM. A caller that wants a
+ * communication kernel (an NCCL send/receive of the rows just produced) to run UNDER the next GEMM sets a
+ * margin: these kernels then launch on (SM count - margin) SMs. Process-wide, 0..64, default 0. No reference
+ * counterpart. */
+tn_status tn_set_sm_margin(int sms);
+
 /* Diagnostics, no reference counterpart: launches of the tensor-core GEMM since load, by variant:
  * [0] general kernel, [1] packed-row epilogue, [2] packed rows + fused row statistics, [3] stationary A
  * (short K, A held in tensor memory). Convolutions through the implicit GEMM count under [0]. */

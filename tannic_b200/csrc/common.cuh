@@ -117,6 +117,7 @@ int env_knob(const char* name, int fallback);
 // Number of SMs of the current device (148 on B200); grids of the streaming kernels are sized
 // as a multiple of it.
 int sm_count();
+int sm_margin();  // SMs the persistent GEMM kernels leave to kernels of other streams (0 by default)
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

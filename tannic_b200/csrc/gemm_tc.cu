@@ -1236,7 +1236,7 @@ tn_status launch_one(const CUtensorMap& map_a, const CUtensorMap& map_b, const C
         TN_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<MODE, OUT, SCALE, PACK>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax));
         attr_device = dev;
     }
-    const int64_t sms = sm_count();
+    const int64_t sms = sm_count() - sm_margin();
     const int grid = (int)(g.total_tiles < sms ? g.total_tiles : sms);
     KernelArgs args = g;
     // A long main loop hides a 4-warp epilogue completely; short ones (HBM-bound shapes) are paced
@@ -1373,7 +1373,7 @@ tn_status tc_gemm(const TcGemm& p, cudaStream_t stream) {
     // Short K with B as [K, N] and one A for all batches: A stays in tensor memory (see the stationary kernel).
     static const bool no_stationary = getenv("TN_TC_NO_STATIONARY") != nullptr;
     if (p.b_n_major && p.K <= S_KMAX && (p.a_batch == 0 || p.batches == 1) && g.pack_stage_bytes == 0 && !no_stationary) {
-        const int64_t sms = sm_count();
+        const int64_t sms = sm_count() - sm_margin();
         const int64_t n_tiles = ceil_div(p.N, SN), col_tiles = n_tiles * p.batches;
         const int64_t groups = g.m_tiles <= sms ? sms / g.m_tiles : 0;
         // enough column tiles per CTA to pay for loading A (below about forty the general kernel is as

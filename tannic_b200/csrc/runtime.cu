@@ -161,6 +161,10 @@ int sm_count() {
     return ds.sms;
 }
 
+// SMs that the persistent tensor-core kernels leave free (see tn_set_sm_margin).
+static std::atomic<int> g_sm_margin{0};
+int sm_margin() { return g_sm_margin.load(std::memory_order_relaxed); }
+
 // The backend allocates from a memory pool of its own, so that keeping freed blocks (release
 // threshold = unlimited: the allocate/free pair around every expression temporary never goes back
 // to the driver) does not change the behaviour of the process-wide default pool, which other
@@ -235,6 +239,12 @@ extern "C" {
 size_t tn_dtype_size(tn_dtype dtype) { return (size_t)dtype_bytes((int)dtype); }
 
 const char* tn_last_error(void) { return error_buffer(); }
+
+tn_status tn_set_sm_margin(int sms) {
+    if (sms < 0 || sms > 64) return fail(TN_ERROR, "tn_set_sm_margin: %d is not in 0..64", sms);
+    g_sm_margin.store(sms, std::memory_order_relaxed);
+    return TN_SUCCESS;
+}
 
 uint64_t tn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

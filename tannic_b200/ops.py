@@ -469,6 +469,11 @@ def program_jit_stats() -> dict:
     return {"compiled": c.value, "failed": f.value, "available": bool(a.value), "log": (A.lib().tn_program_jit_log() or b"").decode(errors="replace")}
 
 
+def sm_margin(sms: int) -> None:
+    """SMs the persistent tensor-core kernels leave free for kernels of other streams (0 = none)."""
+    A.check(A.lib().tn_set_sm_margin(int(sms)))
+
+
 def gemm_path_launches() -> dict:
     """Tensor-core GEMM launches since load, by kernel variant."""
     c = (C.c_uint64 * 4)()

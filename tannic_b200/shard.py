@@ -75,40 +75,85 @@ def gather_shards(local: torch.Tensor, total_rows: int, out: torch.Tensor | None
     return torch.cat([p[: b - a] for p, (a, b) in zip(parts, sizes)], dim=0)
 
 
-def produce_and_gather(out: torch.Tensor, rows_per_rank: int, produce, pieces: int = 4) -> torch.Tensor:
-    """Compute this rank's `rows_per_rank` leading rows of `out` piece by piece and ship every finished
-    piece to all other ranks while the next one is being computed.
+class PeerBuffer:
+    """A result buffer that every rank of the box can write into: `local` is this rank's copy of the whole
+    result (an ordinary CUDA tensor, allocated as symmetric memory), `peers[p]` is rank p's copy mapped into
+    this process. A copy into `peers[p]` is a device-to-device `cudaMemcpyAsync` that the copy engines carry
+    over NVLink: no SM is involved, so it runs beside a kernel that fills every SM. Plumbing only (torch's
+    symmetric-memory allocator and rendezvous); no kernel of this library ever takes a peer's memory as an
+    operand. CUDA + NCCL process groups only."""
 
-    `out` is the WHOLE result on every rank ([world * rows_per_rank, ...], dense); rank r owns rows
-    [r * rows_per_rank, (r + 1) * rows_per_rank). `produce(lo, hi, dst)` must enqueue, on the current
-    stream, the work that writes local rows [lo, hi) into `dst` (a view of this rank's own rows of `out`:
-    nothing is staged or copied on the owner). After each piece the N - 1 sends of it and the N - 1
-    receives of the peers' matching pieces go out as one grouped point-to-point call; the communication
-    library orders them after the work already on the current stream and runs them on its own stream, so
-    they overlap the next piece's kernel. Returns `out` once every piece of every rank has arrived.
-    With one rank it just runs `produce` over all rows."""
+    def __init__(self, shape, dtype, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        device = torch.device("cuda", torch.cuda.current_device())
+        self.local = symm.empty(tuple(shape), dtype=dtype, device=device)
+        self.handle = symm.rendezvous(self.local, self.group)
+        w = dist.get_world_size(self.group)
+        self.peers = [self.handle.get_buffer(p, tuple(shape), dtype) for p in range(w)]
+        self.side = torch.cuda.Stream()
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def fence(self):
+        """Stream-ordered barrier over the group: whatever the ranks enqueued before it is complete
+        everywhere before anything enqueued after it starts (a one-element all-reduce)."""
+        dist.all_reduce(self._flag, group=self.group)
+
+
+def produce_and_gather(out, rows_per_rank: int, produce, pieces: int = 4) -> torch.Tensor:
+    """Compute this rank's `rows_per_rank` leading rows of the whole result piece by piece and ship every
+    finished piece to all other ranks while the next one is being computed.
+
+    `out` is the WHOLE result on every rank ([world * rows_per_rank, ...], dense): a `PeerBuffer`, or a
+    plain tensor. Rank r owns rows [r * rows_per_rank, (r + 1) * rows_per_rank). `produce(lo, hi, dst)`
+    must enqueue, on the current stream, the work that writes local rows [lo, hi) into `dst` (a view of
+    this rank's own rows of the result: nothing is staged or copied on the owner).
+
+    With a `PeerBuffer` every finished piece is copied into the peers' buffers by the copy engines on a side
+    stream (one `cudaMemcpyAsync` per peer and piece, ordered after the piece's kernel by an event), so the
+    transfer costs the producing kernel no SM; a stream-ordered fence before the first piece (nobody still
+    reads the previous result) and after the last copy (every piece has landed everywhere) brackets the call.
+    With a plain tensor the N - 1 sends of a piece and the N - 1 receives of the peers' matching pieces go out
+    as one grouped point-to-point call of the process group (NCCL: SM-based kernels, which overlap a
+    persistent GEMM only if it leaves them SMs, see tn_set_sm_margin; gloo on CPU). Returns the whole result
+    once every piece of every rank has arrived (in stream order). With one rank it just runs `produce`."""
     w, r = world()
-    mine = out[r * rows_per_rank:(r + 1) * rows_per_rank]
+    whole = out.local if isinstance(out, PeerBuffer) else out
+    mine = whole[r * rows_per_rank:(r + 1) * rows_per_rank]
     if w == 1:
         produce(0, rows_per_rank, mine)
-        return out
+        return whole
     pieces = max(1, min(int(pieces), rows_per_rank))
+    bounds = [(c * rows_per_rank // pieces, (c + 1) * rows_per_rank // pieces) for c in range(pieces)]
+    bounds = [(lo, hi) for lo, hi in bounds if hi > lo]
+    if isinstance(out, PeerBuffer):
+        out.fence()
+        main = torch.cuda.current_stream()
+        for lo, hi in bounds:
+            produce(lo, hi, mine[lo:hi])
+            done = torch.cuda.Event()
+            done.record(main)
+            out.side.wait_event(done)
+            with torch.cuda.stream(out.side):
+                for k in range(1, w):
+                    p = (r + k) % w  # every rank starts with a different peer
+                    out.peers[p][r * rows_per_rank + lo:r * rows_per_rank + hi].copy_(mine[lo:hi], non_blocking=True)
+        main.wait_stream(out.side)
+        out.fence()
+        return whole
     pending = []
-    for c in range(pieces):
-        lo, hi = c * rows_per_rank // pieces, (c + 1) * rows_per_rank // pieces
-        if hi <= lo:
-            continue
+    for lo, hi in bounds:
         produce(lo, hi, mine[lo:hi])
         ops = []
         for peer in range(w):
             if peer == r:
                 continue
             ops.append(dist.P2POp(dist.isend, mine[lo:hi], peer))
-            ops.append(dist.P2POp(dist.irecv, out[peer * rows_per_rank + lo:peer * rows_per_rank + hi], peer))
+            ops.append(dist.P2POp(dist.irecv, whole[peer * rows_per_rank + lo:peer * rows_per_rank + hi], peer))
         pending.extend(dist.batch_isend_irecv(ops))
     for req in pending:
         req.wait()
-    return out
+    return whole
 
 
 def combine_sum(partial: torch.Tensor) -> torch.Tensor:
