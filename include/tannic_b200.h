@@ -273,9 +273,11 @@ tn_status tn_eltwise_program_host(const tn_device_t* device, const tn_tensor_t* 
  * environment selects 0), 2 = always compile. */
 tn_status tn_program_jit_enable(int mode);
 /* Counters since the process started: programs compiled, compilations that failed (those programs are
- * interpreted from then on), and whether NVRTC and its headers were found (0 before the first attempt
- * finds them missing, too). Any pointer may be null. */
-tn_status tn_program_jit_stats(unsigned int* compiled, unsigned int* failed, unsigned int* available);
+ * interpreted from then on), whether NVRTC and its headers were found, and programs whose image was read
+ * from the disk cache instead of being compiled: when TN_PROGRAM_JIT_CACHE names a directory, compiled images
+ * are kept there between processes under a hash of everything they depend on (nothing is written anywhere
+ * otherwise). Any pointer may be null. */
+tn_status tn_program_jit_stats(unsigned int* compiled, unsigned int* failed, unsigned int* available, unsigned int* from_disk);
 /* Compiler output of the last failed compilation (empty when none failed); for diagnostics. */
 const char* tn_program_jit_log(void);
 

@@ -116,7 +116,7 @@ PROTOTYPES = {
     "tn_host_allocate_pinned_near": [C.POINTER(DeviceT), C.c_size_t, C.POINTER(C.c_void_p)],
     "tn_bind_thread_near": [C.POINTER(DeviceT), C.POINTER(C.c_int)],
     "tn_program_jit_enable": [C.c_int],
-    "tn_program_jit_stats": [C.POINTER(C.c_uint), C.POINTER(C.c_uint), C.POINTER(C.c_uint)],
+    "tn_program_jit_stats": [C.POINTER(C.c_uint), C.POINTER(C.c_uint), C.POINTER(C.c_uint), C.POINTER(C.c_uint)],
     "tn_eltwise_program_host": [C.POINTER(DeviceT), C.POINTER(_TP), C.c_int, C.POINTER(EltwiseNode), C.c_int, _TP, C.c_int],
     "tn_gemm_scaled_stats": [_TP, _TP, C.POINTER(ScalarT), _TP, _TP, _TP, _TP, StreamT],
     "tn_rsqrt": [_TP, _TP, StreamT, C.c_float],

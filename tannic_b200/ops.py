@@ -464,9 +464,9 @@ def program_jit(mode: int) -> None:
 
 def program_jit_stats() -> dict:
     """Run-time compiled programs so far, failed compilations, and whether NVRTC is usable."""
-    c, f, a = C.c_uint(0), C.c_uint(0), C.c_uint(0)
-    A.check(A.lib().tn_program_jit_stats(C.byref(c), C.byref(f), C.byref(a)))
-    return {"compiled": c.value, "failed": f.value, "available": bool(a.value), "log": (A.lib().tn_program_jit_log() or b"").decode(errors="replace")}
+    c, f, a, d = C.c_uint(0), C.c_uint(0), C.c_uint(0), C.c_uint(0)
+    A.check(A.lib().tn_program_jit_stats(C.byref(c), C.byref(f), C.byref(a), C.byref(d)))
+    return {"compiled": c.value, "failed": f.value, "available": bool(a.value), "from_disk": d.value, "log": (A.lib().tn_program_jit_log() or b"").decode(errors="replace")}
 
 
 def sm_margin(sms: int) -> None:

@@ -91,3 +91,32 @@ def test_small_results_are_interpreted_by_default():
     assert tb.program_jit_stats()["compiled"] == before
     with pytest.raises(A.TannicError):
         tb.program_jit(3)
+
+
+def test_disk_cache_between_processes(tmp_path):
+    """With TN_PROGRAM_JIT_CACHE set, a second process loads the image the first one compiled."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    script = (
+        "import json, torch, oracle\n"
+        "from tannic_b200 import _abi as A, ops as tb\n"
+        "x = oracle.fill((64, 512), torch.float16, 140, 'uniform', 0.5, 2.0).cuda()\n"
+        "w = oracle.fill((64, 512), torch.float16, 141, 'uniform', -1.0, 1.0).cuda()\n"
+        "tb.program_jit(2)\n"
+        "z = tb.program([x, w], [(A.OP_ADD, 0, 1), (A.OP_SINH, 4, 4), (A.OP_MUL, 5, 1)])\n"
+        "torch.cuda.synchronize()\n"
+        "s = tb.program_jit_stats(); s['sum'] = float(z.float().sum()); print(json.dumps(s))\n"
+    )
+    env = dict(os.environ, TN_PROGRAM_JIT_CACHE=str(tmp_path), PYTHONPATH=os.pathsep.join(sys.path))
+    runs = []
+    for _ in range(2):
+        done = subprocess.run([sys.executable, "-c", script], env=env, capture_output=True, text=True, timeout=300)
+        assert done.returncode == 0, done.stderr[-2000:]
+        runs.append(json.loads(done.stdout.strip().splitlines()[-1]))
+    assert runs[0]["compiled"] == 1 and runs[0]["from_disk"] == 0 and runs[0]["failed"] == 0
+    assert runs[1]["compiled"] == 0 and runs[1]["from_disk"] == 1 and runs[1]["failed"] == 0
+    assert runs[0]["sum"] == runs[1]["sum"]
+    assert len(list(tmp_path.glob("tnjit_*.bin"))) == 1
