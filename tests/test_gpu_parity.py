@@ -849,6 +849,28 @@ def test_matmul_short_k_shared_first_operand_float32_result():
     assert tb.device_errors() == 0
 
 
+def test_matmul_with_an_sm_margin():
+    """tn_set_sm_margin: the persistent tensor-core kernels run on fewer SMs and give the same bits."""
+    a, w = gen((3, 700, 256), torch.bfloat16, 77, -1, 1), gen((3, 520, 256), torch.bfloat16, 78, -1, 1)
+    x = gen((4, 64, 30, 40), torch.float16, 79, -1, 1)
+    k = gen((48, 64, 3, 3), torch.float16, 80, -0.2, 0.2)
+    want = tb.matmul(dev(a), dev(w).transpose(-1, -2))
+    want_conv = tb.convolve2D(dev(x), dev(k), 1, 1)
+    try:
+        for margin in (1, 32, 64):
+            tb.sm_margin(margin)
+            assert torch.equal(tb.matmul(dev(a), dev(w).transpose(-1, -2)).view(torch.int16), want.view(torch.int16))
+            assert torch.equal(tb.convolve2D(dev(x), dev(k), 1, 1).view(torch.int16), want_conv.view(torch.int16))
+        with pytest.raises(A.TannicError):
+            tb.sm_margin(65)
+        with pytest.raises(A.TannicError):
+            tb.sm_margin(-1)
+    finally:
+        tb.sm_margin(0)
+    assert_close(want[1], oracle.matmul(a[1], w[1].t(), acc=oracle.ACC_WIDE))
+    assert tb.device_errors() == 0
+
+
 def test_matmul_errors():
     a, b = dev(gen((4, 5), torch.float16, 1)), dev(gen((5, 3), torch.bfloat16, 2))
     with pytest.raises(A.TannicError) as e:
