@@ -117,7 +117,7 @@ def produce_and_gather(out, rows_per_rank: int, produce, pieces: int | None = No
     as one grouped point-to-point call of the process group (NCCL: SM-based kernels, which overlap a
     persistent GEMM only if it leaves them SMs, see tn_set_sm_margin; gloo on CPU). Returns the whole result
     once every piece of every rank has arrived (in stream order). With one rank it just runs `produce`.
-    `pieces` = None picks four pieces for two ranks and two from four ranks on."""
+    `pieces` = None picks four pieces for two ranks, two for up to four and one beyond."""
     w, r = world()
     whole = out.local if isinstance(out, PeerBuffer) else out
     mine = whole[r * rows_per_rank:(r + 1) * rows_per_rank]
@@ -127,8 +127,9 @@ def produce_and_gather(out, rows_per_rank: int, produce, pieces: int | None = No
     if pieces is None:
         # every copy or send costs a fixed few microseconds of idle link: with two ranks the kernel is the longer
         # part and four pieces hide most of the exchange; from four ranks on the exchange is the longer part and
-        # two large pieces keep the links busier (measured on config 3: 4 pieces 0.79 ms, 2 pieces 0.72 ms on 4 GPUs)
-        pieces = 4 if w <= 2 else 2
+        # fewer, larger pieces keep the links busier (measured on config 3: 4 / 2 / 1 pieces take 0.79 / 0.72 / 0.84 ms
+        # on 4 GPUs and 1.00 / 0.88 / 0.86 ms on 8, where the exchange is four times the kernel)
+        pieces = 4 if w <= 2 else 2 if w <= 4 else 1
     pieces = max(1, min(int(pieces), rows_per_rank))
     bounds = [(c * rows_per_rank // pieces, (c + 1) * rows_per_rank // pieces) for c in range(pieces)]
     bounds = [(lo, hi) for lo, hi in bounds if hi > lo]
