@@ -84,6 +84,11 @@ class PeerBuffer:
     operand. CUDA + NCCL process groups only."""
 
     def __init__(self, shape, dtype, group=None):
+        import os
+
+        # only plain peer copies are used here: no multicast object is bound to the buffer (a process that dies while
+        # its memory is bound to one can raise NVLink faults on its peers)
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
         self.group = group if group is not None else dist.group.WORLD
         device = torch.device("cuda", torch.cuda.current_device())
