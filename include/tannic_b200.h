@@ -318,6 +318,19 @@ tn_status tn_conv2d(const tn_tensor_t* x, const tn_tensor_t* w, tn_tensor_t* y, 
 tn_status tn_conv2d_bias(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_t* bias,
                          tn_tensor_t* y, tn_stream_t stream, const size_t pad[2],
                          const size_t stride[2]);
+/* Weights packed ahead of time, for callers whose convolution weights do not change between calls (no
+ * reference counterpart; the reference's kernel reads NCHW weights in place, src/cuda/conv2d.cu:8-47).
+ * The k x k tensor-core convolution reads its weights as [tap][Cout][Cin rounded up to 8]; tn_conv2d builds
+ * that copy on every call (inside the launch that re-lays the activation). tn_conv2d_packed_weights_size
+ * gives the size of the packed form (0: this dtype has none, 16-bit floats only), tn_conv2d_pack_weights
+ * writes it into `packed` (device memory of that size, 16-byte aligned), and tn_conv2d_prepacked is
+ * tn_conv2d / tn_conv2d_bias (bias may be null) that uses it wherever it would have packed `w` itself;
+ * `w` is still passed for its shape and for the convolutions that read it in place (1 x 1, fallback). */
+tn_status tn_conv2d_packed_weights_size(const tn_tensor_t* w, size_t* nbytes);
+tn_status tn_conv2d_pack_weights(const tn_tensor_t* w, void* packed, tn_stream_t stream);
+tn_status tn_conv2d_prepacked(const tn_tensor_t* x, const tn_tensor_t* w, const void* packed, const tn_tensor_t* bias,
+                              tn_tensor_t* y, tn_stream_t stream, const size_t pad[2], const size_t stride[2]);
+
 /* reference: cuda::conv1d, src/cuda/conv1d.cu (CPU twin src/cpu/conv1d.cpp): [N, C, L] signal,
  * [Cout, Cin, K] kernel; evaluated as the H = 1 case of conv2d. */
 tn_status tn_conv1d(const tn_tensor_t* x, const tn_tensor_t* w, tn_tensor_t* y, tn_stream_t stream,

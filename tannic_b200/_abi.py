@@ -126,6 +126,9 @@ PROTOTYPES = {
     "tn_gemm_scaled": [_TP, _TP, C.POINTER(ScalarT), _TP, StreamT],
     "tn_conv2d": [_TP, _TP, _TP, StreamT, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)],
     "tn_conv2d_bias": [_TP, _TP, _TP, _TP, StreamT, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)],
+    "tn_conv2d_packed_weights_size": [_TP, C.POINTER(C.c_size_t)],
+    "tn_conv2d_pack_weights": [_TP, C.c_void_p, StreamT],
+    "tn_conv2d_prepacked": [_TP, _TP, C.c_void_p, _TP, _TP, StreamT, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)],
     "tn_conv1d": [_TP, _TP, _TP, StreamT, C.c_size_t, C.c_size_t],
     "tn_outer": [_TP, _TP, _TP, StreamT],
     "tn_repeat": [_TP, _TP, C.c_int, C.c_int, StreamT],

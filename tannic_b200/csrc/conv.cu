@@ -172,8 +172,9 @@ bool dense_nchw(const tn_tensor_t* t) {
     return true;
 }
 
+// `prepacked`: weights already in the implicit GEMM's layout (tn_conv2d_pack_weights), or null.
 tn_status conv_impl(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_t* bias, tn_tensor_t* y,
-                    tn_stream_t stream, const size_t pad[2], const size_t stride[2]) {
+                    tn_stream_t stream, const size_t pad[2], const size_t stride[2], const void* prepacked = nullptr) {
     if (!x || !w || !y || !pad || !stride) return fail(TN_ERROR, "null argument");
     // dtypes must match, as in the reference's tables (src/cpu/conv2d.cpp:221-253)
     if (x->dtype != w->dtype || !is_numeric(x->dtype) || y->dtype != x->dtype || (bias && bias->dtype != x->dtype))
@@ -263,23 +264,25 @@ tn_status conv_impl(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_
             // storage) is read in place; only the weights are repacked then
             const bool x_is_nhwc = Cp == g.Cin && g.xs[1] == 1 && g.xs[3] == g.Cin && g.xs[2] == g.W * g.Cin && g.xs[0] == g.H * g.W * g.Cin &&
                                    (reinterpret_cast<uintptr_t>(g.x) & 15) == 0;
-            const size_t x_bytes = x_is_nhwc ? 0 : (size_t)(g.N * g.H * g.W * Cp) * 2, w_bytes = (size_t)(g.Kh * g.Kw * g.Cout * Cp) * 2;
+            if (prepacked != nullptr && (reinterpret_cast<uintptr_t>(prepacked) & 15) != 0) return fail(TN_ERROR, "conv2d: packed weights must be 16-byte aligned");
+            const size_t x_bytes = x_is_nhwc ? 0 : (size_t)(g.N * g.H * g.W * Cp) * 2;
+            const size_t w_bytes = prepacked ? 0 : (size_t)(g.Kh * g.Kw * g.Cout * Cp) * 2;
             const size_t x_padded = (x_bytes + 255) & ~size_t(255);
             uint8_t* scratch = nullptr;
-            TN_TRY(scratch_alloc(reinterpret_cast<void**>(&scratch), x_padded + w_bytes, s));
+            if (x_padded + w_bytes > 0) TN_TRY(scratch_alloc(reinterpret_cast<void**>(&scratch), x_padded + w_bytes, s));
             uint16_t* xh = reinterpret_cast<uint16_t*>(scratch);
-            uint16_t* wp = reinterpret_cast<uint16_t*>(scratch + x_padded);
+            uint16_t* wp = prepacked ? const_cast<uint16_t*>(static_cast<const uint16_t*>(prepacked)) : reinterpret_cast<uint16_t*>(scratch + x_padded);
             const dim3 tgrid((unsigned)ceil_div(g.H * g.W, 64), (unsigned)ceil_div(g.Cin, 64), (unsigned)g.N);
             tn_status st = TN_SUCCESS;
-            bool weights_packed = false;
+            bool weights_packed = prepacked != nullptr;
             const bool vec_staging = !x_is_nhwc && Cp == g.Cin && dense_nchw(x) && (g.H * g.W) % 8 == 0 && (reinterpret_cast<uintptr_t>(g.x) & 15) == 0;
             const WeightJob job{static_cast<const uint16_t*>(g.w), wp, g.Cout, g.Cin, Cp, g.Kh, g.Kw, g.ws[0], g.ws[1], g.ws[2], g.ws[3]};
             if (x_is_nhwc) {
                 xh = const_cast<uint16_t*>(static_cast<const uint16_t*>(g.x));
             } else {
                 if (vec_staging) {
-                    // one launch for both re-layouts: the weights ride along in one extra z slice
-                    const dim3 both(tgrid.x, tgrid.y, tgrid.z + 1);
+                    // one launch for both re-layouts: the weights ride along in one extra z slice (none when they came packed)
+                    const dim3 both(tgrid.x, tgrid.y, tgrid.z + (prepacked ? 0 : 1));
                     nchw_to_nhwc_vec<<<both, 256, 0, s>>>(static_cast<const uint16_t*>(g.x), xh, g.Cin, g.H * g.W, g.N, job);
                     weights_packed = true;
                 } else {
@@ -298,7 +301,7 @@ tn_status conv_impl(const tn_tensor_t* x, const tn_tensor_t* w, const tn_tensor_
                 p.w_packed = wp;
                 st = tc_conv(p, s);
             }
-            const tn_status fr = scratch_free(scratch, s);
+            const tn_status fr = scratch ? scratch_free(scratch, s) : TN_SUCCESS;
             return st != TN_SUCCESS ? st : fr;
         }
     }
@@ -322,6 +325,38 @@ extern "C" {
 tn_status tn_conv2d(const tn_tensor_t* x, const tn_tensor_t* w, tn_tensor_t* y, tn_stream_t stream, const size_t pad[2],
                     const size_t stride[2]) {
     return conv_impl(x, w, nullptr, y, stream, pad, stride);
+}
+
+// Weights in the layout the implicit GEMM reads: [tap][Cout][Cin rounded up to 8], zero-filled padding.
+static bool packable(const tn_tensor_t* w) { return w && w->rank == 4 && is_half(w->dtype); }
+
+tn_status tn_conv2d_packed_weights_size(const tn_tensor_t* w, size_t* nbytes) {
+    if (!w || !nbytes) return fail(TN_ERROR, "null argument");
+    if (w->rank != 4) return fail(TN_ERROR, "conv2d: expected weights of rank 4");
+    const size_t cp = (w->shape.sizes[1] + 7) & ~size_t(7);
+    *nbytes = packable(w) ? w->shape.sizes[2] * w->shape.sizes[3] * w->shape.sizes[0] * cp * 2 : 0;
+    return TN_SUCCESS;
+}
+
+tn_status tn_conv2d_pack_weights(const tn_tensor_t* w, void* packed, tn_stream_t stream) {
+    if (!w || !packed) return fail(TN_ERROR, "null argument");
+    if (!packable(w)) return fail(TN_UNSUPPORTED_DTYPE, "conv2d: only float16 / bfloat16 weights of rank 4 have a packed form");
+    if ((reinterpret_cast<uintptr_t>(packed) & 15) != 0) return fail(TN_ERROR, "conv2d: packed weights must be 16-byte aligned");
+    TN_TRY(use_device_of(w));
+    const int64_t cout = w->shape.sizes[0], cin = w->shape.sizes[1], kh = w->shape.sizes[2], kw = w->shape.sizes[3];
+    const int64_t cp = (cin + 7) & ~int64_t(7);
+    if (cout * cp * kh * kw == 0) return TN_SUCCESS;
+    const WeightJob job{static_cast<const uint16_t*>(w->address), static_cast<uint16_t*>(packed), cout, cin, cp, kh, kw,
+                        w->strides.sizes[0], w->strides.sizes[1], w->strides.sizes[2], w->strides.sizes[3]};
+    int64_t blocks = ceil_div(kh * kw * cout * cp, 256);
+    if (blocks > 1184) blocks = 1184;
+    pack_weights<<<(unsigned)blocks, 256, 0, as_cuda(stream)>>>(job);
+    return after_launch("pack_weights");
+}
+
+tn_status tn_conv2d_prepacked(const tn_tensor_t* x, const tn_tensor_t* w, const void* packed, const tn_tensor_t* bias, tn_tensor_t* y,
+                              tn_stream_t stream, const size_t pad[2], const size_t stride[2]) {
+    return conv_impl(x, w, bias, y, stream, pad, stride, packed);
 }
 
 // 1-D convolution as the H = 1 case of conv2d: [N, C, L] * [Cout, Cin, K] -> [N, Cout, Lout].

@@ -300,8 +300,23 @@ def _pair(v):
     return (v, v) if isinstance(v, int) else tuple(v)
 
 
-def convolve2D(x: torch.Tensor, w: torch.Tensor, stride=1, padding=0, bias: torch.Tensor | None = None) -> torch.Tensor:
-    """include/tannic/convolutions.hpp:185-273; note the reference's argument order (stride, padding)."""
+def pack_conv_weights(w: torch.Tensor) -> torch.Tensor | None:
+    """The weights in the layout the k x k tensor-core convolution reads (tn_conv2d_pack_weights), for
+    `convolve2D(..., packed=...)`; None for dtypes that have no packed form."""
+    n = C.c_size_t(0)
+    dw = desc(w)
+    A.check(A.lib().tn_conv2d_packed_weights_size(C.byref(dw), C.byref(n)))
+    if n.value == 0:
+        return None
+    packed = torch.empty(n.value // 2, dtype=torch.int16, device=w.device)
+    A.check(A.lib().tn_conv2d_pack_weights(C.byref(dw), C.c_void_p(packed.data_ptr()), current_stream(w)))
+    return packed
+
+
+def convolve2D(x: torch.Tensor, w: torch.Tensor, stride=1, padding=0, bias: torch.Tensor | None = None,
+               packed: torch.Tensor | None = None) -> torch.Tensor:
+    """include/tannic/convolutions.hpp:185-273; note the reference's argument order (stride, padding).
+    `packed`: the result of pack_conv_weights(w), for weights that do not change between calls."""
     if x.dim() != 4 or w.dim() != 4:
         raise ValueError("Only rank 4 tensors supported.")
     if x.dtype != w.dtype or (bias is not None and bias.dtype != x.dtype):
@@ -315,7 +330,11 @@ def convolve2D(x: torch.Tensor, w: torch.Tensor, stride=1, padding=0, bias: torc
     pad = (C.c_size_t * 2)(*p)
     strd = (C.c_size_t * 2)(*s)
     dx, dw, dd = desc(x), desc(w), desc(out)
-    if bias is None:
+    if packed is not None:
+        dbias = desc(bias) if bias is not None else None
+        A.check(A.lib().tn_conv2d_prepacked(C.byref(dx), C.byref(dw), C.c_void_p(packed.data_ptr()), C.byref(dbias) if dbias is not None else None,
+                                            C.byref(dd), current_stream(x), pad, strd))
+    elif bias is None:
         A.check(A.lib().tn_conv2d(C.byref(dx), C.byref(dw), C.byref(dd), current_stream(x), pad, strd))
     else:
         dbias = desc(bias)

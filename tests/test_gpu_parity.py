@@ -736,6 +736,26 @@ def test_conv2d_channel_counts_that_are_not_multiples_of_8(dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", HALVES)
+@pytest.mark.parametrize("shape", [(2, 64, 20, 24, 40, 3, 3, 1, 1), (2, 3, 32, 32, 16, 5, 5, 2, 2), (3, 72, 9, 16, 8, 1, 1, 1, 0)])
+def test_conv2d_with_weights_packed_ahead(dtype, shape):
+    """tn_conv2d_pack_weights + tn_conv2d_prepacked give the bits of tn_conv2d (with and without bias), the packed
+    copy is reusable, and the call that uses it launches no weight packing of its own."""
+    n, cin, h, w, cout, kh, kw, stride, pad = shape
+    x = dev(gen((n, cin, h, w), dtype, 58, -1, 1))
+    wt = dev(gen((cout, cin, kh, kw), dtype, 59, -0.2, 0.2))
+    bias = dev(gen((cout,), dtype, 60, -1, 1))
+    packed = tb.pack_conv_weights(wt)
+    assert packed is not None and packed.numel() == kh * kw * cout * ((cin + 7) // 8 * 8)
+    for b in (None, bias):
+        want = tb.convolve2D(x, wt, stride, pad, bias=b)
+        for _ in range(2):
+            got = tb.convolve2D(x, wt, stride, pad, bias=b, packed=packed)
+            assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    assert tb.pack_conv_weights(dev(gen((4, 3, 3, 3), torch.float32, 61, -1, 1))) is None
+    assert tb.device_errors() == 0
+
+
+@pytest.mark.parametrize("dtype", HALVES)
 def test_conv2d_1x1_many_images_with_bias(dtype):
     """1x1 convolution on NCHW with enough images for the stationary-weights kernel; bias per output channel."""
     x = gen((336, 72, 40, 40), dtype, 72, -1, 1)
