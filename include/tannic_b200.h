@@ -420,6 +420,17 @@ tn_status tn_le(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, tn
  * healthy run); synchronises the device. The reference has no device-side waits to bound. */
 tn_status tn_device_errors(unsigned int* count);
 
+/* The product, written into `dst` and, tile by tile from the same kernel, into up to seven further buffers of the
+ * same dtype, shape and strides: memory of OTHER GPUs mapped into this process (symmetric memory, IPC). The epilogue
+ * stores every 16 bytes of a result tile into each of them with plain stores that NVLink carries while the tensor
+ * cores work on the next tile, so a batch-sharded GEMM whose whole result every GPU needs is one kernel, not a GEMM
+ * followed by an all-gather. The caller orders the exchange (nobody reads a mirror before the kernel and a fence
+ * over the group have completed; `tannic_b200.shard.matmul_into_all` does it with two one-element all-reduces).
+ * 16-bit operands and result on the tensor-core path with 16-byte aligned bases and pitches; otherwise
+ * TN_ERROR (dst alone is then written). No reference counterpart. */
+tn_status tn_gemm_mirrored(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, const tn_tensor_t* const* mirrors,
+                           int n_mirrors, tn_stream_t stream);
+
 /* The tensor-core GEMM and convolution kernels are persistent, one thread block per SM, and a block fills
  * its SM's shared memory: while one runs, no kernel of another stream gets an SM. A caller that wants a
  * communication kernel (an NCCL send/receive of the rows just produced) to run UNDER the next GEMM sets a

@@ -144,6 +144,7 @@ PROTOTYPES = {
     "tn_device_errors": [C.POINTER(C.c_uint)],
     "tn_selftest_bounded_wait": [C.POINTER(DeviceT), StreamT, C.c_uint],
     "tn_launch_count": [],
+    "tn_gemm_mirrored": [_TP, _TP, _TP, C.POINTER(_TP), C.c_int, StreamT],
     "tn_set_sm_margin": [C.c_int],
     "tn_gemm_path_launches": [C.POINTER(C.c_uint64)],
     "tn_program_jit_log": [],

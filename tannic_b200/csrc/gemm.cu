@@ -216,6 +216,11 @@ struct StatsRequest {
     tn_tensor_t* sum = nullptr;
     tn_tensor_t* argmax = nullptr;
     bool any() const { return max || sum || argmax; }
+    // tn_gemm_mirrored: further result buffers (peer memory) the epilogue writes as well; `mirrored` reports
+    // whether the kernel that can do that took the product
+    void* mirrors[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int n_mirrors = 0;
+    bool* mirrored = nullptr;
 };
 
 tn_status gemm_impl(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, const tn_scalar_t* scale,
@@ -416,9 +421,15 @@ tn_status gemm_impl(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst
             p.stat_argmax = stats->argmax ? static_cast<int64_t*>(stats->argmax->address) : nullptr;
             if (stats_done) *stats_done = true;
         }
+        if (with_stats && stats && stats->n_mirrors > 0) {
+            for (int m = 0; m < stats->n_mirrors; ++m) p.mirrors[m] = stats->mirrors[m];
+            p.n_mirrors = stats->n_mirrors;
+        }
         if (tc_gemm_eligible(p)) {
             *launched = true;
-            return tc_gemm(p, s);
+            TN_TRY(tc_gemm(p, s));
+            if (p.n_mirrors > 0 && stats->mirrored) *stats->mirrored = true;
+            return TN_SUCCESS;
         }
         if (with_stats && stats_done) *stats_done = false;
         return TN_SUCCESS;
@@ -581,6 +592,31 @@ tn_status tn_device_errors(unsigned int* count) {
     TN_TRY(tc_abort_count(&tc));
     TN_TRY(reduce_abort_count(&red));
     *count = tc + red;
+    return TN_SUCCESS;
+}
+
+tn_status tn_gemm_mirrored(const tn_tensor_t* a, const tn_tensor_t* b, tn_tensor_t* dst, const tn_tensor_t* const* mirrors, int n_mirrors,
+                           tn_stream_t stream) {
+    if (!dst || (n_mirrors > 0 && !mirrors)) return fail(TN_ERROR, "null argument");
+    if (n_mirrors < 0 || n_mirrors > 7) return fail(TN_ERROR, "gemm_mirrored: %d mirrors, at most 7", n_mirrors);
+    StatsRequest request;
+    bool mirrored = false;
+    for (int m = 0; m < n_mirrors; ++m) {
+        const tn_tensor_t* t = mirrors[m];
+        if (!t) return fail(TN_ERROR, "gemm_mirrored: null mirror");
+        bool same = t->rank == dst->rank && t->dtype == dst->dtype && t->environment.kind == TN_DEVICE;
+        for (int d = 0; same && d < dst->rank; ++d) same = t->shape.sizes[d] == dst->shape.sizes[d] && t->strides.sizes[d] == dst->strides.sizes[d];
+        if (!same) return fail(TN_ERROR, "gemm_mirrored: mirror %d must have the result's dtype, shape and strides", m);
+        request.mirrors[m] = t->address;
+    }
+    request.n_mirrors = n_mirrors;
+    request.mirrored = &mirrored;
+    if (n_mirrors == 0) return gemm_entry(a, b, dst, nullptr, stream);
+    bool unused = false;
+    TN_TRY(gemm_entry(a, b, dst, nullptr, stream, &request, &unused));
+    if (!mirrored)
+        return fail(TN_ERROR, "gemm_mirrored: this product does not run on the tensor-core kernel that writes mirrors (16-bit operands and result, "
+                              "16-byte aligned bases and pitches); the result was written to dst only");
     return TN_SUCCESS;
 }
 

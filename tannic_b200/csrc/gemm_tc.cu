@@ -239,6 +239,10 @@ struct KernelArgs {
     int cblocks, kw, pad_h, pad_w, hbox, str_h;
     int epi_warps;             // 4 or 8 epilogue warps take part (the others exit at once)
     uint32_t pack_stage_bytes; // packed epilogue: bytes of one warp's staging block (multiple of 128)
+    // mirrored results: the same tile is also written, at the same offsets, into these buffers (other GPUs' memory
+    // mapped into this process); 16-bit results through the 16-byte store path only
+    void* mirror[7];
+    int n_mirrors;
     // stationary-A variant
     const void* a;             // first operand [M, K], K contiguous
     int64_t lda;
@@ -327,6 +331,9 @@ struct EpilogueTile {
     int batch;
     int64_t n_total;     // columns of the whole result
     const CUtensorMap* map_d;
+    void* const* mirrors;  // n_mirrors further result buffers of the same layout (peer memory), or null
+    int n_mirrors;
+    int64_t batch_elems;   // element offset of this batch inside a result buffer
 };
 
 // Writes one 32 x 32 block (lane = row, v = 32 consecutive columns starting at col0) through a
@@ -398,9 +405,15 @@ __device__ __forceinline__ void store_block(const EpilogueTile& e, uint32_t (&v)
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int r = i * 8 + (lane >> 2);
-                if (r < e.rows && col < e.col_end)
-                    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(e.dbase) + (e.row0 + r) * e.ldd + col) =
-                        *reinterpret_cast<const uint4*>(stage + r * 80 + seg * 16);
+                if (r < e.rows && col < e.col_end) {
+                    const uint4 val = *reinterpret_cast<const uint4*>(stage + r * 80 + seg * 16);
+                    const int64_t at = (e.row0 + r) * e.ldd + col;
+                    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(e.dbase) + at) = val;
+                    // the same 16 bytes into every mirror (plain stores into peer memory: NVLink carries them while
+                    // the tensor cores work on the next tile)
+                    for (int m = 0; m < e.n_mirrors; ++m)
+                        *reinterpret_cast<uint4*>(static_cast<uint16_t*>(e.mirrors[m]) + e.batch_elems + at) = val;
+                }
             }
         } else {
             // any alignment: one row of 32 elements per store instruction
@@ -906,6 +919,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             e.batch = batch;
             e.n_total = g.N;
             e.map_d = &map_d;
+            e.mirrors = g.mirror;
+            e.n_mirrors = g.n_mirrors;
+            e.batch_elems = static_cast<int64_t>(batch) * g.d_batch;
             drain_tile<typename out_type<OUT>::type, SCALE>(e, stage, lane, flip);
             // this warp has finished reading the accumulator
             tc_fence_before();
@@ -1121,6 +1137,9 @@ tc_gemm_stationary_kernel(const __grid_constant__ CUtensorMap map_b, const __gri
             e.batch = batch;
             e.n_total = g.N;
             e.map_d = &map_d;
+            e.mirrors = nullptr;
+            e.n_mirrors = 0;
+            e.batch_elems = 0;
             drain_tile<typename out_type<OUT>::type, SCALE>(e, stage, lane, flip);
             tc_fence_before();
             __syncwarp();
@@ -1369,6 +1388,21 @@ tn_status tc_gemm(const TcGemm& p, cudaStream_t stream) {
         g.stat_max = p.stat_max;
         g.stat_sum = p.stat_sum;
         g.stat_argmax = p.stat_argmax;
+    }
+    if (p.n_mirrors > 0) {
+        // mirrored results leave through the 16-byte store path only
+        if (p.n_mirrors > 7) return fail(TN_ERROR, "gemm: at most 7 mirrors");
+        if (g.d_is_f32 || !g.vec_store || wants_stats) return fail(TN_ERROR, "gemm: mirrored results need a 16-bit result whose base and pitches are multiples of 16 bytes");
+        for (int m = 0; m < p.n_mirrors; ++m) {
+            if (!aligned16(p.mirrors[m])) return fail(TN_ERROR, "gemm: mirror %d is not 16-byte aligned", m);
+            g.mirror[m] = p.mirrors[m];
+        }
+        g.n_mirrors = p.n_mirrors;
+        g.tma_store = 0;
+        g.pack_stage_bytes = 0;
+        g.stat_max = g.stat_sum = nullptr;
+        g.stat_argmax = nullptr;
+        return p.b_n_major ? launch<MODE_N>(map_a, map_b, map_d, g, stream) : launch<MODE_K>(map_a, map_b, map_d, g, stream);
     }
     // Short K with B as [K, N] and one A for all batches: A stays in tensor memory (see the stationary kernel).
     static const bool no_stationary = getenv("TN_TC_NO_STATIONARY") != nullptr;

@@ -25,6 +25,10 @@ struct TcGemm {
     float scale = 1.0f;
     // Optional fused row statistics of the (rounded, scaled) result along its last axis, indexed by
     // batch * M + row; usable when tc_gemm_can_fuse_stats(p). Value outputs have the result's dtype.
+    // Further result buffers of the same shape, dtype and pitches (memory of other GPUs mapped into this
+    // process): every tile is written into each of them as well, by plain 16-byte stores from the epilogue.
+    void* mirrors[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int n_mirrors = 0;
     void* stat_max = nullptr;
     void* stat_sum = nullptr;
     int64_t* stat_argmax = nullptr;

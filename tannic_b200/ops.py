@@ -278,6 +278,16 @@ def matmul(a: torch.Tensor, b: torch.Tensor, scale_by=None, out_dtype: int | Non
     return out
 
 
+def matmul_mirrored(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, mirrors) -> torch.Tensor:
+    """matmul(a, b) into `out` and, from the same kernel, into every tensor of `mirrors` (views of other GPUs'
+    memory with out's shape, dtype and strides): tn_gemm_mirrored."""
+    da, db, dd = desc(a), desc(b), desc(out)
+    records = [desc(m) for m in mirrors]
+    ptrs = (C.POINTER(A.TensorT) * _b.max(1, len(records)))(*[C.pointer(r) for r in records])
+    A.check(A.lib().tn_gemm_mirrored(C.byref(da), C.byref(db), C.byref(dd), ptrs, len(records), current_stream(a)))
+    return out
+
+
 def matmul_stats(a: torch.Tensor, b: torch.Tensor, scale_by=None, out: torch.Tensor | None = None):
     """(S, max, sum, argmax) with S = matmul(a, b) [* scalar] and the three statistics taken along S's
     last axis in the same kernel where the shape allows (tn_gemm_scaled_stats)."""

@@ -168,6 +168,27 @@ def produce_and_gather(out, rows_per_rank: int, produce, pieces: int | None = No
     return whole
 
 
+def matmul_into_all(buffer: PeerBuffer, rows_per_rank: int, a_local: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """The batch- or row-sharded product whose whole result every rank needs, as ONE kernel per rank: rank r
+    computes its `rows_per_rank` rows of `a_local @ b` and the GEMM's epilogue stores every result tile into
+    its slot of the whole result on this GPU and, through plain peer stores, on every other GPU
+    (`tn_gemm_mirrored`), so NVLink carries a tile while the tensor cores work on the next one. A
+    stream-ordered fence before the kernel (nobody still reads the previous result) and after it (every
+    rank's tiles have landed everywhere) brackets the call. Returns this rank's copy of the whole result."""
+    from . import ops as tb
+
+    w, r = world()
+    lo, hi = r * rows_per_rank, (r + 1) * rows_per_rank
+    mine = buffer.local[lo:hi]
+    if w == 1:
+        tb.matmul(a_local, b, out=mine)
+        return buffer.local
+    buffer.fence()
+    tb.matmul_mirrored(a_local, b, mine, [buffer.peers[(r + k) % w][lo:hi] for k in range(1, w)])
+    buffer.fence()
+    return buffer.local
+
+
 def combine_sum(partial: torch.Tensor) -> torch.Tensor:
     """Sum over ranks of per-rank partial sums, accumulated as wide as the one-GPU reduction does
     (float32 for 16-bit floats, float64 for float32 / float64, int64 for integers)."""

@@ -46,6 +46,12 @@ def _worker(rank, world, port, results):
             shard.produce_and_gather(shared, rows, produce, pieces=3)
             torch.cuda.synchronize()
             ok = ok and torch.equal(shared.local.view(torch.int16), whole.view(torch.int16))
+        # the same exchange inside the GEMM kernel: the epilogue stores every tile into the peers' buffers too
+        for _ in range(2):
+            shared.local.zero_()
+            got = shard.matmul_into_all(shared, rows, da, dw.t())
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(got.view(torch.int16), whole.view(torch.int16))
         ok = ok and tb.device_errors() == 0
         results[rank] = bool(ok)
     finally:
