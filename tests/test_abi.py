@@ -86,6 +86,28 @@ def test_host_tensors_are_refused_not_computed():
     assert lib.tn_argmean(C.byref(tb.desc(torch.ones(4, dtype=torch.int32))), C.byref(dd), A.StreamT(0), 0) == A.UNSUPPORTED_DTYPE
 
 
+def test_process_wide_switches_validate_their_arguments():
+    """Settings and counters that need no device: the SM margin, the run-time compiler's mode, the path counters."""
+    lib = A.lib()
+    assert lib.tn_set_sm_margin(65) == A.ERROR and b"0..64" in lib.tn_last_error()
+    assert lib.tn_set_sm_margin(-1) == A.ERROR
+    assert lib.tn_set_sm_margin(0) == A.SUCCESS
+    assert lib.tn_program_jit_enable(3) == A.ERROR
+    assert lib.tn_program_jit_enable(1) == A.SUCCESS
+    counts = (C.c_uint64 * 4)(9, 9, 9, 9)
+    assert lib.tn_gemm_path_launches(counts) == A.SUCCESS and list(counts) == [0, 0, 0, 0]  # nothing was launched in this process
+    stats = tb.program_jit_stats()
+    assert stats["compiled"] == 0 and stats["failed"] == 0 and stats["from_disk"] == 0 and stats["log"] == ""
+    # mirrors and packed weights are checked before any device work
+    t = tb.desc(torch.ones(2, 2, dtype=torch.bfloat16))
+    assert lib.tn_gemm_mirrored(C.byref(t), C.byref(t), C.byref(t), None, 8, A.StreamT(0)) == A.ERROR
+    n = C.c_size_t(7)
+    w = tb.desc(torch.ones(4, 3, 3, 3, dtype=torch.float16))
+    assert lib.tn_conv2d_packed_weights_size(C.byref(w), C.byref(n)) == A.SUCCESS and n.value == 3 * 3 * 4 * 8 * 2
+    w32 = tb.desc(torch.ones(4, 3, 3, 3, dtype=torch.float32))
+    assert lib.tn_conv2d_packed_weights_size(C.byref(w32), C.byref(n)) == A.SUCCESS and n.value == 0
+
+
 def test_front_end_rules_mirror_the_reference():
     # NumPy broadcast, include/tannic/operations.hpp:137-152
     assert tb.broadcast_shape((2, 1, 3), (1, 4, 3)) == (2, 4, 3)
